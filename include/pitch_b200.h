@@ -1,0 +1,199 @@
+/*
+ * pitch_b200.h - C ABI of the B200 (sm_100a) KV-cache codec.
+ *
+ * Drop-in boundary for the codec hot path of SwiftCham/PITCH.  The reference
+ * has no C interface: its kernels are reached through the Swift command
+ * encoders `Codec` (Sources/PITCH/Core/Codec.swift) and `ChannelCodec`
+ * (Sources/PITCH/PerChannel.swift:300-390), which validate the caller's
+ * buffers and append one compute dispatch to the caller's command buffer.
+ * Every entry point below replaces one of those methods; the comment on each
+ * names it.  Translation of terms:
+ *
+ *   MTLBuffer + byte offset   ->  pitch_buffer { device pointer, length, offset }
+ *   MTLCommandBuffer          ->  cudaStream_t (passed as void*)
+ *   throws PITCHError.<case>  ->  returned pitch_status (never throws, never aborts)
+ *
+ * All enqueue functions are stream-ordered: they launch and return; outputs
+ * are valid once the work queued on `stream` before them has completed.  They
+ * allocate nothing, are re-entrant and thread-safe, write exactly the bytes
+ * documented and leave every other byte of the output buffers untouched.
+ * Inputs are not inspected on the device path (same contract as
+ * Sources/PITCH/PITCH.swift:136-143).
+ *
+ * Plain C: no CUDA or torch types appear in any signature.
+ */
+#ifndef PITCH_B200_H
+#define PITCH_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PITCH_ABI_VERSION 1
+#define PITCH_DEFAULT_SEED 0x50495443u /* Sources/PITCH/PITCH.swift:18 */
+#define PITCH_MAX_DIM 1024             /* Sources/PITCH/Models/QuantConfig.swift:13 */
+#define PITCH_MIN_BITS 2               /* Sources/PITCH/Models/QuantConfig.swift:12 */
+#define PITCH_MAX_BITS 8
+#define PITCH_MAX_GROUP 65536          /* Sources/PITCH/PerChannel.swift:18 */
+
+/* One code per case of PITCHError (Sources/PITCH/Core/PITCHError.swift:10-19). */
+typedef enum pitch_status {
+    PITCH_OK = 0,
+    PITCH_ERR_INVALID_INPUT = 1,          /* .invalidInput */
+    PITCH_ERR_INVALID_BIT_WIDTH = 2,      /* .invalidBitWidth */
+    PITCH_ERR_INVALID_DIMENSION = 3,      /* .invalidDimension */
+    PITCH_ERR_CONFIGURATION_MISMATCH = 4, /* .configurationMismatch */
+    PITCH_ERR_KERNEL_UNAVAILABLE = 5,     /* .shaderCompilationFailed: no kernel image for this GPU */
+    PITCH_ERR_ENCODING_FAILED = 6,        /* .encodingFailed: launch error on an encode path */
+    PITCH_ERR_DECODING_FAILED = 7,        /* .decodingFailed: launch error on a decode path */
+    PITCH_ERR_DEVICE_NOT_SUPPORTED = 8    /* .metalNotSupported: no usable CUDA device */
+} pitch_status;
+
+/* Sources/PITCH/Models/QuantMethod.swift:8-11 */
+typedef enum pitch_method { PITCH_TURBO_QUANT = 0, PITCH_POLAR_QUANT = 1 } pitch_method;
+
+/* Element type of the full-precision side (encode input / decode output).  The reference is
+ * float32 only (README.md "Limitations"); fp16 and bf16 are converted inside the kernels. */
+typedef enum pitch_dtype { PITCH_F32 = 0, PITCH_F16 = 1, PITCH_BF16 = 2 } pitch_dtype;
+
+/* A device allocation and a byte offset into it: the (MTLBuffer, offset) pair of the reference.
+ * `offset` must be a non-negative multiple of 4 and `length - offset` must cover what the call
+ * reads or writes (Codec.check, Sources/PITCH/Core/Codec.swift:37-47). */
+typedef struct pitch_buffer {
+    void*   base;    /* device pointer to the start of the allocation */
+    int64_t length;  /* bytes in the allocation */
+    int64_t offset;  /* byte offset at which this call starts */
+} pitch_buffer;
+
+int pitch_abi_version(void);
+/* Static description of a status code. */
+const char* pitch_status_string(int status);
+/* Detail of the last failure on the calling thread (the associated String of PITCHError). */
+const char* pitch_last_error(void);
+
+/* Bytes of packed codes per vector / token: ceil(dim*bits/32)*4.
+ * QuantConfig.codeStride, Sources/PITCH/Models/QuantConfig.swift:47. */
+int pitch_code_stride(int dim, int bits);
+
+/* Registers the 2^bits ascending float32 centroids TurboQuant uses for (dim, bits), copied into
+ * a host-side table; kernels receive them by value at launch, as Codec.swift:93 does with
+ * setBytes.  Replaces TurboCodebooks.codebook(dim:bits:) (Sources/PITCH/TurboCodebooks.swift),
+ * whose values are reference/codebooks.json. */
+int pitch_set_codebook(int dim, int bits, const float* centroids);
+int pitch_has_codebook(int dim, int bits);
+
+/* Codec.encodeCompress (Sources/PITCH/Core/Codec.swift:70-103), reached from
+ * PITCH.enqueueEncode (Sources/PITCH/PITCH.swift:144-154).
+ * Reads  count*dim elements of `dtype` from input.
+ * Writes count*stride bytes of codes and count float32 scales (norm or rmax).
+ * count*dim is not limited to 32 bits (the reference rejects more, Codec.swift:30-32). */
+int pitch_enqueue_encode(int method, int dim, int bits, uint32_t seed, int dtype,
+                         pitch_buffer input, pitch_buffer codes, pitch_buffer scales,
+                         int64_t count, void* stream);
+
+/* Codec.encodeDecompress (Sources/PITCH/Core/Codec.swift:107-140), reached from
+ * PITCH.enqueueDecode (Sources/PITCH/PITCH.swift:156-165).
+ * Writes count*dim elements of `dtype` to output. */
+int pitch_enqueue_decode(int method, int dim, int bits, uint32_t seed, int dtype,
+                         pitch_buffer codes, pitch_buffer scales, pitch_buffer output,
+                         int64_t count, void* stream);
+
+/* ChannelCodec.encode (Sources/PITCH/PerChannel.swift:338-363), reached from
+ * PITCH.enqueuePerChannelEncode (PerChannel.swift:251-260).  Token-major input, groups of
+ * `group_size` tokens (the last may be partial).  Writes count*stride code bytes and
+ * ceil(count/group_size) * 2*dim fp16 values: dim minima then dim maxima per group. */
+int pitch_enqueue_channel_encode(int dim, int bits, int group_size, int dtype,
+                                 pitch_buffer input, pitch_buffer codes, pitch_buffer ranges,
+                                 int64_t count, void* stream);
+
+/* ChannelCodec.decode (Sources/PITCH/PerChannel.swift:365-389), reached from
+ * PITCH.enqueuePerChannelDecode (PerChannel.swift:261-270). */
+int pitch_enqueue_channel_decode(int dim, int bits, int group_size, int dtype,
+                                 pitch_buffer codes, pitch_buffer ranges, pitch_buffer output,
+                                 int64_t count, void* stream);
+
+/* The rotation alone, float32 in and out: wht / rotate / unrotate of the specification
+ * (reference/pitch_reference.py:21-34; wht_inplace and rand_sign in
+ * Sources/PITCH/Shaders/PITCHKernels.metal:34-55).  mode 0: unnormalised Walsh-Hadamard
+ * transform; 1: WHT(x * signs) / sqrt(dim); 2: WHT(y) * signs / sqrt(dim).  */
+int pitch_enqueue_rotate(int mode, int dim, uint32_t seed, pitch_buffer input, pitch_buffer output,
+                         int64_t count, void* stream);
+
+/* pack_codes / unpack_codes of the specification (reference/pitch_reference.py:68-90;
+ * pack_codes / unpack_code in Sources/PITCH/Shaders/PITCHKernels.metal:86-111): conversion
+ * between one int32 per code, shape (count, dim), and the packed little-endian bit stream. */
+int pitch_enqueue_pack_codes(int dim, int bits, pitch_buffer codes_i32, pitch_buffer packed,
+                             int64_t count, void* stream);
+int pitch_enqueue_unpack_codes(int dim, int bits, pitch_buffer packed, pitch_buffer codes_i32,
+                               int64_t count, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Whole-cache decode: the per-step bottleneck named in README.md:96 and shown in the usage
+ * pattern README.md:62-77 (one enqueueDecode per tensor over the whole cache).  One launch
+ * decodes every plane (a K or V tensor of the cache) for every segment (layer x KV head held by
+ * this GPU).  It computes exactly what one pitch_enqueue_decode / pitch_enqueue_channel_decode
+ * per (plane, segment) would, with the same results.
+ * ------------------------------------------------------------------------------------------- */
+typedef enum pitch_plane_kind {
+    PITCH_PLANE_TURBO = 0,   /* TurboQuant codes + float32 norms  */
+    PITCH_PLANE_POLAR = 1,   /* PolarQuant codes + float32 rmax   */
+    PITCH_PLANE_CHANNEL = 2  /* per-channel codes + fp16 ranges   */
+} pitch_plane_kind;
+
+typedef struct pitch_plane {
+    int32_t  kind;        /* pitch_plane_kind */
+    int32_t  bits;
+    int32_t  group_size;  /* PITCH_PLANE_CHANNEL only */
+    uint32_t seed;        /* rotation seed (turbo / polar) */
+    void*    codes;       /* segment s, token t at codes + s*codes_seg_stride + t*stride(dim,bits) */
+    int64_t  codes_seg_stride;
+    void*    side;        /* float32 [tokens] per segment, or fp16 [groups][2][dim] per segment */
+    int64_t  side_seg_stride;
+    void*    out;         /* [tokens][dim] of out_dtype per segment */
+    int64_t  out_seg_stride;
+} pitch_plane;
+
+typedef struct pitch_cache_desc {
+    int32_t dim;
+    int32_t out_dtype;   /* pitch_dtype */
+    int64_t segments;    /* layers x KV heads on this GPU */
+    int64_t tokens;      /* tokens currently held per segment */
+    int32_t n_planes;    /* 1..4 */
+    int32_t reserved;
+    pitch_plane planes[4];
+} pitch_cache_desc;
+
+/* All pointers must be 16-byte aligned and all segment strides multiples of 16. */
+int pitch_enqueue_cache_decode(const pitch_cache_desc* desc, void* stream);
+
+/* Appends n_new tokens per segment to every plane of a cache: the growing-cache pattern of
+ * README.md:62-71 (enqueueEncode of the new token at codesOffset = t*h*codeStride) and, for
+ * per-channel planes, README.md:85 ("the newest, partial group can be ... re-encoded as it
+ * grows").  desc->tokens is the number of tokens held BEFORE the call; the codes and side
+ * information of tokens [tokens, tokens + n_new) are written, for all segments, by one launch
+ * per plane.  Per-channel planes keep the newest group of each segment in float32 in
+ * `residual` ([segments][group_size][dim]); the new tokens are copied there and the whole group
+ * is re-encoded, so codes and ranges always equal a bulk encode of the tokens seen so far.
+ * All new tokens of a call must fall into one group: (tokens % group_size) + n_new <= group_size. */
+typedef struct pitch_append_src {
+    const void* input;            /* [segments][n_new][dim] elements of in_dtype */
+    int64_t input_seg_stride;     /* bytes between segments */
+    void*   residual;             /* per-channel planes only, else NULL */
+    int64_t residual_seg_stride;  /* bytes between segments, >= group_size*dim*4 */
+} pitch_append_src;
+
+int pitch_enqueue_cache_append(const pitch_cache_desc* desc, const pitch_append_src* src, int in_dtype,
+                               int64_t n_new, void* stream);
+
+/* 64-bit checksum of `bytes` bytes (multiple of 4) at buf: sum over 32-bit words w_i of
+ * (w_i + 1) * (2*i + 1) mod 2^64, ADDED onto *result (a device uint64 the caller zeroes).
+ * Used to compare shards across GPUs without moving them; no counterpart in the reference. */
+int pitch_enqueue_checksum(pitch_buffer buf, int64_t bytes, uint64_t* result_device, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PITCH_B200_H */

@@ -126,9 +126,11 @@ def unpack_codes(buf: bytes, n: int, d: int, b: int) -> np.ndarray:
     """Inverse of pack_codes (reference/pitch_reference.py:81-90)."""
     stride = code_stride_bytes(d, b)
     raw = np.frombuffer(buf, dtype=np.uint8, count=n * stride).reshape(n, stride)
-    bits = np.unpackbits(raw, axis=1, bitorder="little")[:, :d * b].reshape(n, d, b)
-    weights = (1 << np.arange(b, dtype=np.int64))
-    return (bits.astype(np.int64) * weights).sum(axis=2)
+    bits = np.unpackbits(raw, axis=1, bitorder="little")
+    codes = np.zeros((n, d), dtype=np.int64)
+    for k in range(b):
+        codes |= bits[:, k:d * b:b].astype(np.int64) << k
+    return codes
 
 
 # --------------------------------------------------------------------------- TurboQuant

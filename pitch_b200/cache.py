@@ -1,0 +1,235 @@
+"""A compressed KV cache held by one GPU, with one-launch whole-cache decode.
+
+The reference describes the pattern but leaves it to the caller (README.md:62-85): per
+generated token, ``enqueueEncode`` the new token of every head at its offset, then
+``enqueueDecode`` the whole cache; per-channel keys are encoded group by group, the
+newest partial group being re-encoded as it grows.  ``KVCache`` packages that pattern:
+
+* a *segment* is one (layer, KV head); a cache sharded over GPUs gives each rank a
+  contiguous range of segments and no rank ever touches another rank's memory;
+* a *plane* is one tensor of the cache (keys or values) with its codec: per-channel
+  (``ChannelQuantConfig``) or per-vector (``QuantConfig``, TurboQuant or PolarQuant);
+* ``append`` encodes new tokens for all segments (one launch per plane);
+* ``decode`` reconstructs every token of every segment and plane (one launch).
+
+Layout in device memory, per plane, segment-major and token-major:
+codes ``[segments][capacity * code_stride]`` bytes, side information
+``[segments][capacity]`` float32 (norm / rmax) or ``[segments][groups][2][dim]`` fp16
+(minima then maxima), output ``[segments][capacity][dim]`` of ``out_dtype``.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+from . import _native, codebooks
+from .codec import PITCH, native_dtype, stream_handle, torch_dtype
+from .config import ChannelQuantConfig, QuantConfig, QuantMethod
+from .errors import InvalidInput
+
+
+def _torch():
+    import torch
+    return torch
+
+
+@dataclass
+class _Plane:
+    name: str
+    config: object           # QuantConfig | ChannelQuantConfig
+    codes: object            # uint8 [segments, capacity * stride]
+    side: object             # float32 [segments, capacity] | float16 [segments, groups, 2, dim]
+    out: object              # out_dtype [segments, capacity, dim]
+    residual: object | None  # float32 [segments, group_size, dim] for per-channel planes
+
+    @property
+    def is_channel(self) -> bool:
+        return isinstance(self.config, ChannelQuantConfig)
+
+    @property
+    def kind(self) -> int:
+        if self.is_channel:
+            return _native.PLANE_CHANNEL
+        return _native.PLANE_TURBO if self.config.method is QuantMethod.turboQuant else _native.PLANE_POLAR
+
+
+class KVCache:
+    """Compressed keys and values for ``segments`` (layer x KV head) sequences of up to
+    ``capacity`` tokens of dimension ``dim``."""
+
+    def __init__(self, segments: int, dim: int, capacity: int, key_config, value_config, *,
+                 out_dtype="bfloat16", device=None, pitch: PITCH | None = None):
+        torch = _torch()
+        self.pitch = pitch if pitch is not None else PITCH(device)
+        self.device = self.pitch.device
+        if segments < 1 or capacity < 1:
+            raise InvalidInput("segments and capacity must be at least 1")
+        for cfg in (key_config, value_config):
+            if cfg.dim != dim:
+                raise InvalidInput(f"codec dimension {cfg.dim} differs from the cache's {dim}")
+        self.segments, self.dim = int(segments), int(dim)
+        self.capacity = (int(capacity) + 127) // 128 * 128      # keeps every segment stride 16-byte aligned
+        self.out_dtype = torch_dtype(out_dtype)
+        self.tokens = 0
+        self.planes = [self._make_plane("keys", key_config), self._make_plane("values", value_config)]
+        codebooks.register_all()
+
+    def _make_plane(self, name: str, cfg) -> _Plane:
+        torch = _torch()
+        S, C, d, dev = self.segments, self.capacity, self.dim, self.device
+        codes = torch.zeros((S, C * cfg.code_stride), dtype=torch.uint8, device=dev)
+        out = torch.zeros((S, C, d), dtype=self.out_dtype, device=dev)
+        if isinstance(cfg, ChannelQuantConfig):
+            groups = cfg.group_count(C)
+            side = torch.zeros((S, groups, 2, d), dtype=torch.float16, device=dev)
+            residual = torch.zeros((S, cfg.group_size, d), dtype=torch.float32, device=dev)
+        else:
+            side = torch.zeros((S, C), dtype=torch.float32, device=dev)
+            residual = None
+        return _Plane(name, cfg, codes, side, out, residual)
+
+    # ------------------------------------------------------------------ descriptors
+    def _desc(self, tokens: int) -> _native.CacheDesc:
+        d = _native.CacheDesc()
+        d.dim = self.dim
+        d.out_dtype = native_dtype(self.out_dtype)
+        d.segments = self.segments
+        d.tokens = tokens
+        d.n_planes = len(self.planes)
+        for i, pl in enumerate(self.planes):
+            q = d.planes[i]
+            q.kind = pl.kind
+            q.bits = pl.config.bits
+            q.group_size = pl.config.group_size if pl.is_channel else 0
+            q.seed = 0 if pl.is_channel else pl.config.seed
+            q.codes = pl.codes.data_ptr()
+            q.codes_seg_stride = pl.codes.stride(0) * pl.codes.element_size()
+            q.side = pl.side.data_ptr()
+            q.side_seg_stride = pl.side.stride(0) * pl.side.element_size()
+            q.out = pl.out.data_ptr()
+            q.out_seg_stride = pl.out.stride(0) * pl.out.element_size()
+        return d
+
+    # ------------------------------------------------------------------ writing
+    def _check_new(self, x, name: str):
+        torch = _torch()
+        if not (isinstance(x, torch.Tensor) and x.is_cuda and x.is_contiguous()):
+            raise InvalidInput(f"{name} must be a contiguous CUDA tensor")
+        if x.dim() != 3 or x.shape[0] != self.segments or x.shape[2] != self.dim:
+            raise InvalidInput(f"{name} must have shape [segments={self.segments}, n_new, dim={self.dim}]")
+        torch_dtype(x.dtype)
+        return x
+
+    def append(self, keys, values, stream=None) -> None:
+        """Encodes ``n_new`` tokens per segment (tensors ``[segments, n_new, dim]``, float32 /
+        float16 / bfloat16, same dtype for both) at positions ``[tokens, tokens + n_new)``.
+        Stream-ordered; never waits."""
+        keys, values = self._check_new(keys, "keys"), self._check_new(values, "values")
+        if keys.shape != values.shape or keys.dtype != values.dtype:
+            raise InvalidInput("keys and values must have the same shape and dtype")
+        n_new = int(keys.shape[1])
+        if n_new < 1:
+            raise InvalidInput("n_new must be at least 1")
+        if self.tokens + n_new > self.capacity:
+            raise InvalidInput(f"cache holds {self.tokens} of {self.capacity} tokens; cannot append {n_new}")
+        limit = min([pl.config.group_size for pl in self.planes if pl.is_channel] + [65535])
+        done = 0
+        while done < n_new:
+            room = limit - (self.tokens % limit) if limit != 65535 else limit
+            step = min(room, n_new - done)
+            self._append_piece(keys, values, done, step, stream)
+            self.tokens += step
+            done += step
+
+    def _append_piece(self, keys, values, first: int, n: int, stream) -> None:
+        desc = self._desc(self.tokens)
+        src = (_native.AppendSrc * 4)()
+        for i, (pl, x) in enumerate(zip(self.planes, (keys, values))):
+            esz = x.element_size()
+            src[i].input = x.data_ptr() + first * self.dim * esz
+            src[i].input_seg_stride = x.stride(0) * esz
+            if pl.residual is not None:
+                src[i].residual = pl.residual.data_ptr()
+                src[i].residual_seg_stride = pl.residual.stride(0) * 4
+        st = _native.lib().pitch_enqueue_cache_append(ctypes.byref(desc), src, native_dtype(keys.dtype), n,
+                                                      stream_handle(stream, self.device))
+        _native.check(st)
+
+    def prefill(self, keys, values, stream=None) -> None:
+        """Bulk-encodes ``[segments, T, dim]`` tensors into an empty cache with the stand-alone
+        encoders (whole groups for per-channel planes), then appends what is left of a final
+        partial group so that it stays re-encodable."""
+        keys, values = self._check_new(keys, "keys"), self._check_new(values, "values")
+        if self.tokens != 0:
+            raise InvalidInput("prefill needs an empty cache")
+        T = int(keys.shape[1])
+        if T > self.capacity:
+            raise InvalidInput(f"{T} tokens exceed the capacity {self.capacity}")
+        groups = [pl.config.group_size for pl in self.planes if pl.is_channel]
+        bulk = T if not groups else T // max(groups) * max(groups)
+        if len(set(groups)) > 1:
+            raise InvalidInput("per-channel planes of one cache must share a group size")
+        p = self.pitch
+        esz = keys.element_size()
+        for pl, x in zip(self.planes, (keys, values)):
+            if bulk == 0:
+                break
+            for s in range(self.segments):
+                in_off = s * x.stride(0) * esz
+                c_off = s * pl.codes.stride(0)
+                s_off = s * pl.side.stride(0) * pl.side.element_size()
+                if pl.is_channel:
+                    p.enqueue_per_channel_encode(x, pl.codes, pl.side, bulk, pl.config, input_offset=in_off,
+                                                 codes_offset=c_off, ranges_offset=s_off, stream=stream)
+                else:
+                    p.enqueue_encode(x, pl.codes, pl.side, bulk, pl.config, input_offset=in_off,
+                                     codes_offset=c_off, scales_offset=s_off, stream=stream)
+        self.tokens = bulk
+        if bulk < T:
+            self.append(keys[:, bulk:].contiguous(), values[:, bulk:].contiguous(), stream)
+
+    def truncate(self, tokens: int) -> None:
+        """Forgets every token from ``tokens`` on (host-side bookkeeping only).  The new length
+        must be a multiple of the per-channel group size so that no partial group is cut."""
+        if not 0 <= tokens <= self.tokens:
+            raise InvalidInput(f"cannot truncate {self.tokens} tokens to {tokens}")
+        for pl in self.planes:
+            if pl.is_channel and tokens % pl.config.group_size:
+                raise InvalidInput("truncate to a multiple of the group size")
+        self.tokens = int(tokens)
+
+    # ------------------------------------------------------------------ reading
+    def decode(self, stream=None):
+        """Queues the reconstruction of all ``tokens`` tokens of every segment and plane and
+        returns views ``[segments, tokens, dim]`` of the key and value output buffers (valid
+        once the stream reaches this point)."""
+        if self.tokens < 1:
+            raise InvalidInput("the cache is empty")
+        desc = self._desc(self.tokens)
+        st = _native.lib().pitch_enqueue_cache_decode(ctypes.byref(desc), stream_handle(stream, self.device))
+        _native.check(st)
+        return tuple(pl.out[:, :self.tokens] for pl in self.planes)
+
+    # ------------------------------------------------------------------ accounting
+    def stored_bytes(self, tokens: int | None = None) -> int:
+        """Bytes of packed codes plus side information for ``tokens`` tokens per segment."""
+        t = self.tokens if tokens is None else tokens
+        total = 0
+        for pl in self.planes:
+            total += t * pl.config.code_stride
+            total += pl.config.group_count(t) * pl.config.range_stride if pl.is_channel else t * 4
+        return total * self.segments
+
+    def decoded_bytes(self, tokens: int | None = None) -> int:
+        t = self.tokens if tokens is None else tokens
+        return len(self.planes) * self.segments * t * self.dim * self.planes[0].out.element_size()
+
+    def checksums(self) -> dict:
+        """Position-weighted 64-bit checksums of the stored codes and of the decoded outputs,
+        per plane (only the bytes of the ``tokens`` tokens currently held)."""
+        out = {}
+        for pl in self.planes:
+            c = pl.codes[:, :self.tokens * pl.config.code_stride].contiguous()
+            o = pl.out[:, :self.tokens].contiguous()
+            out[pl.name] = {"codes": self.pitch.checksum(c), "decoded": self.pitch.checksum(o)}
+        return out

@@ -1,0 +1,279 @@
+// Shared device helpers: element types, the rotation's sign diagonal, bit packing,
+// Walsh-Hadamard butterflies.  Compiled with -fmad=false: every float operation below is
+// one IEEE-754 rounding unless written as an explicit fused call.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace pitch {
+
+constexpr unsigned FULL = 0xFFFFFFFFu;
+constexpr float TWO_PI_F = 6.28318530717958647692f;
+
+// ------------------------------------------------------------------------------------------
+// Element types of the full-precision side
+// ------------------------------------------------------------------------------------------
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+    static __device__ __forceinline__ float to_f32(float v) { return v; }
+    static __device__ __forceinline__ float from_f32(float v) { return v; }
+};
+template <> struct Elem<__half> {
+    static __device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+    static __device__ __forceinline__ __half from_f32(float v) { return __float2half_rn(v); }
+};
+template <> struct Elem<__nv_bfloat16> {
+    static __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+    static __device__ __forceinline__ __nv_bfloat16 from_f32(float v) { return __float2bfloat16_rn(v); }
+};
+
+// Converts `N` floats to T and returns them packed in 32-bit words (N*sizeof(T)/4 words).
+template <typename T, int N> struct Packer;
+template <int N> struct Packer<float, N> {
+    static constexpr int WORDS = N;
+    static __device__ __forceinline__ void pack(const float* v, uint32_t* w) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) w[i] = __float_as_uint(v[i]);
+    }
+    static __device__ __forceinline__ void unpack(const uint32_t* w, float* v) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) v[i] = __uint_as_float(w[i]);
+    }
+};
+template <int N> struct Packer<__half, N> {
+    static constexpr int WORDS = N / 2;
+    static __device__ __forceinline__ void pack(const float* v, uint32_t* w) {
+#pragma unroll
+        for (int i = 0; i < N / 2; ++i) {
+            __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+    }
+    static __device__ __forceinline__ void unpack(const uint32_t* w, float* v) {
+#pragma unroll
+        for (int i = 0; i < N / 2; ++i) {
+            __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+            float2 f = __half22float2(h);
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    }
+};
+template <int N> struct Packer<__nv_bfloat16, N> {
+    static constexpr int WORDS = N / 2;
+    static __device__ __forceinline__ void pack(const float* v, uint32_t* w) {
+#pragma unroll
+        for (int i = 0; i < N / 2; ++i) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+    }
+    static __device__ __forceinline__ void unpack(const uint32_t* w, float* v) {
+#pragma unroll
+        for (int i = 0; i < N / 2; ++i) {
+            // bf16 -> f32 is a 16-bit shift
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+        }
+    }
+};
+
+// ------------------------------------------------------------------------------------------
+// Rotation diagonal.  PCG-style hash of (seed + i) mod 2^32; sign is +1 when the low bit is
+// set.  Follows reference/pitch_reference.py:11-19 and PITCHKernels.metal:26-37.
+// ------------------------------------------------------------------------------------------
+__host__ __device__ __forceinline__ uint32_t pcg_hash(uint32_t v) {
+    uint32_t state = v * 747796405u + 2891336453u;
+    uint32_t word = ((state >> ((state >> 28u) + 4u)) ^ state) * 277803737u;
+    return (word >> 22u) ^ word;
+}
+
+// Bit j of the result is 1 when coordinate (first + j) is NEGATED by the diagonal.
+__host__ __device__ __forceinline__ uint32_t negate_mask32(uint32_t seed, uint32_t first) {
+    uint32_t m = 0;
+#pragma unroll 4
+    for (uint32_t j = 0; j < 32; ++j) m |= ((pcg_hash(seed + first + j) & 1u) ^ 1u) << j;
+    return m;
+}
+
+__device__ __forceinline__ float flip_if(float v, uint32_t mask, int bit) {
+    return __uint_as_float(__float_as_uint(v) ^ (((mask >> bit) & 1u) << 31));
+}
+
+// ------------------------------------------------------------------------------------------
+// Bit stream of b-bit codes, LSB first in little-endian 32-bit words; code i of a vector
+// occupies bits [i*b, i*b+b).  reference/pitch_reference.py:65-90.
+// ------------------------------------------------------------------------------------------
+__host__ __device__ __forceinline__ int words_per_vector(int dim, int bits) { return (dim * bits + 31) >> 5; }
+
+// Code `i` (compile-time after unrolling) out of a register array of words.
+template <int BITS>
+__device__ __forceinline__ uint32_t extract_code(const uint32_t* w, int i) {
+    const int start = i * BITS, word = start >> 5, off = start & 31;
+    uint32_t v = w[word] >> off;
+    if (off + BITS > 32) v |= w[word + 1] << (32 - off);
+    return v & ((1u << BITS) - 1u);
+}
+
+template <int BITS>
+__device__ __forceinline__ void insert_code(uint32_t* w, int i, uint32_t code) {
+    const int start = i * BITS, word = start >> 5, off = start & 31;
+    w[word] |= code << off;
+    if (off + BITS > 32) w[word + 1] |= code >> (32 - off);
+}
+
+// Runtime-indexed variant reading from memory (global or shared).
+__device__ __forceinline__ uint32_t read_code(const uint32_t* buf, int i, int bits) {
+    const int start = i * bits, word = start >> 5, off = start & 31;
+    uint32_t v = buf[word] >> off;
+    if (off + bits > 32) v |= buf[word + 1] << (32 - off);
+    return v & ((1u << bits) - 1u);
+}
+
+// ------------------------------------------------------------------------------------------
+// Walsh-Hadamard butterflies on N register-resident values: stages h = 1, 2, 4 ... < limit,
+// (a, b) -> (a + b, a - b) on index bit h.  PITCHKernels.metal:46-55, pitch_reference.py:21-31.
+// ------------------------------------------------------------------------------------------
+template <int N>
+__device__ __forceinline__ void wht_regs(float (&x)[N], int limit) {
+#pragma unroll
+    for (int h = 1; h < N; h <<= 1) {
+        if (h < limit) {
+#pragma unroll
+            for (int i = 0; i < N; ++i) {
+                if (!(i & h)) {
+                    const float a = x[i], b = x[i | h];
+                    x[i] = a + b;
+                    x[i | h] = a - b;
+                }
+            }
+        }
+    }
+}
+
+// Stages across lanes: lane bit m corresponds to element bit m * N.
+template <int N>
+__device__ __forceinline__ void wht_lanes(float (&x)[N], int lanes_per_vector, int lane) {
+    for (int m = 1; m < lanes_per_vector; m <<= 1) {
+        const bool upper = (lane & m) != 0;
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+            const float o = __shfl_xor_sync(FULL, x[i], m);
+            x[i] = upper ? (o - x[i]) : (x[i] + o);
+        }
+    }
+}
+
+// Balanced pairwise sum over adjacent elements: level 1 adds t[2j] + t[2j+1], and so on.
+// Values beyond `limit` must be zero.  Independent of how a vector is split over lanes as
+// long as each lane owns a contiguous power-of-two block.
+template <int N>
+__device__ __forceinline__ float tree_sum_regs(float (&t)[N]) {
+#pragma unroll
+    for (int n = N; n > 1; n >>= 1) {
+#pragma unroll
+        for (int j = 0; j < n / 2; ++j) t[j] = t[2 * j] + t[2 * j + 1];
+    }
+    return t[0];
+}
+
+__device__ __forceinline__ float lanes_sum(float v, int lanes_per_vector) {
+    for (int m = 1; m < lanes_per_vector; m <<= 1) v = v + __shfl_xor_sync(FULL, v, m);
+    return v;
+}
+
+__device__ __forceinline__ float lanes_max(float v, int lanes_per_vector) {
+    for (int m = 1; m < lanes_per_vector; m <<= 1) v = fmaxf(v, __shfl_xor_sync(FULL, v, m));
+    return v;
+}
+
+// 128-bit global accesses.  Codes and side information are read once: bypass L1 allocation.
+__device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void stg_stream(uint4* p, const uint4& v) {
+    asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+
+// ------------------------------------------------------------------------------------------
+// Warp tile <-> registers.  The tile is 32 rows of E contiguous elements of T (32*E contiguous
+// elements of global memory); lane r ends up with (or starts from) row r in registers while
+// every global access is a contiguous 512-byte warp transaction.  Row r lives at r * PITCHB
+// bytes of a warp-private shared buffer; the 16-byte pad keeps both the row-owner accesses
+// and the transposed accesses free of bank conflicts.
+// ------------------------------------------------------------------------------------------
+template <typename T, int E> struct WarpStage {
+    static constexpr int ROWB = E * (int)sizeof(T);
+    static constexpr int PITCHB = ROWB + 16;
+    static constexpr int BYTES = 32 * PITCHB;
+    static constexpr int CPR = ROWB / 16;            // 16-byte chunks per row
+    static constexpr int EPC = 16 / (int)sizeof(T);  // elements per chunk
+    static constexpr int WORDS = ROWB / 4;
+
+    static __device__ __forceinline__ void load(const T* __restrict__ g, int valid_elems, bool vec_ok,
+                                                unsigned char* sm, int lane, float (&x)[E]) {
+        if (vec_ok) {
+#pragma unroll
+            for (int k = 0; k < CPR; ++k) {
+                const int c = k * 32 + lane;
+                uint4 q = make_uint4(0, 0, 0, 0);
+                if (c * EPC < valid_elems) q = ldg_stream(reinterpret_cast<const uint4*>(g) + c);
+                *reinterpret_cast<uint4*>(sm + (c / CPR) * PITCHB + (c % CPR) * 16) = q;
+            }
+        } else {
+#pragma unroll 4
+            for (int k = 0; k < E; ++k) {
+                const int e = k * 32 + lane;
+                T v = Elem<T>::from_f32(0.0f);
+                if (e < valid_elems) v = g[e];
+                *reinterpret_cast<T*>(sm + (e / E) * PITCHB + (e % E) * (int)sizeof(T)) = v;
+            }
+        }
+        __syncwarp();
+        uint32_t w[WORDS];
+#pragma unroll
+        for (int j = 0; j < CPR; ++j) {
+            const uint4 q = *reinterpret_cast<const uint4*>(sm + lane * PITCHB + j * 16);
+            w[4 * j] = q.x; w[4 * j + 1] = q.y; w[4 * j + 2] = q.z; w[4 * j + 3] = q.w;
+        }
+        Packer<T, E>::unpack(w, x);
+        __syncwarp();
+    }
+
+    static __device__ __forceinline__ void store(T* __restrict__ g, int valid_elems, bool vec_ok,
+                                                 unsigned char* sm, int lane, const float (&x)[E]) {
+        uint32_t w[WORDS];
+        Packer<T, E>::pack(x, w);
+#pragma unroll
+        for (int j = 0; j < CPR; ++j)
+            *reinterpret_cast<uint4*>(sm + lane * PITCHB + j * 16) =
+                make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+        __syncwarp();
+        if (vec_ok) {
+#pragma unroll
+            for (int k = 0; k < CPR; ++k) {
+                const int c = k * 32 + lane;
+                const uint4 q = *reinterpret_cast<const uint4*>(sm + (c / CPR) * PITCHB + (c % CPR) * 16);
+                if (c * EPC < valid_elems) stg_stream(reinterpret_cast<uint4*>(g) + c, q);
+            }
+        } else {
+#pragma unroll 4
+            for (int k = 0; k < E; ++k) {
+                const int e = k * 32 + lane;
+                const T v = *reinterpret_cast<const T*>(sm + (e / E) * PITCHB + (e % E) * (int)sizeof(T));
+                if (e < valid_elems) g[e] = v;
+            }
+        }
+        __syncwarp();
+    }
+};
+
+}  // namespace pitch

@@ -1,0 +1,678 @@
+// C ABI of the B200 KV-cache codec: argument validation, kernel selection and launch.
+// Declarations and the reference interfaces they replace: include/pitch_b200.h.
+//
+// Validation mirrors Codec.params / Codec.check (Sources/PITCH/Core/Codec.swift:28-47) and
+// ChannelCodec.params / check (Sources/PITCH/PerChannel.swift:308-329), QuantConfig.init
+// (Sources/PITCH/Models/QuantConfig.swift:24-35) and ChannelQuantConfig.init
+// (Sources/PITCH/PerChannel.swift:30-43).  Nothing here allocates device memory.
+#include "../../include/pitch_b200.h"
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include "cache_kernels.cuh"
+#include "channel_kernels.cuh"
+#include "common.cuh"
+#include "vector_kernels.cuh"
+
+using namespace pitch;
+
+namespace {
+
+thread_local std::string g_error;
+
+int fail(int status, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_error = buf;
+    return status;
+}
+
+// ---- host-side codebook table (TurboCodebooks.codebook(dim:bits:)) --------------------------
+struct BookTable {
+    std::mutex lock;
+    bool present[11][9] = {};
+    float values[11][9][256];
+} g_books;
+
+int log2_exact(int v) {
+    int l = 0;
+    while ((1 << l) < v) ++l;
+    return l;
+}
+
+bool valid_vector_dim(int dim) { return dim >= 2 && dim <= PITCH_MAX_DIM && (dim & (dim - 1)) == 0; }
+bool valid_bits(int bits) { return bits >= PITCH_MIN_BITS && bits <= PITCH_MAX_BITS; }
+
+template <int BITS>
+bool fetch_book(int dim, Codebook<BITS>& out) {
+    std::lock_guard<std::mutex> guard(g_books.lock);
+    const int l = log2_exact(dim);
+    if (!g_books.present[l][BITS]) return false;
+    memcpy(out.c, g_books.values[l][BITS], sizeof(float) << BITS);
+    return true;
+}
+
+// ---- buffer checks (Codec.check) ------------------------------------------------------------
+int check_buffer(const pitch_buffer& b, int64_t needs, const char* name) {
+    if (b.base == nullptr) return fail(PITCH_ERR_INVALID_INPUT, "%s buffer is null", name);
+    if (b.offset < 0 || (b.offset & 3) != 0)
+        return fail(PITCH_ERR_INVALID_INPUT, "%s offset %lld must be a non-negative multiple of 4", name,
+                    (long long)b.offset);
+    if (b.length < b.offset + needs)
+        return fail(PITCH_ERR_INVALID_INPUT, "%s buffer has %lld bytes after offset; needs %lld", name,
+                    (long long)(b.length - b.offset), (long long)needs);
+    return PITCH_OK;
+}
+
+// All buffers of a call must be device-accessible memory of one GPU ("belongs to a different
+// MTLDevice", Codec.swift:38-40).  Returns that GPU's ordinal in *device.
+int check_same_device(const pitch_buffer* bufs, const char* const* names, int n, int* device) {
+    int dev = -1;
+    for (int i = 0; i < n; ++i) {
+        cudaPointerAttributes attr;
+        cudaError_t e = cudaPointerGetAttributes(&attr, bufs[i].base);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            if (e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver)
+                return fail(PITCH_ERR_DEVICE_NOT_SUPPORTED, "no usable CUDA device: %s", cudaGetErrorString(e));
+            return fail(PITCH_ERR_INVALID_INPUT, "%s buffer: %s", names[i], cudaGetErrorString(e));
+        }
+        if (attr.type != cudaMemoryTypeDevice && attr.type != cudaMemoryTypeManaged)
+            return fail(PITCH_ERR_INVALID_INPUT, "%s buffer is not device memory", names[i]);
+        if (dev >= 0 && attr.type == cudaMemoryTypeDevice && attr.device != dev)
+            return fail(PITCH_ERR_INVALID_INPUT, "%s buffer belongs to a different GPU", names[i]);
+        if (attr.type == cudaMemoryTypeDevice) dev = attr.device;
+    }
+    if (dev < 0) cudaGetDevice(&dev);
+    *device = dev;
+    return PITCH_OK;
+}
+
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int dev) {
+        cudaGetDevice(&prev);
+        if (prev != dev) cudaSetDevice(dev); else prev = -1;
+    }
+    ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+};
+
+int launch_status(bool encode, const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) return PITCH_OK;
+    if (e == cudaErrorNoKernelImageForDevice || e == cudaErrorInvalidDeviceFunction)
+        return fail(PITCH_ERR_KERNEL_UNAVAILABLE, "%s: %s (library is built for sm_100a)", what, cudaGetErrorString(e));
+    return fail(encode ? PITCH_ERR_ENCODING_FAILED : PITCH_ERR_DECODING_FAILED, "%s: %s", what, cudaGetErrorString(e));
+}
+
+inline unsigned char* at(const pitch_buffer& b) { return static_cast<unsigned char*>(b.base) + b.offset; }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+inline float rsqrt_dim(int dim) { return (float)(1.0 / std::sqrt((double)dim)); }
+inline int elem_size(int dtype) { return dtype == PITCH_F32 ? 4 : 2; }
+
+int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+int check_vector_config(int method, int dim, int bits, int dtype) {
+    if (method != PITCH_TURBO_QUANT && method != PITCH_POLAR_QUANT)
+        return fail(PITCH_ERR_INVALID_INPUT, "unknown method %d", method);
+    if (!valid_vector_dim(dim))
+        return fail(PITCH_ERR_INVALID_DIMENSION, "Invalid dimension %d. Must be a power of two in [2, %d].", dim, PITCH_MAX_DIM);
+    if (!valid_bits(bits)) return fail(PITCH_ERR_INVALID_BIT_WIDTH, "Invalid bit width %d. Must be in 2...8.", bits);
+    if (dtype < PITCH_F32 || dtype > PITCH_BF16) return fail(PITCH_ERR_INVALID_INPUT, "unknown dtype %d", dtype);
+    return PITCH_OK;
+}
+
+int check_channel_config(int dim, int bits, int group_size, int dtype) {
+    if (dim < 1 || dim > PITCH_MAX_DIM)
+        return fail(PITCH_ERR_INVALID_INPUT, "per-channel dimension %d must be in 1...%d", dim, PITCH_MAX_DIM);
+    if (!valid_bits(bits)) return fail(PITCH_ERR_INVALID_BIT_WIDTH, "Invalid bit width %d. Must be in 2...8.", bits);
+    if (group_size < 1 || group_size > PITCH_MAX_GROUP)
+        return fail(PITCH_ERR_INVALID_INPUT, "group size %d must be in 1...%d", group_size, PITCH_MAX_GROUP);
+    if (dtype < PITCH_F32 || dtype > PITCH_BF16) return fail(PITCH_ERR_INVALID_INPUT, "unknown dtype %d", dtype);
+    return PITCH_OK;
+}
+
+// ---- dispatch helpers -------------------------------------------------------------------------
+#define PITCH_DISPATCH_BITS(bits, ...)                   \
+    switch (bits) {                                      \
+        case 2: { constexpr int BITS = 2; __VA_ARGS__; break; } \
+        case 3: { constexpr int BITS = 3; __VA_ARGS__; break; } \
+        case 4: { constexpr int BITS = 4; __VA_ARGS__; break; } \
+        case 5: { constexpr int BITS = 5; __VA_ARGS__; break; } \
+        case 6: { constexpr int BITS = 6; __VA_ARGS__; break; } \
+        case 7: { constexpr int BITS = 7; __VA_ARGS__; break; } \
+        default: { constexpr int BITS = 8; __VA_ARGS__; break; } \
+    }
+
+#define PITCH_DISPATCH_DTYPE(dtype, ...)                                  \
+    switch (dtype) {                                                      \
+        case PITCH_F32: { typedef float T; __VA_ARGS__; break; }          \
+        case PITCH_F16: { typedef __half T; __VA_ARGS__; break; }         \
+        default: { typedef __nv_bfloat16 T; __VA_ARGS__; break; }         \
+    }
+
+unsigned vec_grid(int64_t count, int dim) {
+    const int vpw = dim < 32 ? 32 : 1024 / dim;
+    return (unsigned)ceil_div(ceil_div(count, vpw), VEC_WARPS);
+}
+
+template <int BITS, typename T>
+int launch_turbo_encode(int dim, uint32_t seed, const void* in, void* codes, void* scales, int64_t count,
+                        cudaStream_t s) {
+    Codebook<BITS> book;
+    if (!fetch_book<BITS>(dim, book))
+        return fail(PITCH_ERR_INVALID_INPUT, "no TurboQuant codebook for dim %d, bits %d", dim, BITS);
+    turbo_encode_kernel<BITS, T><<<vec_grid(count, dim), VEC_THREADS, 0, s>>>(
+        static_cast<const T*>(in), static_cast<uint32_t*>(codes), static_cast<float*>(scales), count, dim, seed,
+        rsqrt_dim(dim), aligned16(in) ? 1 : 0, book);
+    return PITCH_OK;
+}
+
+template <int BITS, typename T>
+int launch_turbo_decode(int dim, uint32_t seed, const void* codes, const void* scales, void* out, int64_t count,
+                        cudaStream_t s) {
+    Codebook<BITS> book;
+    if (!fetch_book<BITS>(dim, book))
+        return fail(PITCH_ERR_INVALID_INPUT, "no TurboQuant codebook for dim %d, bits %d", dim, BITS);
+    if (BITS == 4 && dim == 64 && aligned16(codes) && aligned16(out)) {
+        Book16 b16;
+        memcpy(b16.c, book.c, sizeof b16.c);
+        turbo64_decode_kernel<T><<<(unsigned)ceil_div(count, C64_TILE), C64_THREADS, 0, s>>>(
+            static_cast<const uint4*>(codes), static_cast<const float*>(scales), static_cast<T*>(out), count,
+            negate_mask32(seed, 0), negate_mask32(seed, 32), b16);
+        return PITCH_OK;
+    }
+    turbo_decode_kernel<BITS, T><<<vec_grid(count, dim), VEC_THREADS, 0, s>>>(
+        static_cast<const uint32_t*>(codes), static_cast<const float*>(scales), static_cast<T*>(out), count, dim, seed,
+        rsqrt_dim(dim), aligned16(out) ? 1 : 0, book);
+    return PITCH_OK;
+}
+
+// slab mapping applies when dim/8 is a power of two in 1...32 and the buffers allow 16-byte access
+bool slab_ok(int dim, int bits) {
+    if (bits != 2 && bits != 4 && bits != 8) return false;
+    if (dim % 8 != 0) return false;
+    const int slabs = dim / 8;
+    return slabs <= 32 && (slabs & (slabs - 1)) == 0;
+}
+
+__global__ void pack_codes_kernel(const int32_t* __restrict__ codes, uint32_t* __restrict__ packed, int64_t count,
+                                  int dim, int bits, int wpv) {
+    const int64_t total = count * wpv;
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t v = e / wpv;
+        const int w = (int)(e - v * wpv);
+        const int bit0 = w * 32;
+        const int i0 = bit0 / bits;
+        int i1 = (bit0 + 31) / bits;
+        if (i1 > dim - 1) i1 = dim - 1;
+        uint32_t word = 0;
+        for (int i = i0; i <= i1; ++i) {
+            const uint32_t c = (uint32_t)codes[v * dim + i] & ((1u << bits) - 1u);
+            const int shift = i * bits - bit0;
+            word |= shift >= 0 ? (c << shift) : (c >> (-shift));
+        }
+        packed[e] = word;
+    }
+}
+
+__global__ void unpack_codes_kernel(const uint32_t* __restrict__ packed, int32_t* __restrict__ codes, int64_t count,
+                                    int dim, int bits, int wpv) {
+    const int64_t total = count * dim;
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t v = e / dim;
+        const int i = (int)(e - v * dim);
+        codes[e] = (int32_t)read_code(packed + v * wpv, i, bits);
+    }
+}
+
+__global__ void checksum_kernel(const uint32_t* __restrict__ words, int64_t n, unsigned long long* result) {
+    unsigned long long acc = 0;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        acc += ((unsigned long long)words[i] + 1ull) * (2ull * (unsigned long long)i + 1ull);
+    for (int m = 16; m > 0; m >>= 1) acc += __shfl_xor_sync(FULL, acc, m);
+    if ((threadIdx.x & 31) == 0 && acc != 0) atomicAdd(result, acc);
+}
+
+}  // namespace
+
+// =================================================================================================
+extern "C" {
+
+int pitch_abi_version(void) { return PITCH_ABI_VERSION; }
+
+const char* pitch_status_string(int status) {
+    switch (status) {
+        case PITCH_OK: return "ok";
+        case PITCH_ERR_INVALID_INPUT: return "invalid input";
+        case PITCH_ERR_INVALID_BIT_WIDTH: return "invalid bit width";
+        case PITCH_ERR_INVALID_DIMENSION: return "invalid dimension";
+        case PITCH_ERR_CONFIGURATION_MISMATCH: return "configuration mismatch";
+        case PITCH_ERR_KERNEL_UNAVAILABLE: return "no kernel image for this GPU";
+        case PITCH_ERR_ENCODING_FAILED: return "encoding failed";
+        case PITCH_ERR_DECODING_FAILED: return "decoding failed";
+        case PITCH_ERR_DEVICE_NOT_SUPPORTED: return "CUDA device not supported";
+        default: return "unknown status";
+    }
+}
+
+const char* pitch_last_error(void) { return g_error.c_str(); }
+
+int pitch_code_stride(int dim, int bits) { return words_per_vector(dim, bits) * 4; }
+
+int pitch_set_codebook(int dim, int bits, const float* centroids) {
+    if (!valid_vector_dim(dim))
+        return fail(PITCH_ERR_INVALID_DIMENSION, "Invalid dimension %d. Must be a power of two in [2, %d].", dim, PITCH_MAX_DIM);
+    if (!valid_bits(bits)) return fail(PITCH_ERR_INVALID_BIT_WIDTH, "Invalid bit width %d. Must be in 2...8.", bits);
+    if (centroids == nullptr) return fail(PITCH_ERR_INVALID_INPUT, "centroids is null");
+    const int n = 1 << bits;
+    for (int i = 0; i < n; ++i) {
+        if (!std::isfinite(centroids[i])) return fail(PITCH_ERR_INVALID_INPUT, "centroid %d is not finite", i);
+        if (i > 0 && !(centroids[i] > centroids[i - 1]))
+            return fail(PITCH_ERR_INVALID_INPUT, "centroids must be strictly ascending (index %d)", i);
+    }
+    std::lock_guard<std::mutex> guard(g_books.lock);
+    const int l = log2_exact(dim);
+    memcpy(g_books.values[l][bits], centroids, sizeof(float) * n);
+    g_books.present[l][bits] = true;
+    return PITCH_OK;
+}
+
+int pitch_has_codebook(int dim, int bits) {
+    if (!valid_vector_dim(dim) || !valid_bits(bits)) return 0;
+    std::lock_guard<std::mutex> guard(g_books.lock);
+    return g_books.present[log2_exact(dim)][bits] ? 1 : 0;
+}
+
+// ---------------------------------------------------------------------------------- per-vector
+int pitch_enqueue_encode(int method, int dim, int bits, uint32_t seed, int dtype, pitch_buffer input,
+                         pitch_buffer codes, pitch_buffer scales, int64_t count, void* stream) {
+    int st = check_vector_config(method, dim, bits, dtype);
+    if (st) return st;
+    if (count < 1) return fail(PITCH_ERR_INVALID_INPUT, "count must be at least 1");
+    const int64_t stride = pitch_code_stride(dim, bits);
+    if ((st = check_buffer(input, count * dim * elem_size(dtype), "input"))) return st;
+    if ((st = check_buffer(codes, count * stride, "codes"))) return st;
+    if ((st = check_buffer(scales, count * 4, "scales"))) return st;
+    const pitch_buffer bufs[3] = {input, codes, scales};
+    const char* const names[3] = {"input", "codes", "scales"};
+    int dev;
+    if ((st = check_same_device(bufs, names, 3, &dev))) return st;
+    DeviceGuard guard(dev);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const float rs = rsqrt_dim(dim);
+    if (method == PITCH_TURBO_QUANT) {
+        PITCH_DISPATCH_BITS(bits, PITCH_DISPATCH_DTYPE(dtype, st = (launch_turbo_encode<BITS, T>(
+                                                                  dim, seed, at(input), at(codes), at(scales), count, s))));
+        if (st) return st;
+    } else {
+        PITCH_DISPATCH_BITS(bits, PITCH_DISPATCH_DTYPE(dtype, (polar_encode_kernel<BITS, T><<<vec_grid(count, dim), VEC_THREADS, 0, s>>>(
+                                                                  reinterpret_cast<const T*>(at(input)),
+                                                                  reinterpret_cast<uint32_t*>(at(codes)),
+                                                                  reinterpret_cast<float*>(at(scales)), count, dim, seed, rs,
+                                                                  aligned16(at(input)) ? 1 : 0))));
+    }
+    return launch_status(true, method == PITCH_TURBO_QUANT ? "turbo_encode" : "polar_encode");
+}
+
+int pitch_enqueue_decode(int method, int dim, int bits, uint32_t seed, int dtype, pitch_buffer codes,
+                         pitch_buffer scales, pitch_buffer output, int64_t count, void* stream) {
+    int st = check_vector_config(method, dim, bits, dtype);
+    if (st) return st;
+    if (count < 1) return fail(PITCH_ERR_INVALID_INPUT, "count must be at least 1");
+    const int64_t stride = pitch_code_stride(dim, bits);
+    if ((st = check_buffer(codes, count * stride, "codes"))) return st;
+    if ((st = check_buffer(scales, count * 4, "scales"))) return st;
+    if ((st = check_buffer(output, count * dim * elem_size(dtype), "output"))) return st;
+    const pitch_buffer bufs[3] = {codes, scales, output};
+    const char* const names[3] = {"codes", "scales", "output"};
+    int dev;
+    if ((st = check_same_device(bufs, names, 3, &dev))) return st;
+    DeviceGuard guard(dev);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const float rs = rsqrt_dim(dim);
+    if (method == PITCH_TURBO_QUANT) {
+        PITCH_DISPATCH_BITS(bits, PITCH_DISPATCH_DTYPE(dtype, st = (launch_turbo_decode<BITS, T>(
+                                                                  dim, seed, at(codes), at(scales), at(output), count, s))));
+        if (st) return st;
+    } else {
+        PITCH_DISPATCH_BITS(bits, PITCH_DISPATCH_DTYPE(dtype, (polar_decode_kernel<BITS, T><<<vec_grid(count, dim), VEC_THREADS, 0, s>>>(
+                                                                  reinterpret_cast<const uint32_t*>(at(codes)),
+                                                                  reinterpret_cast<const float*>(at(scales)),
+                                                                  reinterpret_cast<T*>(at(output)), count, dim, seed, rs,
+                                                                  aligned16(at(output)) ? 1 : 0))));
+    }
+    return launch_status(false, method == PITCH_TURBO_QUANT ? "turbo_decode" : "polar_decode");
+}
+
+// --------------------------------------------------------------------------------- per-channel
+int pitch_enqueue_channel_encode(int dim, int bits, int group_size, int dtype, pitch_buffer input,
+                                 pitch_buffer codes, pitch_buffer ranges, int64_t count, void* stream) {
+    int st = check_channel_config(dim, bits, group_size, dtype);
+    if (st) return st;
+    if (count < 1) return fail(PITCH_ERR_INVALID_INPUT, "count must be at least 1");
+    const int64_t stride = pitch_code_stride(dim, bits);
+    const int64_t groups = ceil_div(count, group_size);
+    if ((st = check_buffer(input, count * dim * elem_size(dtype), "input"))) return st;
+    if ((st = check_buffer(codes, count * stride, "codes"))) return st;
+    if ((st = check_buffer(ranges, groups * 4 * dim, "ranges"))) return st;
+    const pitch_buffer bufs[3] = {input, codes, ranges};
+    const char* const names[3] = {"input", "codes", "ranges"};
+    int dev;
+    if ((st = check_same_device(bufs, names, 3, &dev))) return st;
+    DeviceGuard guard(dev);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool slab = slab_ok(dim, bits) && aligned16(at(input)) && aligned16(at(ranges)) &&
+                      (reinterpret_cast<uintptr_t>(at(codes)) % (bits == 8 ? 8 : 4)) == 0;
+    if (slab) {
+        const int l2 = log2_exact(dim / 8);
+        const unsigned grid = (unsigned)ceil_div(groups, CH_WARPS);
+#define PITCH_SLAB_ENC(B)                                                                                      \
+    PITCH_DISPATCH_DTYPE(dtype, (channel_encode_slab_kernel<B, T><<<grid, CH_THREADS, 0, s>>>(                 \
+                                    reinterpret_cast<const T*>(at(input)), at(codes),                          \
+                                    reinterpret_cast<__half*>(at(ranges)), count, dim, l2, group_size, groups)))
+        if (bits == 2) { PITCH_SLAB_ENC(2); } else if (bits == 4) { PITCH_SLAB_ENC(4); } else { PITCH_SLAB_ENC(8); }
+#undef PITCH_SLAB_ENC
+    } else {
+        PITCH_DISPATCH_DTYPE(dtype, (channel_encode_general_kernel<T><<<(unsigned)groups, 256, 0, s>>>(
+                                        reinterpret_cast<const T*>(at(input)), reinterpret_cast<uint32_t*>(at(codes)),
+                                        reinterpret_cast<__half*>(at(ranges)), count, dim, bits, group_size)));
+    }
+    return launch_status(true, "channel_encode");
+}
+
+int pitch_enqueue_channel_decode(int dim, int bits, int group_size, int dtype, pitch_buffer codes,
+                                 pitch_buffer ranges, pitch_buffer output, int64_t count, void* stream) {
+    int st = check_channel_config(dim, bits, group_size, dtype);
+    if (st) return st;
+    if (count < 1) return fail(PITCH_ERR_INVALID_INPUT, "count must be at least 1");
+    const int64_t stride = pitch_code_stride(dim, bits);
+    const int64_t groups = ceil_div(count, group_size);
+    if ((st = check_buffer(codes, count * stride, "codes"))) return st;
+    if ((st = check_buffer(ranges, groups * 4 * dim, "ranges"))) return st;
+    if ((st = check_buffer(output, count * dim * elem_size(dtype), "output"))) return st;
+    const pitch_buffer bufs[3] = {codes, ranges, output};
+    const char* const names[3] = {"codes", "ranges", "output"};
+    int dev;
+    if ((st = check_same_device(bufs, names, 3, &dev))) return st;
+    DeviceGuard guard(dev);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool slab = slab_ok(dim, bits) && aligned16(at(output)) && aligned16(at(ranges)) &&
+                      (reinterpret_cast<uintptr_t>(at(codes)) % (bits == 8 ? 8 : 4)) == 0;
+    if (slab) {
+        const int l2 = log2_exact(dim / 8);
+        const int chunks = (int)ceil_div(group_size, CH_CHUNK);
+        const int64_t tiles = groups * chunks;
+        const unsigned grid = (unsigned)ceil_div(tiles, CH_WARPS);
+#define PITCH_SLAB_DEC(B)                                                                                      \
+    PITCH_DISPATCH_DTYPE(dtype, (channel_decode_slab_kernel<B, T><<<grid, CH_THREADS, 0, s>>>(                 \
+                                    at(codes), reinterpret_cast<const __half*>(at(ranges)),                    \
+                                    reinterpret_cast<T*>(at(output)), count, dim, l2, group_size, chunks, tiles)))
+        if (bits == 2) { PITCH_SLAB_DEC(2); } else if (bits == 4) { PITCH_SLAB_DEC(4); } else { PITCH_SLAB_DEC(8); }
+#undef PITCH_SLAB_DEC
+    } else {
+        const int64_t total = count * dim;
+        int64_t blocks = ceil_div(total, 256);
+        if (blocks > 148 * 64) blocks = 148 * 64;
+        PITCH_DISPATCH_DTYPE(dtype, (channel_decode_general_kernel<T><<<(unsigned)blocks, 256, 0, s>>>(
+                                        reinterpret_cast<const uint32_t*>(at(codes)),
+                                        reinterpret_cast<const __half*>(at(ranges)), reinterpret_cast<T*>(at(output)),
+                                        count, dim, bits, group_size)));
+    }
+    return launch_status(false, "channel_decode");
+}
+
+// ------------------------------------------------------------------------------------ rotation
+int pitch_enqueue_rotate(int mode, int dim, uint32_t seed, pitch_buffer input, pitch_buffer output, int64_t count,
+                         void* stream) {
+    if (mode < 0 || mode > 2) return fail(PITCH_ERR_INVALID_INPUT, "unknown rotation mode %d", mode);
+    if (!valid_vector_dim(dim))
+        return fail(PITCH_ERR_INVALID_DIMENSION, "Invalid dimension %d. Must be a power of two in [2, %d].", dim, PITCH_MAX_DIM);
+    if (count < 1) return fail(PITCH_ERR_INVALID_INPUT, "count must be at least 1");
+    int st;
+    if ((st = check_buffer(input, count * dim * 4, "input"))) return st;
+    if ((st = check_buffer(output, count * dim * 4, "output"))) return st;
+    const pitch_buffer bufs[2] = {input, output};
+    const char* const names[2] = {"input", "output"};
+    int dev;
+    if ((st = check_same_device(bufs, names, 2, &dev))) return st;
+    DeviceGuard guard(dev);
+    rotate_kernel<<<vec_grid(count, dim), VEC_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const float*>(at(input)), reinterpret_cast<float*>(at(output)), count, dim, seed,
+        rsqrt_dim(dim), mode, aligned16(at(input)) ? 1 : 0, aligned16(at(output)) ? 1 : 0);
+    return launch_status(true, "rotate");
+}
+
+// ----------------------------------------------------------------------------- pack / unpack
+static int pack_common(bool pack, int dim, int bits, pitch_buffer codes_i32, pitch_buffer packed, int64_t count,
+                       void* stream) {
+    if (dim < 1 || dim > PITCH_MAX_DIM) return fail(PITCH_ERR_INVALID_INPUT, "dimension %d must be in 1...%d", dim, PITCH_MAX_DIM);
+    if (!valid_bits(bits)) return fail(PITCH_ERR_INVALID_BIT_WIDTH, "Invalid bit width %d. Must be in 2...8.", bits);
+    if (count < 1) return fail(PITCH_ERR_INVALID_INPUT, "count must be at least 1");
+    int st;
+    const int wpv = words_per_vector(dim, bits);
+    if ((st = check_buffer(codes_i32, count * dim * 4, "codes_i32"))) return st;
+    if ((st = check_buffer(packed, count * wpv * 4, "packed"))) return st;
+    const pitch_buffer bufs[2] = {codes_i32, packed};
+    const char* const names[2] = {"codes_i32", "packed"};
+    int dev;
+    if ((st = check_same_device(bufs, names, 2, &dev))) return st;
+    DeviceGuard guard(dev);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int64_t blocks = ceil_div(count * (pack ? wpv : dim), 256);
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (pack)
+        pack_codes_kernel<<<(unsigned)blocks, 256, 0, s>>>(reinterpret_cast<const int32_t*>(at(codes_i32)),
+                                                           reinterpret_cast<uint32_t*>(at(packed)), count, dim, bits, wpv);
+    else
+        unpack_codes_kernel<<<(unsigned)blocks, 256, 0, s>>>(reinterpret_cast<const uint32_t*>(at(packed)),
+                                                             reinterpret_cast<int32_t*>(at(codes_i32)), count, dim, bits, wpv);
+    return launch_status(pack, pack ? "pack_codes" : "unpack_codes");
+}
+
+int pitch_enqueue_pack_codes(int dim, int bits, pitch_buffer codes_i32, pitch_buffer packed, int64_t count, void* stream) {
+    return pack_common(true, dim, bits, codes_i32, packed, count, stream);
+}
+int pitch_enqueue_unpack_codes(int dim, int bits, pitch_buffer packed, pitch_buffer codes_i32, int64_t count, void* stream) {
+    return pack_common(false, dim, bits, codes_i32, packed, count, stream);
+}
+
+// ------------------------------------------------------------------------------- whole cache
+static int64_t plane_side_bytes(const pitch_plane& pl, int dim, int64_t tokens) {
+    if (pl.kind == PITCH_PLANE_CHANNEL) return ceil_div(tokens, pl.group_size) * 4 * dim;
+    return tokens * 4;
+}
+
+int pitch_enqueue_cache_decode(const pitch_cache_desc* d, void* stream) {
+    if (d == nullptr) return fail(PITCH_ERR_INVALID_INPUT, "descriptor is null");
+    if (d->n_planes < 1 || d->n_planes > 4) return fail(PITCH_ERR_INVALID_INPUT, "n_planes %d must be in 1...4", d->n_planes);
+    if (d->segments < 1 || d->tokens < 1) return fail(PITCH_ERR_INVALID_INPUT, "segments and tokens must be at least 1");
+    if (d->out_dtype < PITCH_F32 || d->out_dtype > PITCH_BF16) return fail(PITCH_ERR_INVALID_INPUT, "unknown dtype %d", d->out_dtype);
+    const int dim = d->dim;
+    bool fused = dim == 64;
+    for (int i = 0; i < d->n_planes; ++i) {
+        const pitch_plane& pl = d->planes[i];
+        int st;
+        if (pl.kind == PITCH_PLANE_CHANNEL) {
+            if ((st = check_channel_config(dim, pl.bits, pl.group_size, d->out_dtype))) return st;
+        } else if (pl.kind == PITCH_PLANE_TURBO || pl.kind == PITCH_PLANE_POLAR) {
+            if ((st = check_vector_config(pl.kind, dim, pl.bits, d->out_dtype))) return st;
+        } else {
+            return fail(PITCH_ERR_INVALID_INPUT, "plane %d: unknown kind %d", i, pl.kind);
+        }
+        if (!pl.codes || !pl.side || !pl.out) return fail(PITCH_ERR_INVALID_INPUT, "plane %d: null pointer", i);
+        if (!aligned16(pl.codes) || !aligned16(pl.side) || !aligned16(pl.out) || (pl.codes_seg_stride & 15) ||
+            (pl.side_seg_stride & 15) || (pl.out_seg_stride & 15))
+            return fail(PITCH_ERR_INVALID_INPUT, "plane %d: pointers and segment strides must be multiples of 16", i);
+        const int64_t stride = pitch_code_stride(dim, pl.bits);
+        if (d->segments > 1 && (pl.codes_seg_stride < d->tokens * stride ||
+                                pl.side_seg_stride < plane_side_bytes(pl, dim, d->tokens) ||
+                                pl.out_seg_stride < d->tokens * dim * elem_size(d->out_dtype)))
+            return fail(PITCH_ERR_INVALID_INPUT, "plane %d: a segment stride is smaller than one segment", i);
+        if (pl.bits != 4) fused = false;
+        if (pl.kind == PITCH_PLANE_POLAR) fused = false;
+        if (pl.kind == PITCH_PLANE_CHANNEL && pl.group_size % 32 != 0) fused = false;
+    }
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, d->planes[0].out) != cudaSuccess ||
+        (attr.type != cudaMemoryTypeDevice && attr.type != cudaMemoryTypeManaged)) {
+        cudaGetLastError();
+        return fail(PITCH_ERR_INVALID_INPUT, "plane 0: output is not device memory");
+    }
+    int dev = attr.device;
+    DeviceGuard guard(dev);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+    if (fused) {
+        Cache64Params p;
+        memset(&p, 0, sizeof p);
+        p.n_planes = d->n_planes;
+        p.tiles_per_seg = (int)ceil_div(d->tokens, C64_TILE);
+        p.tokens = d->tokens;
+        bool need_book = false;
+        for (int i = 0; i < d->n_planes; ++i) {
+            const pitch_plane& pl = d->planes[i];
+            Plane64& q = p.plane[i];
+            q.kind = pl.kind == PITCH_PLANE_CHANNEL ? 1 : 0;
+            q.group_size = pl.group_size;
+            q.neg_lo = negate_mask32(pl.seed, 0);
+            q.neg_hi = negate_mask32(pl.seed, 32);
+            q.codes = static_cast<const unsigned char*>(pl.codes);
+            q.codes_seg_stride = pl.codes_seg_stride;
+            q.side = static_cast<const unsigned char*>(pl.side);
+            q.side_seg_stride = pl.side_seg_stride;
+            q.out = static_cast<unsigned char*>(pl.out);
+            q.out_seg_stride = pl.out_seg_stride;
+            need_book |= q.kind == 0;
+        }
+        if (need_book) {
+            Codebook<4> book;
+            if (!fetch_book<4>(64, book)) return fail(PITCH_ERR_INVALID_INPUT, "no TurboQuant codebook for dim 64, bits 4");
+            memcpy(p.book.c, book.c, sizeof p.book.c);
+        }
+        const int64_t grid = d->segments * p.tiles_per_seg * p.n_planes;
+        if (grid > 0x7FFFFFFFLL) return fail(PITCH_ERR_INVALID_INPUT, "cache too large for one launch");
+        PITCH_DISPATCH_DTYPE(d->out_dtype, (cache_decode_d64b4_kernel<T><<<(unsigned)grid, C64_THREADS, 0, s>>>(p)));
+        return launch_status(false, "cache_decode");
+    }
+
+    // Any other shape: one stand-alone decode per (plane, segment), same results.
+    for (int i = 0; i < d->n_planes; ++i) {
+        const pitch_plane& pl = d->planes[i];
+        const int64_t stride = pitch_code_stride(dim, pl.bits);
+        for (int64_t sgm = 0; sgm < d->segments; ++sgm) {
+            pitch_buffer codes = {pl.codes, sgm * pl.codes_seg_stride + d->tokens * stride, sgm * pl.codes_seg_stride};
+            pitch_buffer side = {pl.side, sgm * pl.side_seg_stride + plane_side_bytes(pl, dim, d->tokens), sgm * pl.side_seg_stride};
+            pitch_buffer out = {pl.out, sgm * pl.out_seg_stride + d->tokens * dim * elem_size(d->out_dtype), sgm * pl.out_seg_stride};
+            int st;
+            if (pl.kind == PITCH_PLANE_CHANNEL)
+                st = pitch_enqueue_channel_decode(dim, pl.bits, pl.group_size, d->out_dtype, codes, side, out, d->tokens, stream);
+            else
+                st = pitch_enqueue_decode(pl.kind, dim, pl.bits, pl.seed, d->out_dtype, codes, side, out, d->tokens, stream);
+            if (st) return st;
+        }
+    }
+    return PITCH_OK;
+}
+
+int pitch_enqueue_cache_append(const pitch_cache_desc* d, const pitch_append_src* src, int in_dtype, int64_t n_new,
+                               void* stream) {
+    if (d == nullptr || src == nullptr) return fail(PITCH_ERR_INVALID_INPUT, "descriptor is null");
+    if (d->n_planes < 1 || d->n_planes > 4) return fail(PITCH_ERR_INVALID_INPUT, "n_planes %d must be in 1...4", d->n_planes);
+    if (d->segments < 1 || d->segments > 65535) return fail(PITCH_ERR_INVALID_INPUT, "segments must be in 1...65535");
+    if (d->tokens < 0) return fail(PITCH_ERR_INVALID_INPUT, "tokens must not be negative");
+    if (n_new < 1 || n_new > 65535) return fail(PITCH_ERR_INVALID_INPUT, "n_new must be in 1...65535");
+    if (in_dtype < PITCH_F32 || in_dtype > PITCH_BF16) return fail(PITCH_ERR_INVALID_INPUT, "unknown dtype %d", in_dtype);
+    const int dim = d->dim;
+    for (int i = 0; i < d->n_planes; ++i) {
+        const pitch_plane& pl = d->planes[i];
+        int st;
+        if (pl.kind == PITCH_PLANE_CHANNEL) {
+            if ((st = check_channel_config(dim, pl.bits, pl.group_size, in_dtype))) return st;
+            if (src[i].residual == nullptr) return fail(PITCH_ERR_INVALID_INPUT, "plane %d: residual buffer is null", i);
+            if (src[i].residual_seg_stride < (int64_t)pl.group_size * dim * 4 || (src[i].residual_seg_stride & 3))
+                return fail(PITCH_ERR_INVALID_INPUT, "plane %d: residual segment stride too small", i);
+            if (d->tokens % pl.group_size + n_new > pl.group_size)
+                return fail(PITCH_ERR_INVALID_INPUT, "plane %d: new tokens must fall into one group of %d", i, pl.group_size);
+        } else if (pl.kind == PITCH_PLANE_TURBO || pl.kind == PITCH_PLANE_POLAR) {
+            if ((st = check_vector_config(pl.kind, dim, pl.bits, in_dtype))) return st;
+        } else {
+            return fail(PITCH_ERR_INVALID_INPUT, "plane %d: unknown kind %d", i, pl.kind);
+        }
+        if (!pl.codes || !pl.side || !src[i].input) return fail(PITCH_ERR_INVALID_INPUT, "plane %d: null pointer", i);
+        if ((reinterpret_cast<uintptr_t>(pl.codes) & 3) || (reinterpret_cast<uintptr_t>(pl.side) & 3) ||
+            (reinterpret_cast<uintptr_t>(src[i].input) & 3) || (pl.codes_seg_stride & 3) || (pl.side_seg_stride & 3) ||
+            (src[i].input_seg_stride & 3))
+            return fail(PITCH_ERR_INVALID_INPUT, "plane %d: pointers and strides must be multiples of 4", i);
+    }
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, d->planes[0].codes) != cudaSuccess ||
+        (attr.type != cudaMemoryTypeDevice && attr.type != cudaMemoryTypeManaged)) {
+        cudaGetLastError();
+        return fail(PITCH_ERR_INVALID_INPUT, "plane 0: codes is not device memory");
+    }
+    DeviceGuard guard(attr.device);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    for (int i = 0; i < d->n_planes; ++i) {
+        const pitch_plane& pl = d->planes[i];
+        const unsigned char* in = static_cast<const unsigned char*>(src[i].input);
+        if (pl.kind == PITCH_PLANE_CHANNEL) {
+            PITCH_DISPATCH_DTYPE(in_dtype, (cache_append_channel_kernel<T><<<(unsigned)d->segments, 256, 0, s>>>(
+                                               in, src[i].input_seg_stride, static_cast<float*>(src[i].residual),
+                                               src[i].residual_seg_stride / 4, static_cast<unsigned char*>(pl.codes),
+                                               pl.codes_seg_stride, static_cast<unsigned char*>(pl.side),
+                                               pl.side_seg_stride, d->tokens, (int)n_new, dim, pl.bits, pl.group_size)));
+        } else {
+            Book256 book;
+            memset(&book, 0, sizeof book);
+            if (pl.kind == PITCH_PLANE_TURBO) {
+                std::lock_guard<std::mutex> guardb(g_books.lock);
+                const int l = log2_exact(dim);
+                if (!g_books.present[l][pl.bits])
+                    return fail(PITCH_ERR_INVALID_INPUT, "no TurboQuant codebook for dim %d, bits %d", dim, pl.bits);
+                memcpy(book.c, g_books.values[l][pl.bits], sizeof(float) << pl.bits);
+            }
+            const dim3 grid((unsigned)n_new, (unsigned)d->segments);
+            const unsigned threads = dim < 32 ? 32 : dim;
+            PITCH_DISPATCH_DTYPE(in_dtype, (cache_append_vector_kernel<T><<<grid, threads, 0, s>>>(
+                                               in, src[i].input_seg_stride, static_cast<unsigned char*>(pl.codes),
+                                               pl.codes_seg_stride, static_cast<unsigned char*>(pl.side),
+                                               pl.side_seg_stride, d->tokens, dim, pl.bits,
+                                               pl.kind == PITCH_PLANE_TURBO ? 0 : 1, pl.seed, rsqrt_dim(dim), book)));
+        }
+        const int st = launch_status(true, "cache_append");
+        if (st) return st;
+    }
+    return PITCH_OK;
+}
+
+// --------------------------------------------------------------------------------- checksum
+int pitch_enqueue_checksum(pitch_buffer buf, int64_t bytes, uint64_t* result_device, void* stream) {
+    if (bytes < 0 || (bytes & 3)) return fail(PITCH_ERR_INVALID_INPUT, "bytes %lld must be a non-negative multiple of 4", (long long)bytes);
+    if (result_device == nullptr) return fail(PITCH_ERR_INVALID_INPUT, "result pointer is null");
+    int st;
+    if ((st = check_buffer(buf, bytes, "buffer"))) return st;
+    const pitch_buffer bufs[1] = {buf};
+    const char* const names[1] = {"buffer"};
+    int dev;
+    if ((st = check_same_device(bufs, names, 1, &dev))) return st;
+    if (bytes == 0) return PITCH_OK;
+    DeviceGuard guard(dev);
+    const int64_t n = bytes / 4;
+    int64_t blocks = ceil_div(n, 256 * 8);
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks < 1) blocks = 1;
+    checksum_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const uint32_t*>(at(buf)), n, reinterpret_cast<unsigned long long*>(result_device));
+    return launch_status(false, "checksum");
+}
+
+}  // extern "C"

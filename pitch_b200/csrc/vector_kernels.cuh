@@ -1,0 +1,343 @@
+// Per-vector codecs (TurboQuant, PolarQuant variant), general path: every power-of-two
+// dim 2...1024, every bit width 2...8, fp32 / fp16 / bf16 on the full-precision side.
+//
+// Mapping.  A warp owns a tile of 32 x E contiguous coordinates, E = min(dim, 32); each lane
+// keeps its E contiguous coordinates in registers.  dim >= 32: dim/32 adjacent lanes share a
+// vector (1024/dim vectors per warp tile), the low five Walsh-Hadamard stages run in registers
+// and the remaining log2(dim/32) stages as lane-xor shuffles.  dim < 32: one vector per lane.
+// Because 32 codes of b bits are exactly b words, every lane's slice of the packed stream is
+// word aligned for any b, including the widths whose codes straddle words.
+//
+// Global traffic is staged through a warp-private, padded shared-memory tile so that every
+// global access of the full-precision tensor is a contiguous 512-byte warp transaction
+// while each lane still ends up with its own contiguous row.
+#pragma once
+
+#include "common.cuh"
+
+namespace pitch {
+
+constexpr int VEC_WARPS = 4;               // warps per CTA
+constexpr int VEC_THREADS = VEC_WARPS * 32;
+
+template <int BITS> struct Codebook { float c[1 << BITS]; };
+
+// Geometry of a warp tile for a given dim.
+struct TileGeom {
+    int e;        // coordinates per lane
+    int tpv;      // lanes per vector
+    int vpw;      // vectors per warp tile
+    int wpv;      // packed words per vector
+    __device__ __forceinline__ TileGeom(int dim, int bits) {
+        e = dim < 32 ? dim : 32;
+        tpv = dim < 32 ? 1 : dim >> 5;
+        vpw = 32 / tpv;
+        wpv = words_per_vector(dim, bits);
+    }
+};
+
+template <typename T>
+__device__ __forceinline__ void load_lane_coords(const T* __restrict__ in, int64_t v0, int64_t count, int dim,
+                                                 const TileGeom& g, bool vec_ok, unsigned char* stage,
+                                                 int lane, bool valid, int64_t v, float (&x)[32]) {
+    if (dim >= 32) {
+        const int64_t left = count - v0;
+        const int valid_elems = (int)(left < g.vpw ? left : g.vpw) * dim;
+        WarpStage<T, 32>::load(in + v0 * dim, valid_elems, vec_ok, stage, lane, x);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) x[i] = (i < dim && valid) ? Elem<T>::to_f32(in[v * dim + i]) : 0.0f;
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ void store_lane_coords(T* __restrict__ out, int64_t v0, int64_t count, int dim,
+                                                  const TileGeom& g, bool vec_ok, unsigned char* stage,
+                                                  int lane, bool valid, int64_t v, const float (&x)[32]) {
+    if (dim >= 32) {
+        const int64_t left = count - v0;
+        const int valid_elems = (int)(left < g.vpw ? left : g.vpw) * dim;
+        WarpStage<T, 32>::store(out + v0 * dim, valid_elems, vec_ok, stage, lane, x);
+    } else if (valid) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (i < dim) out[v * dim + i] = Elem<T>::from_f32(x[i]);
+    }
+}
+
+template <int BITS>
+__device__ __forceinline__ void load_lane_words(const uint32_t* __restrict__ codes, int64_t v, int sub, int dim,
+                                                const TileGeom& g, bool valid, uint32_t (&w)[BITS]) {
+#pragma unroll
+    for (int k = 0; k < BITS; ++k) {
+        w[k] = 0;
+        if (valid && (dim >= 32 || k < g.wpv)) w[k] = __ldg(codes + v * g.wpv + sub * BITS + k);
+    }
+}
+
+template <int BITS>
+__device__ __forceinline__ void store_lane_words(uint32_t* __restrict__ codes, int64_t v, int sub, int dim,
+                                                 const TileGeom& g, bool valid, const uint32_t (&w)[BITS]) {
+#pragma unroll
+    for (int k = 0; k < BITS; ++k)
+        if (valid && (dim >= 32 || k < g.wpv)) codes[v * g.wpv + sub * BITS + k] = w[k];
+}
+
+__device__ __forceinline__ void init_negate_masks(uint32_t* s_neg, uint32_t seed, int dim, int tid, int nthreads) {
+    const int nw = dim < 32 ? 1 : dim >> 5;
+    for (int k = tid; k < nw; k += nthreads) s_neg[k] = negate_mask32(seed, 32u * (uint32_t)k);
+}
+
+// ------------------------------------------------------------------------------------------
+// TurboQuant encode: norm, unit vector, sign flip, WHT, 1/sqrt(d), codebook search, pack.
+// Follows reference/pitch_reference.py:92-102 in float32 (PITCHKernels.metal:114-152).
+// A code is the number of decision boundaries strictly below the rotated coordinate.
+// ------------------------------------------------------------------------------------------
+template <int BITS, typename T>
+__global__ void __launch_bounds__(VEC_THREADS)
+turbo_encode_kernel(const T* __restrict__ in, uint32_t* __restrict__ codes, float* __restrict__ norms,
+                    int64_t count, int dim, uint32_t seed, float rs, int vec_ok, const Codebook<BITS> book) {
+    __shared__ float s_edges[1 << BITS];
+    __shared__ uint32_t s_neg[32];
+    __shared__ __align__(16) unsigned char s_stage[VEC_WARPS][WarpStage<T, 32>::BYTES];
+    for (int k = threadIdx.x; k < (1 << BITS) - 1; k += VEC_THREADS) s_edges[k] = 0.5f * (book.c[k] + book.c[k + 1]);
+    init_negate_masks(s_neg, seed, dim, threadIdx.x, VEC_THREADS);
+    __syncthreads();
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const TileGeom g(dim, BITS);
+    const int64_t v0 = ((int64_t)blockIdx.x * VEC_WARPS + warp) * g.vpw;
+    if (v0 >= count) return;
+    const int sub = lane & (g.tpv - 1);
+    const int64_t v = v0 + lane / g.tpv;
+    const bool valid = v < count;
+
+    float x[32];
+    load_lane_coords<T>(in, v0, count, dim, g, vec_ok != 0, s_stage[warp], lane, valid, v, x);
+
+    float t[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) t[i] = x[i] * x[i];
+    const float norm = sqrtf(lanes_sum(tree_sum_regs(t), g.tpv));
+    const float inv = norm > 0.0f ? 1.0f / norm : 0.0f;
+    const uint32_t neg = s_neg[sub];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) x[i] = flip_if(x[i], neg, i) * inv;
+    wht_regs(x, g.e);
+    wht_lanes(x, g.tpv, lane);
+
+    uint32_t w[BITS];
+#pragma unroll
+    for (int k = 0; k < BITS; ++k) w[k] = 0;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        if (i < g.e) {
+            const float u = x[i] * rs;
+            uint32_t code = 0;
+#pragma unroll
+            for (int step = (1 << BITS) >> 1; step > 0; step >>= 1) {
+                const uint32_t cand = code + step;
+                if (u > s_edges[cand - 1]) code = cand;
+            }
+            insert_code<BITS>(w, i, code);
+        }
+    }
+    store_lane_words<BITS>(codes, v, sub, dim, g, valid, w);
+    if (valid && sub == 0) norms[v] = norm;
+}
+
+// ------------------------------------------------------------------------------------------
+// TurboQuant decode: centroid lookup, WHT, sign, 1/sqrt(d), norm.
+// reference/pitch_reference.py:104-107, PITCHKernels.metal:154-174.
+// ------------------------------------------------------------------------------------------
+template <int BITS, typename T>
+__global__ void __launch_bounds__(VEC_THREADS)
+turbo_decode_kernel(const uint32_t* __restrict__ codes, const float* __restrict__ norms, T* __restrict__ out,
+                    int64_t count, int dim, uint32_t seed, float rs, int vec_ok, const Codebook<BITS> book) {
+    __shared__ float s_book[1 << BITS];
+    __shared__ uint32_t s_neg[32];
+    __shared__ __align__(16) unsigned char s_stage[VEC_WARPS][WarpStage<T, 32>::BYTES];
+    for (int k = threadIdx.x; k < (1 << BITS); k += VEC_THREADS) s_book[k] = book.c[k];
+    init_negate_masks(s_neg, seed, dim, threadIdx.x, VEC_THREADS);
+    __syncthreads();
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const TileGeom g(dim, BITS);
+    const int64_t v0 = ((int64_t)blockIdx.x * VEC_WARPS + warp) * g.vpw;
+    if (v0 >= count) return;
+    const int sub = lane & (g.tpv - 1);
+    const int64_t v = v0 + lane / g.tpv;
+    const bool valid = v < count;
+
+    uint32_t w[BITS];
+    load_lane_words<BITS>(codes, v, sub, dim, g, valid, w);
+    const float norm = valid ? __ldg(norms + v) : 0.0f;
+
+    float x[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) x[i] = (i < g.e) ? s_book[extract_code<BITS>(w, i)] : 0.0f;
+    wht_regs(x, g.e);
+    wht_lanes(x, g.tpv, lane);
+    const uint32_t neg = s_neg[sub];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) x[i] = flip_if(x[i], neg, i) * rs * norm;
+    store_lane_coords<T>(out, v0, count, dim, g, vec_ok != 0, s_stage[warp], lane, valid, v, x);
+}
+
+// ------------------------------------------------------------------------------------------
+// PolarQuant variant encode: sign flip, WHT, 1/sqrt(d); pairs (y[2p], y[2p+1]) -> (r, theta);
+// radius code on 2^b - 1 steps of [0, rmax], angle code on 2^b circular bins.
+// reference/pitch_reference.py:109-121, PITCHKernels.metal:178-222.
+// ------------------------------------------------------------------------------------------
+template <int BITS, typename T>
+__global__ void __launch_bounds__(VEC_THREADS)
+polar_encode_kernel(const T* __restrict__ in, uint32_t* __restrict__ codes, float* __restrict__ scales,
+                    int64_t count, int dim, uint32_t seed, float rs, int vec_ok) {
+    __shared__ uint32_t s_neg[32];
+    __shared__ __align__(16) unsigned char s_stage[VEC_WARPS][WarpStage<T, 32>::BYTES];
+    init_negate_masks(s_neg, seed, dim, threadIdx.x, VEC_THREADS);
+    __syncthreads();
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const TileGeom g(dim, BITS);
+    const int64_t v0 = ((int64_t)blockIdx.x * VEC_WARPS + warp) * g.vpw;
+    if (v0 >= count) return;
+    const int sub = lane & (g.tpv - 1);
+    const int64_t v = v0 + lane / g.tpv;
+    const bool valid = v < count;
+
+    float x[32];
+    load_lane_coords<T>(in, v0, count, dim, g, vec_ok != 0, s_stage[warp], lane, valid, v, x);
+    const uint32_t neg = s_neg[sub];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) x[i] = flip_if(x[i], neg, i);
+    wht_regs(x, g.e);
+    wht_lanes(x, g.tpv, lane);
+
+    float r[16];
+    float rmax = 0.0f;
+#pragma unroll
+    for (int p = 0; p < 16; ++p) {
+        x[2 * p] = x[2 * p] * rs;
+        x[2 * p + 1] = x[2 * p + 1] * rs;
+        const float aa = x[2 * p] * x[2 * p], cc = x[2 * p + 1] * x[2 * p + 1];
+        r[p] = sqrtf(aa + cc);
+        if (2 * p < g.e) rmax = fmaxf(rmax, r[p]);
+    }
+    rmax = lanes_max(rmax, g.tpv);
+    const float safe = rmax > 0.0f ? rmax : 1.0f;
+    constexpr float RL = (float)((1 << BITS) - 1);
+    constexpr float NB = (float)(1 << BITS);
+
+    uint32_t w[BITS];
+#pragma unroll
+    for (int k = 0; k < BITS; ++k) w[k] = 0;
+#pragma unroll
+    for (int p = 0; p < 16; ++p) {
+        if (2 * p < g.e) {
+            float q = floorf(r[p] / safe * RL + 0.5f);
+            q = fminf(fmaxf(q, 0.0f), RL);
+            insert_code<BITS>(w, 2 * p, (uint32_t)q);
+            float theta = atan2f(x[2 * p + 1], x[2 * p]);
+            if (theta < 0.0f) theta += TWO_PI_F;
+            const uint32_t tq = (uint32_t)floorf(theta / TWO_PI_F * NB + 0.5f) & ((1u << BITS) - 1u);
+            insert_code<BITS>(w, 2 * p + 1, tq);
+        }
+    }
+    store_lane_words<BITS>(codes, v, sub, dim, g, valid, w);
+    if (valid && sub == 0) scales[v] = rmax;
+}
+
+// ------------------------------------------------------------------------------------------
+// PolarQuant variant decode.  reference/pitch_reference.py:123-129, PITCHKernels.metal:224-246.
+// The 2^b angles are tabulated once per CTA.
+// ------------------------------------------------------------------------------------------
+template <int BITS, typename T>
+__global__ void __launch_bounds__(VEC_THREADS)
+polar_decode_kernel(const uint32_t* __restrict__ codes, const float* __restrict__ scales, T* __restrict__ out,
+                    int64_t count, int dim, uint32_t seed, float rs, int vec_ok) {
+    __shared__ float s_cos[1 << BITS], s_sin[1 << BITS];
+    __shared__ uint32_t s_neg[32];
+    __shared__ __align__(16) unsigned char s_stage[VEC_WARPS][WarpStage<T, 32>::BYTES];
+    for (int k = threadIdx.x; k < (1 << BITS); k += VEC_THREADS) {
+        const float theta = (float)k / (float)(1 << BITS) * TWO_PI_F;
+        s_cos[k] = cosf(theta);
+        s_sin[k] = sinf(theta);
+    }
+    init_negate_masks(s_neg, seed, dim, threadIdx.x, VEC_THREADS);
+    __syncthreads();
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const TileGeom g(dim, BITS);
+    const int64_t v0 = ((int64_t)blockIdx.x * VEC_WARPS + warp) * g.vpw;
+    if (v0 >= count) return;
+    const int sub = lane & (g.tpv - 1);
+    const int64_t v = v0 + lane / g.tpv;
+    const bool valid = v < count;
+
+    uint32_t w[BITS];
+    load_lane_words<BITS>(codes, v, sub, dim, g, valid, w);
+    const float scale = valid ? __ldg(scales + v) : 0.0f;
+    constexpr float RL = (float)((1 << BITS) - 1);
+
+    float x[32];
+#pragma unroll
+    for (int p = 0; p < 16; ++p) {
+        if (2 * p < g.e) {
+            const float r = (float)extract_code<BITS>(w, 2 * p) / RL * scale;
+            const uint32_t tq = extract_code<BITS>(w, 2 * p + 1);
+            x[2 * p] = r * s_cos[tq];
+            x[2 * p + 1] = r * s_sin[tq];
+        } else {
+            x[2 * p] = 0.0f;
+            x[2 * p + 1] = 0.0f;
+        }
+    }
+    wht_regs(x, g.e);
+    wht_lanes(x, g.tpv, lane);
+    const uint32_t neg = s_neg[sub];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) x[i] = flip_if(x[i], neg, i) * rs;
+    store_lane_coords<T>(out, v0, count, dim, g, vec_ok != 0, s_stage[warp], lane, valid, v, x);
+}
+
+// ------------------------------------------------------------------------------------------
+// The rotation on its own (float32 in, float32 out).  mode 0: unnormalised WHT; mode 1:
+// rotate = WHT(x * signs) / sqrt(d); mode 2: unrotate = WHT(y) * signs / sqrt(d).
+// reference/pitch_reference.py:21-34.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(VEC_THREADS)
+rotate_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t count, int dim, uint32_t seed,
+              float rs, int mode, int vec_in_ok, int vec_out_ok) {
+    __shared__ uint32_t s_neg[32];
+    __shared__ __align__(16) unsigned char s_stage[VEC_WARPS][WarpStage<float, 32>::BYTES];
+    init_negate_masks(s_neg, seed, dim, threadIdx.x, VEC_THREADS);
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const TileGeom g(dim, 8);
+    const int64_t v0 = ((int64_t)blockIdx.x * VEC_WARPS + warp) * g.vpw;
+    if (v0 >= count) return;
+    const int sub = lane & (g.tpv - 1);
+    const int64_t v = v0 + lane / g.tpv;
+    const bool valid = v < count;
+    float x[32];
+    load_lane_coords<float>(in, v0, count, dim, g, vec_in_ok != 0, s_stage[warp], lane, valid, v, x);
+    const uint32_t neg = s_neg[sub];
+    if (mode == 1) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) x[i] = flip_if(x[i], neg, i);
+    }
+    wht_regs(x, g.e);
+    wht_lanes(x, g.tpv, lane);
+    if (mode == 2) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) x[i] = flip_if(x[i], neg, i);
+    }
+    if (mode != 0) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) x[i] = x[i] * rs;
+    }
+    store_lane_coords<float>(out, v0, count, dim, g, vec_out_ok != 0, s_stage[warp], lane, valid, v, x);
+}
+
+}  // namespace pitch

@@ -1,0 +1,194 @@
+"""Parity at the benchmark configurations' shapes and size-independent properties at full size.
+
+Synthetic inputs stand in for real KV data: seeded NumPy generators with the distributions the
+configurations name (Gaussian vectors scaled by lognormal norms; biased keys with outlier
+channels).  The float32 C oracle is the bit-exact checker; the float64 NumPy specification
+gives the count of boundary ties.
+"""
+import numpy as np
+import pytest
+
+from conftest import max_rel_l2, mean_rel_err
+from oracle import kernel_f32, spec_np
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def q():
+    from pitch_b200 import PITCH
+    return PITCH()
+
+
+def lognormal_vectors(rng, n, d):
+    return (rng.standard_normal((n, d)) * rng.lognormal(0.0, 0.5, size=(n, 1))).astype(np.float32)
+
+
+def biased_keys(rng, n, d):
+    X = rng.standard_normal((n, d)) + rng.normal(0.0, 2.0, size=(1, d))
+    X[:, rng.choice(d, size=4, replace=False)] *= 20.0
+    return X.astype(np.float32)
+
+
+def unpack(buf, n, d, b):
+    return spec_np.unpack_codes(bytes(buf), n, d, b)
+
+
+def test_config1_turbo_round_trip_d64_b4(q):
+    """Config 1 at full size: 65,536 vectors, d=64, b=4."""
+    from pitch_b200 import QuantConfig
+    rng = np.random.default_rng(1)
+    n, d, b = 65536, 64, 4
+    X = lognormal_vectors(rng, n, d)
+    cfg = QuantConfig("turboQuant", d, b)
+    batch = q.encode(X, config=cfg)
+    o_codes, o_norms = kernel_f32.encode("turboQuant", X, b)
+    assert batch.codes == o_codes.tobytes()                      # bit-exact vs float32 oracle
+    assert batch.scales.tobytes() == o_norms.tobytes()
+    s_codes, s_norms = spec_np.turbo_encode(X.astype(np.float64), b)
+    ties = int((unpack(batch.codes, n, d, b) != s_codes).sum())
+    print(f"\nconfig 1: {ties} boundary ties of {n * d} codes vs the float64 specification")
+    assert ties <= 16                                            # a few per million (expected ~1)
+    assert np.all(np.abs(batch.scales - s_norms) <= 1e-5 * np.maximum(1, s_norms))
+    rec = q.decode(batch).reshape(n, d)
+    spec_rec = spec_np.turbo_decode(unpack(batch.codes, n, d, b), batch.scales.astype(np.float64), b)
+    assert max_rel_l2(rec, spec_rec) < 1e-5
+    assert 0.0085 < mean_rel_err(X, rec) < 0.0098                # 0.00905 published for Gaussian d=64 b=4
+
+
+def test_config2_per_channel_keys(q):
+    """Config 2 at full size: T=32,768, d=64, G=64, b=4; everything bit-exact."""
+    from pitch_b200 import ChannelQuantConfig
+    rng = np.random.default_rng(2)
+    n, d, b, G = 32768, 64, 4, 64
+    X = biased_keys(rng, n, d)
+    block = q.encode_per_channel(X, config=ChannelQuantConfig(d, b, G))
+    codes, ranges = spec_np.channel_encode(X, b, G)
+    assert block.ranges.tobytes() == ranges.view(np.uint16).tobytes()
+    assert block.codes == spec_np.pack_codes(codes, b)
+    rec = q.decode_per_channel(block).reshape(n, d)
+    assert rec.tobytes() == spec_np.channel_decode(codes, ranges, b, G).tobytes()
+
+
+@pytest.mark.parametrize("bits", [3, 4])
+def test_config3_polar_d128(q, bits):
+    """Config 3 shape (d=128, b in {3,4}) on 65,536 vectors."""
+    from pitch_b200 import QuantConfig
+    rng = np.random.default_rng(3)
+    n, d = 65536, 128
+    X = lognormal_vectors(rng, n, d)
+    cfg = QuantConfig("polarQuant", d, bits)
+    batch = q.encode(X, config=cfg)
+    o_codes, o_scales = kernel_f32.encode("polarQuant", X, bits)
+    assert batch.scales.tobytes() == o_scales.tobytes()
+    ours = unpack(batch.codes, n, d, bits)
+    vs_f32 = int((ours != unpack(o_codes, n, d, bits)).sum())
+    s_codes, s_scales = spec_np.polar_encode(X.astype(np.float64), bits)
+    ties = int((ours != s_codes).sum())
+    print(f"\nconfig 3 b={bits}: {ties} ties vs float64 spec, {vs_f32} vs float32 oracle, of {n * d} codes")
+    assert ties <= 64 and vs_f32 <= 16
+    assert np.all(np.abs(batch.scales - s_scales) <= 1e-5 * np.maximum(1, s_scales))
+    rec = q.decode(batch).reshape(n, d)
+    assert max_rel_l2(rec, spec_np.polar_decode(ours, batch.scales.astype(np.float64), bits)) < 1e-5
+
+
+@pytest.mark.parametrize("method", ["turboQuant", "polarQuant"])
+@pytest.mark.parametrize("d", [64, 128, 256, 512, 1024])
+def test_config3_dimension_sweep_b4(q, method, d):
+    """Dimension sweep at b=4 (register, shuffle and multi-lane Walsh-Hadamard paths)."""
+    from pitch_b200 import QuantConfig
+    rng = np.random.default_rng(30 + d)
+    n = (1 << 20) // d
+    X = lognormal_vectors(rng, n, d)
+    batch = q.encode(X, config=QuantConfig(method, d, 4))
+    o_codes, o_scales = kernel_f32.encode(method, X, 4)
+    assert batch.scales.tobytes() == o_scales.tobytes()
+    diff = int((unpack(batch.codes, n, d, 4) != unpack(o_codes, n, d, 4)).sum())
+    assert diff == 0 if method == "turboQuant" else diff <= 4
+    rec = q.decode(batch).reshape(n, d)
+    assert max_rel_l2(rec, kernel_f32.decode(method, np.frombuffer(batch.codes, np.uint8), batch.scales, d, 4)) < 2e-6
+    dec = spec_np.DECODERS[method](unpack(batch.codes, n, d, 4), batch.scales.astype(np.float64), 4)
+    assert max_rel_l2(rec, dec) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+def test_half_precision_io(q, dtype):
+    """fp16 / bf16 on the full-precision side: encode sees exactly the half values widened to
+    float32; decode equals the float32 result rounded to nearest even."""
+    import torch
+    from pitch_b200 import ChannelQuantConfig, QuantConfig
+    tdt = getattr(torch, dtype)
+    rng = np.random.default_rng(7)
+    n, d = 4096, 64
+    X = torch.from_numpy(lognormal_vectors(rng, n, d)).to(tdt)
+    Xf = X.float().numpy()
+    dev = q.device
+    for cfg in (QuantConfig("turboQuant", d, 4), QuantConfig("polarQuant", d, 3), QuantConfig("turboQuant", 256, 5)):
+        dd = cfg.dim
+        xin = X.reshape(-1, dd).to(dev)
+        m = xin.shape[0]
+        codes = torch.empty(m * cfg.code_stride, dtype=torch.uint8, device=dev)
+        scales = torch.empty(m, dtype=torch.float32, device=dev)
+        q.enqueue_encode(xin, codes, scales, m, cfg)
+        ref = q.encode(Xf.reshape(-1, dd), config=cfg)                    # float32 path on the same values
+        assert codes.cpu().numpy().tobytes() == ref.codes
+        assert scales.cpu().numpy().tobytes() == ref.scales.tobytes()
+        out16 = torch.empty((m, dd), dtype=tdt, device=dev)
+        out32 = torch.empty((m, dd), dtype=torch.float32, device=dev)
+        q.enqueue_decode(codes, scales, out16, m, cfg)
+        q.enqueue_decode(codes, scales, out32, m, cfg)
+        assert torch.equal(out16, out32.to(tdt))
+    ccfg = ChannelQuantConfig(d, 4, 64)
+    K = torch.from_numpy(biased_keys(rng, n, d)).to(tdt).to(dev)
+    codes = torch.empty(n * ccfg.code_stride, dtype=torch.uint8, device=dev)
+    ranges = torch.empty(ccfg.group_count(n) * 2 * d, dtype=torch.float16, device=dev)
+    q.enqueue_per_channel_encode(K, codes, ranges, n, ccfg)
+    ref = q.encode_per_channel(K.float().cpu().numpy(), config=ccfg)
+    assert codes.cpu().numpy().tobytes() == ref.codes
+    assert ranges.cpu().numpy().view(np.uint16).tobytes() == ref.ranges.tobytes()
+    out16 = torch.empty((n, d), dtype=tdt, device=dev)
+    out32 = torch.empty((n, d), dtype=torch.float32, device=dev)
+    q.enqueue_per_channel_decode(codes, ranges, out16, n, ccfg)
+    q.enqueue_per_channel_decode(codes, ranges, out32, n, ccfg)
+    assert torch.equal(out16, out32.to(tdt))
+
+
+def test_unaligned_offsets_take_the_scalar_path(q):
+    """Offsets are only 4-byte aligned by contract; results must not depend on alignment."""
+    import torch
+    from pitch_b200 import ChannelQuantConfig, QuantConfig
+    rng = np.random.default_rng(11)
+    dev = q.device
+    for cfg in (QuantConfig("turboQuant", 64, 4), QuantConfig("polarQuant", 128, 3), QuantConfig("turboQuant", 1024, 8)):
+        n, d = 70, cfg.dim
+        X = lognormal_vectors(rng, n, d)
+        ref = q.encode(X, config=cfg)
+        ref_out = q.decode(ref)
+        for off in (4, 8, 12):
+            xin = torch.zeros(n * d + 8, dtype=torch.float32, device=dev)
+            xin[off // 4: off // 4 + n * d] = torch.from_numpy(X.reshape(-1)).to(dev)
+            codes = torch.zeros(n * cfg.code_stride + 16, dtype=torch.uint8, device=dev)
+            scales = torch.zeros(n + 4, dtype=torch.float32, device=dev)
+            q.enqueue_encode(xin, codes, scales, n, cfg, input_offset=off, codes_offset=off, scales_offset=off)
+            assert codes[off: off + n * cfg.code_stride].cpu().numpy().tobytes() == ref.codes
+            out = torch.full((n * d + 8,), -7.0, dtype=torch.float32, device=dev)
+            q.enqueue_decode(codes, scales, out, n, cfg, codes_offset=off, scales_offset=off, output_offset=off)
+            o = out.cpu().numpy()
+            assert np.array_equal(o[off // 4: off // 4 + n * d], ref_out)
+            assert np.all(o[: off // 4] == -7.0) and np.all(o[off // 4 + n * d:] == -7.0)
+    ccfg = ChannelQuantConfig(64, 4, 64)
+    n = 150
+    K = biased_keys(rng, n, 64)
+    ref = q.encode_per_channel(K, config=ccfg)
+    ref_out = q.decode_per_channel(ref)
+    xin = torch.zeros(n * 64 + 8, dtype=torch.float32, device=dev)
+    xin[1: 1 + n * 64] = torch.from_numpy(K.reshape(-1)).to(dev)
+    codes = torch.zeros(n * 32 + 16, dtype=torch.uint8, device=dev)
+    ranges = torch.zeros(3 * 128 + 8, dtype=torch.float16, device=dev)
+    q.enqueue_per_channel_encode(xin, codes, ranges, n, ccfg, input_offset=4, codes_offset=4, ranges_offset=4)
+    assert codes[4: 4 + n * 32].cpu().numpy().tobytes() == ref.codes
+    assert ranges[2: 2 + 384].cpu().numpy().view(np.uint16).tobytes() == ref.ranges.tobytes()
+    out = torch.full((n * 64 + 8,), -7.0, dtype=torch.float32, device=dev)
+    q.enqueue_per_channel_decode(codes, ranges, out, n, ccfg, codes_offset=4, ranges_offset=4, output_offset=4)
+    o = out.cpu().numpy()
+    assert np.array_equal(o[1: 1 + n * 64], ref_out) and o[0] == -7.0 and np.all(o[1 + n * 64:] == -7.0)

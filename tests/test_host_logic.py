@@ -1,0 +1,212 @@
+"""CPU-only tests: the C ABI library loads and exports every declared symbol, host-side value
+types and containers behave like the reference's, sharding and the checksum gather work on two
+gloo ranks.  No compute entry point is called here (there is no GPU and no CPU fallback)."""
+import ctypes
+import re
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from pitch_b200 import build as native_build
+    native_build.build()
+    from pitch_b200 import _native
+    return _native.lib()
+
+
+def test_library_exports_every_declared_symbol(lib):
+    from pitch_b200 import _native
+    header = (ROOT / "include" / "pitch_b200.h").read_text()
+    declared = set(re.findall(r"^\s*(?:int|const char\*)\s+(pitch_\w+)\s*\(", header, flags=re.M))
+    assert declared, "no declarations found in the header"
+    assert declared == set(_native.PROTOTYPES), declared ^ set(_native.PROTOTYPES)
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert lib.pitch_abi_version() == 1
+    assert lib.pitch_status_string(3) == b"invalid dimension"
+
+
+def test_stride_and_codebook_table(lib):
+    from pitch_b200 import codebooks, code_stride_bytes
+    for d, b, want in ((64, 3, 24), (64, 4, 32), (128, 3, 48), (1024, 4, 512), (2, 3, 4), (96, 3, 36), (1, 2, 4)):
+        assert lib.pitch_code_stride(d, b) == want == code_stride_bytes(d, b)      # BatchAPITests.swift:160-175
+    codebooks.register_all()
+    assert lib.pitch_has_codebook(64, 4) == 1 and lib.pitch_has_codebook(100, 4) == 0
+    c = codebooks.turbo_codebook(64, 4)
+    assert c.dtype == np.float64 and c.shape == (16,) and np.array_equal(c, -c[::-1]) and np.all(np.diff(c) > 0)
+    bad = (ctypes.c_float * 4)(0.0, 1.0, 0.5, 2.0)
+    assert lib.pitch_set_codebook(64, 2, bad) == 1                                 # not ascending -> invalid input
+    assert b"ascending" in lib.pitch_last_error()
+    assert lib.pitch_set_codebook(100, 2, bad) == 3 and lib.pitch_set_codebook(64, 9, bad) == 2
+
+
+def test_validation_happens_before_any_device_work(lib):
+    """Argument errors are reported with the reference's status codes even without a GPU."""
+    from pitch_b200 import _native
+    B = _native.Buffer
+    ok = B(0x1000, 1 << 20, 0)
+    f = lib.pitch_enqueue_encode
+    assert f(0, 100, 4, 0, 0, ok, ok, ok, 1, None) == 3            # invalidDimension
+    assert f(0, 64, 9, 0, 0, ok, ok, ok, 1, None) == 2             # invalidBitWidth
+    assert f(0, 64, 4, 0, 0, ok, ok, ok, 0, None) == 1             # count must be at least 1
+    assert f(0, 64, 4, 0, 0, ok, B(0x1000, 1 << 20, 2), ok, 1, None) == 1   # offset not a multiple of 4
+    assert b"multiple of 4" in lib.pitch_last_error()
+    assert f(0, 64, 4, 0, 0, ok, B(0x1000, 64, 0), ok, 4, None) == 1        # codes buffer too small
+    assert b"needs 128" in lib.pitch_last_error()
+    assert f(0, 64, 4, 0, 0, B(None, 0, 0), ok, ok, 1, None) == 1
+    g = lib.pitch_enqueue_channel_decode
+    assert g(0, 4, 64, 0, ok, ok, ok, 1, None) == 1 and g(2048, 4, 64, 0, ok, ok, ok, 1, None) == 1
+    assert g(64, 1, 64, 0, ok, ok, ok, 1, None) == 2 and g(64, 4, 0, 0, ok, ok, ok, 1, None) == 1
+
+
+def test_missing_library_fails_loudly(tmp_path, monkeypatch):
+    from pitch_b200 import KernelUnavailable, _native
+    monkeypatch.setattr(_native, "_lib", None)
+    monkeypatch.setattr(_native, "LIB_PATH", tmp_path / "nope.so")
+    with pytest.raises(KernelUnavailable):
+        _native.lib()
+
+
+def test_product_never_imports_the_oracle():
+    for path in (ROOT / "pitch_b200").rglob("*.py"):
+        text = path.read_text()
+        assert not re.search(r"^\s*(from|import)\s+oracle\b", text, flags=re.M), path
+    for path in (ROOT / "pitch_b200" / "csrc").glob("*"):
+        assert "oracle" not in path.read_text(), path
+
+
+# ---------------------------------------------------------------- configs (QuantConfig / ChannelQuantConfig)
+def test_quant_config_validation_and_accounting():
+    from pitch_b200 import InvalidBitWidth, InvalidDimension, QuantConfig, QuantMethod
+    for dim in (0, 1, 3, 100, 2048):
+        with pytest.raises(InvalidDimension):
+            QuantConfig("turboQuant", dim, 4)
+    for bits in (0, 1, 9, 16):
+        with pytest.raises(InvalidBitWidth):
+            QuantConfig("polarQuant", 64, bits)
+    t = QuantConfig(QuantMethod.turboQuant, 64, 3)
+    assert (t.code_stride, t.bytes_per_vector, t.bits_per_coordinate) == (24, 28, 3.5)
+    p = QuantConfig("polarQuant", 1024, 4)
+    assert p.bytes_per_vector == 516 and abs(p.compression_ratio - 4096 / 516) < 1e-12
+    kv = QuantConfig("turboQuant", np.int64(64), 4)
+    assert abs(kv.compression_ratio_vs_float16 - 16 / 4.5) < 1e-12 and kv.seed == 0x50495443
+    assert QuantConfig.from_json(kv.to_json()) == kv
+
+
+def test_channel_config_validation_and_accounting():
+    from pitch_b200 import ChannelQuantConfig, PITCHError
+    for args in ((0, 4), (2048, 4), (64, 1), (64, 4, 0), (64, 4, 70000)):
+        with pytest.raises(PITCHError):
+            ChannelQuantConfig(*args)
+    c = ChannelQuantConfig(64, 4)
+    assert c.bits_per_coordinate == 4.5 and ChannelQuantConfig(128, 4).bits_per_coordinate == 4.5
+    assert ChannelQuantConfig(128, 4, 128).bits_per_coordinate == 4.25
+    assert c.group_count(150) == 3 and c.range_stride == 256 and ChannelQuantConfig(96, 3).code_stride == 36
+
+
+# ---------------------------------------------------------------- containers
+def test_compressed_batch_rules():
+    from pitch_b200 import CompressedBatch, PITCHError, QuantConfig
+    cfg = QuantConfig("turboQuant", 64, 4)
+    for codes, scales in ((bytes(28), [1]), (bytes(32), [1, 2]), (bytes(32), [float("nan")]), (b"", []), (bytes(32), [-1])):
+        with pytest.raises(PITCHError):
+            CompressedBatch(cfg, codes, scales)
+    a = CompressedBatch(cfg, bytes(range(64)), [1.0, 2.0])
+    b = a.vectors(1, 2)
+    assert b.count == 1 and b.codes == bytes(range(32, 64)) and b.scales[0] == 2.0
+    c = a.vectors(0, 1)
+    c.append(b)
+    assert c == a
+    with pytest.raises(PITCHError):
+        a.vectors(1, 1)
+    with pytest.raises(PITCHError):
+        a.append(CompressedBatch(QuantConfig("turboQuant", 64, 3), bytes(24), [1.0]))
+    assert CompressedBatch.from_json(a.to_json()) == a
+    import json
+    obj = json.loads(a.to_json())
+    assert set(obj) == {"formatVersion", "config", "codes", "scales"} and obj["formatVersion"] == 3
+    assert obj["config"] == {"method": "turboQuant", "dim": 64, "bits": 4, "seed": 0x50495443}
+    obj["formatVersion"] = 4
+    with pytest.raises(PITCHError):
+        CompressedBatch.from_json(json.dumps(obj))
+    with pytest.raises(PITCHError):
+        CompressedBatch.from_json('{"formatVersion":3,"config":{"method":"turboQuant","dim":100,"bits":4,"seed":1},"codes":"","scales":[1]}')
+    assert a.stored_byte_count == 64 + 8 + 16 and a.original_byte_count == 512
+
+
+def test_channel_block_rules():
+    from pitch_b200 import ChannelCompressedBlock, ChannelQuantConfig, PITCHError, half_to_float
+    cfg = ChannelQuantConfig(4, 4)
+    with pytest.raises(PITCHError):
+        ChannelCompressedBlock(cfg, bytes(4), [0, 0])                                  # ranges too short
+    with pytest.raises(PITCHError):
+        ChannelCompressedBlock(cfg, bytes(4), [0x4000, 0, 0, 0, 0x3C00, 0, 0, 0])      # min 2.0 above max 1.0
+    blk = ChannelCompressedBlock(cfg, bytes(4), [0x3C00, 0, 0, 0, 0x4000, 0, 0, 0])
+    assert blk.range(0, 0) == (1.0, 2.0) and blk.count == 1 and blk.group_count == 1
+    assert ChannelCompressedBlock.from_json(blk.to_json()) == blk
+    with pytest.raises(PITCHError):
+        blk.append(blk)                                                                  # partial group
+    for h, want in ((0x3C00, 1.0), (0xC000, -2.0), (0x7BFF, 65504.0), (0x0001, 2.0 ** -24)):
+        assert half_to_float(h) == want
+    assert half_to_float(0x7C00) == float("inf") and np.isnan(half_to_float(0x7E00))
+
+
+# ---------------------------------------------------------------- sharding + gloo gather
+def test_shard_segments_cover_without_overlap():
+    from pitch_b200.shard import shard_segments
+    for world in (1, 2, 4, 8):
+        shards = [shard_segments(24, 2, world, r) for r in range(world)]
+        assert [s.segments for s in shards] == [48 // world] * world
+        covered = [i for s in shards for i in s.segment_range]
+        assert covered == list(range(48))
+        shards = [shard_segments(80, 8, world, r, by="segment") for r in range(world)]
+        assert sum(s.segments for s in shards) == 640 and shards[-1].segment_range[-1] == 639
+    uneven = [shard_segments(5, 1, 3, r, by="segment") for r in range(3)]
+    assert [list(s.segment_range) for s in uneven] == [[0, 1], [2, 3], [4]]
+    with pytest.raises(ValueError):
+        shard_segments(24, 2, 5, 0)
+
+
+_GLOO = r"""
+import os, sys, datetime
+sys.path.insert(0, {root!r})
+import torch.distributed as dist
+from pitch_b200.shard import gather_int64, shard_segments
+rank, world, mode = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3]
+os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=sys.argv[4], RANK=str(rank), WORLD_SIZE=str(world))
+dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=8))
+sh = shard_segments(24, 2, world, rank)
+if mode == "die" and rank == 1:
+    raise SystemExit(3)                      # a rank that never reaches the gather
+got = gather_int64([0xFFFFFFFFFFFFFFF0 + rank, sh.first_segment, sh.segments])
+assert got == [[0xFFFFFFFFFFFFFFF0 + r, r * 24, 24] for r in range(world)], got
+print("ok", rank)
+dist.destroy_process_group()
+"""
+
+
+def _spawn(mode, port):
+    code = _GLOO.format(root=str(ROOT))
+    return [subprocess.Popen([sys.executable, "-c", code, str(r), "2", mode, str(port)], stdout=subprocess.PIPE,
+                             stderr=subprocess.PIPE, text=True) for r in range(2)]
+
+
+def test_checksum_gather_on_two_gloo_ranks():
+    procs = _spawn("ok", 29731)
+    outs = [p.communicate(timeout=120) for p in procs]
+    assert [p.returncode for p in procs] == [0, 0], outs
+    assert all("ok" in o[0] for o in outs)
+
+
+def test_gather_fails_cleanly_when_a_rank_is_missing():
+    procs = _spawn("die", 29733)
+    outs = [p.communicate(timeout=120) for p in procs]
+    assert procs[1].returncode == 3
+    assert procs[0].returncode not in (0, None), outs     # the survivor gets an error, it does not hang
