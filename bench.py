@@ -262,6 +262,8 @@ def run_ours(args) -> None:
         segments = shard_segments(LAYERS, KV_HEADS, n_gpus, rank, by="layer").segments
     else:
         segments = SEGMENTS
+    if args.segments:
+        segments = args.segments
     total_steps = args.warmup + args.steps
     tokens0 = TOKENS - total_steps                       # the last timed step decodes exactly 32,768 tokens
     if tokens0 < 1:
@@ -285,15 +287,15 @@ def run_ours(args) -> None:
             dist.barrier()
         torch.cuda.synchronize(dev)
 
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    t_wall0 = time.time()
     for i in range(args.warmup):
         cache.append(new_k[i], new_v[i])
         cache.decode()
     barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
     bytes_total = 0
-    t_wall0 = time.time()
     for i in range(args.steps):
         ev[i][0].record(stream)
         cache.append(new_k[args.warmup + i], new_v[args.warmup + i])
@@ -303,46 +305,49 @@ def run_ours(args) -> None:
         rd, wr = step_bytes(segments, cache.tokens)
         bytes_total += rd + wr
     barrier()
-    t_wall1 = time.time()
-    clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
     assert cache.tokens == TOKENS
     step_ms = ev[0][0].elapsed_time(ev[-1][2]) / args.steps
     decode_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
     sums = cache.checksums()
 
-    # ---- end to end through the public API with host buffers: the new token comes from pinned host
-    # memory, the decoded cache goes back to pinned host memory, every step
-    e2e_steps = max(2, min(5, args.steps))
-    cache.truncate(TOKENS - GROUP)                      # make room again (group boundary)
-    hk = torch.randn((e2e_steps + 1, segments, 1, DIM)).pin_memory()
-    hv = torch.randn((e2e_steps + 1, segments, 1, DIM)).pin_memory()
-    host_k = torch.empty((segments, TOKENS, DIM), dtype=torch.bfloat16).pin_memory()
-    host_v = torch.empty((segments, TOKENS, DIM), dtype=torch.bfloat16).pin_memory()
+    # ---- end to end through the public API with host buffers: every step the new token comes from
+    # pinned host memory and the decoded cache (both output buffers, whole) goes back to pinned host memory
+    e2e_ms, e2e_bytes, d2h, e2e_steps = 0.0, 0, 0, 0
+    if not args.kernel_only:
+        e2e_steps = max(3, min(10, args.steps))
+        cache.truncate(TOKENS - GROUP)                      # make room again (a group boundary)
+        hk = torch.randn((e2e_steps + 1, segments, 1, DIM)).pin_memory()
+        hv = torch.randn((e2e_steps + 1, segments, 1, DIM)).pin_memory()
+        host_k = torch.empty((segments, cache.capacity, DIM), dtype=torch.bfloat16).pin_memory()
+        host_v = torch.empty((segments, cache.capacity, DIM), dtype=torch.bfloat16).pin_memory()
 
-    def e2e_step(i):
-        dk = hk[i].to(dev, non_blocking=True)
-        dv = hv[i].to(dev, non_blocking=True)
-        cache.append(dk, dv)
-        ko, vo = cache.decode()
-        t = cache.tokens
-        host_k[:, :t].copy_(ko, non_blocking=True)
-        host_v[:, :t].copy_(vo, non_blocking=True)
-        return t
+        def e2e_step(i):
+            dk = hk[i].to(dev, non_blocking=True)
+            dv = hv[i].to(dev, non_blocking=True)
+            cache.append(dk, dv)
+            cache.decode()
+            host_k.copy_(cache.planes[0].out, non_blocking=True)
+            host_v.copy_(cache.planes[1].out, non_blocking=True)
+            return cache.tokens
 
-    e2e_step(0)
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    e2e_bytes = 0
-    d2h = 0
-    for i in range(1, e2e_steps + 1):
-        t = e2e_step(i)
-        rd, wr = step_bytes(segments, t)
-        e2e_bytes += rd + wr
-        d2h = wr
-    e1.record(stream)
-    barrier()
-    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+        e2e_step(0)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(1, e2e_steps + 1):
+            t = e2e_step(i)
+            rd, wr = step_bytes(segments, t)
+            e2e_bytes += rd + wr
+        e1.record(stream)
+        barrier()
+        e2e_ms = e0.elapsed_time(e1) / e2e_steps
+        d2h = host_k.numel() * 2 + host_v.numel() * 2
+    # keep the GPU busy long enough for nvidia-smi (one sample per 100 ms) to see it under load
+    t_busy = time.time()
+    while not args.kernel_only and time.time() - t_busy < 0.6:
+        cache.decode()
+        torch.cuda.synchronize(dev)
+    clocks = sampler.stop(t_wall0, time.time()) if rank == 0 else None
 
     # ---- reduce over ranks: slowest rank sets the time
     stats = torch.tensor([step_ms, decode_ms, e2e_ms], dtype=torch.float64, device=dev)
@@ -368,7 +373,7 @@ def run_ours(args) -> None:
         tf = ROOT / "profiles" / "cache_decode_traffic.json"
         if tf.exists():
             traffic = json.loads(tf.read_text()).get("dram_bytes_per_launch_full_size")
-        cpu = cpu_baseline_sample() if n_gpus == 1 else None
+        cpu = cpu_baseline_sample() if (n_gpus == 1 and not args.kernel_only) else None
         out = {
             "metric": "kv_cache_decode_throughput", "value": round(value, 2), "unit": "GB/s", "n_gpus": n_gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(step_ms, 5), "higher_is_better": True,
@@ -381,14 +386,17 @@ def run_ours(args) -> None:
                          "frac": round(achieved / peak, 4), "traffic": traffic, "peak_source": peak_src,
                          "frac_of_nominal_8000": round(achieved / 8000.0, 4), "kernel": "cache_decode_d64b4_kernel",
                          "kernel_ms": round(decode_ms, 5)},
-            "e2e": {"value": round(e2e_bytes / e2e_steps * n_gpus / (e2e_ms * 1e-3) / 1e9, 3), "unit": "GB/s",
-                    "h2d_bytes_per_step": int(2 * segments * DIM * 4), "d2h_bytes_per_step": int(d2h),
-                    "ms_per_step": round(e2e_ms, 4)},
+            "e2e": None if not e2e_steps else {
+                "value": round(e2e_bytes / e2e_steps * n_gpus / (e2e_ms * 1e-3) / 1e9, 3), "unit": "GB/s",
+                "h2d_bytes_per_step": int(2 * segments * DIM * 4), "d2h_bytes_per_step": int(d2h),
+                "ms_per_step": round(e2e_ms, 4), "steps": e2e_steps},
             "gpu_launches": 3 * args.steps,
             "clocks": clocks,
             "parity_gate": gate,
             "checksums": all_sums,
         }
+        if args.segments:
+            out["reduced"] = True
         if cpu is not None:
             out["cpu_baseline"] = cpu
         print(json.dumps(out))
@@ -400,10 +408,14 @@ def run_ours(args) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
+    ap.add_argument("--segments", type=int, default=0,
+                    help="profiling aid: decode only this many segments per GPU (marks the line \"reduced\")")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="profiling aid: skip the end-to-end and CPU-baseline legs")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
