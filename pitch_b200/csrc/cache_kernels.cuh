@@ -1,16 +1,24 @@
 // Whole-cache decode for head dimension 64 at 4 bits: the per-step bottleneck of a
 // compressed KV cache (all tokens of every layer and KV head are decoded each step).
 //
-// One launch covers every plane (K, V) and every segment (layer x KV head).  A CTA of 128
-// threads decodes 128 consecutive tokens of one (plane, segment):
-//   * TurboQuant plane  - one vector per thread: the thread's 32 code bytes arrive as two
-//     128-bit loads, the 64-point Walsh-Hadamard transform runs entirely in registers, and the
-//     result leaves through a padded warp-private shared tile so that every global store
-//     instruction writes 512 contiguous bytes per warp.
-//   * per-channel plane - a lane owns 8 channels of 4 tokens per step (see channel_kernels.cuh);
-//     loads are 4 bytes and stores 16 bytes per lane, both contiguous across the warp.
-// The kernel is bound by HBM traffic: per token it reads 32 code bytes plus 4 bytes of side
-// information and writes 64 elements.
+// One persistent launch covers every plane (K, V) and every segment (layer x KV head): one CTA
+// of 16 warps per SM; a warp takes tiles of 32 consecutive tokens of one segment round-robin and
+// decodes that tile for every plane before moving on.  Per token the kernel reads 32 code bytes
+// plus 4 bytes of side information and writes 64 elements, so it is bound by HBM traffic as
+// long as the instruction count per token stays low; the two paths are built around that:
+//
+//   * TurboQuant plane - one vector per lane.  Two 128-bit loads bring the lane's 32 code
+//     bytes.  Each byte holds two codes (a, b); a 256-entry table in shared memory maps the byte
+//     to (c[a] + c[b], c[a] - c[b]), i.e. centroid lookup and the first Walsh-Hadamard stage in
+//     one 64-bit load.  The table is replicated over 32 lane slots (entry e, slot l at byte
+//     e*256 + l*8), so a lookup is bank-conflict free for any codes and its address is a single
+//     byte permute of the code word.  The remaining five stages run on float2 pairs with packed
+//     fp32x2 instructions, the result is scaled, rounded, sign-flipped as packed words, and
+//     leaves through a padded warp-private shared tile so that every global store instruction
+//     writes 512 contiguous bytes per warp.
+//   * per-channel plane - a lane owns 8 channels ("slab") of 4 of the 32 tokens per step; codes
+//     become floats by byte permutes into the mantissa of 2^23; loads are 4 bytes and stores 16
+//     bytes per lane, both contiguous across the warp.
 #pragma once
 
 #include "channel_kernels.cuh"
@@ -18,18 +26,85 @@
 
 namespace pitch {
 
-constexpr int C64_THREADS = 128;
-constexpr int C64_WARPS = 4;
-constexpr int C64_TILE = 128;   // tokens per CTA
+constexpr int CD_THREADS = 512;
+constexpr int CD_WARPS = CD_THREADS / 32;
+constexpr int CD_TABLE_BYTES = 256 * 32 * 8;   // byte-pair table: 256 entries x 32 lane slots x float2
 
 struct Book16 { float c[16]; };
 
+// float2 arithmetic on the packed fp32x2 pipe; each component is one IEEE rounding.
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 sub2(float2 a, float2 b) { return __ffma2_rn(b, make_float2(-1.0f, -1.0f), a); }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+
+// Walsh-Hadamard stages h = 2, 4, ..., 32 on 64 values held as 32 adjacent pairs
+// (pair p = elements 2p, 2p+1); stage h = 1 is already folded into the table lookup.
+__device__ __forceinline__ void wht64_pairs_from_stage2(float2 (&v)[32]) {
+#pragma unroll
+    for (int h = 1; h < 32; h <<= 1) {          // pair-index bit h = element bit 2h
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            if (!(i & h)) {
+                const float2 a = v[i], b = v[i | h];
+                v[i] = add2(a, b);
+                v[i | h] = sub2(a, b);
+            }
+        }
+    }
+}
+
+template <typename T> struct PairStore;   // 32 float2 -> this lane's 64-element row in the staging tile
+template <> struct PairStore<float> {
+    static __device__ __forceinline__ void row(const float2 (&v)[32], const uint32_t* sign, unsigned char* dst) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const uint2 m = *reinterpret_cast<const uint2*>(sign + 2 * j);      // same address in every lane: broadcast
+            uint4 q;
+            q.x = __float_as_uint(v[2 * j].x) ^ ((m.x & 0x8000u) << 16);
+            q.y = __float_as_uint(v[2 * j].y) ^ (m.x & 0x80000000u);
+            q.z = __float_as_uint(v[2 * j + 1].x) ^ ((m.y & 0x8000u) << 16);
+            q.w = __float_as_uint(v[2 * j + 1].y) ^ (m.y & 0x80000000u);
+            *reinterpret_cast<uint4*>(dst + j * 16) = q;
+        }
+    }
+};
+template <> struct PairStore<__half> {
+    static __device__ __forceinline__ uint32_t cvt(float2 f) {
+        const __half2 h = __float22half2_rn(f);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    }
+    static __device__ __forceinline__ void row(const float2 (&v)[32], const uint32_t* sign, unsigned char* dst) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint4 m = *reinterpret_cast<const uint4*>(sign + 4 * j);      // same address in every lane: broadcast
+            *reinterpret_cast<uint4*>(dst + j * 16) =
+                make_uint4(cvt(v[4 * j]) ^ m.x, cvt(v[4 * j + 1]) ^ m.y, cvt(v[4 * j + 2]) ^ m.z, cvt(v[4 * j + 3]) ^ m.w);
+        }
+    }
+};
+template <> struct PairStore<__nv_bfloat16> {
+    static __device__ __forceinline__ uint32_t cvt(float2 f) {
+        const __nv_bfloat162 h = __float22bfloat162_rn(f);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    }
+    static __device__ __forceinline__ void row(const float2 (&v)[32], const uint32_t* sign, unsigned char* dst) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint4 m = *reinterpret_cast<const uint4*>(sign + 4 * j);      // same address in every lane: broadcast
+            *reinterpret_cast<uint4*>(dst + j * 16) =
+                make_uint4(cvt(v[4 * j]) ^ m.x, cvt(v[4 * j + 1]) ^ m.y, cvt(v[4 * j + 2]) ^ m.z, cvt(v[4 * j + 3]) ^ m.w);
+        }
+    }
+};
+
 // 32 vectors (d = 64, b = 4) per warp, one per lane.  `codes`, `norms`, `out` point at the
-// warp's first vector; nvalid in 1...32.
+// warp's first vector; nvalid in 1...32.  `table` is the byte-pair table, `sign` 32 words whose
+// bit 15 / bit 31 say whether element 2p / 2p+1 is negated by the rotation's diagonal.
 template <typename T>
 __device__ __forceinline__ void turbo64_decode_warp(const uint4* __restrict__ codes, const float* __restrict__ norms,
-                                                    T* __restrict__ out, int nvalid, const float* s_book,
-                                                    uint32_t neg_lo, uint32_t neg_hi, unsigned char* stage, int lane) {
+                                                    T* __restrict__ out, int nvalid, const unsigned char* table,
+                                                    const uint32_t* sign, unsigned char* stage, int lane) {
+    typedef WarpStage<T, 64> Stage;
     const bool valid = lane < nvalid;
     uint4 c0 = make_uint4(0, 0, 0, 0), c1 = c0;
     float norm = 0.0f;
@@ -39,21 +114,46 @@ __device__ __forceinline__ void turbo64_decode_warp(const uint4* __restrict__ co
         norm = __ldg(norms + lane);
     }
     const uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-    float x[64];
+    const uint32_t slot = (uint32_t)lane * 8u;
+    float2 v[32];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-#pragma unroll
-        for (int k = 0; k < 8; ++k) x[8 * j + k] = s_book[(w[j] >> (4 * k)) & 15u];
+        // byte k of the word -> table offset (byte << 8) | slot, one permute each
+        v[4 * j + 0] = *reinterpret_cast<const float2*>(table + __byte_perm(w[j], slot, 0x5504));
+        v[4 * j + 1] = *reinterpret_cast<const float2*>(table + __byte_perm(w[j], slot, 0x5514));
+        v[4 * j + 2] = *reinterpret_cast<const float2*>(table + __byte_perm(w[j], slot, 0x5524));
+        v[4 * j + 3] = *reinterpret_cast<const float2*>(table + __byte_perm(w[j], slot, 0x5534));
     }
-    wht_regs(x, 64);
+    wht64_pairs_from_stage2(v);
     // 1/sqrt(64) is a power of two, so (x * rs) * norm == x * (rs * norm) in float32.
-    const float scale = 0.125f * norm;
+    const float sc = 0.125f * norm;
+    const float2 scale = make_float2(sc, sc);
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        x[i] = flip_if(x[i], neg_lo, i) * scale;
-        x[32 + i] = flip_if(x[32 + i], neg_hi, i) * scale;
+    for (int i = 0; i < 32; ++i) v[i] = mul2(v[i], scale);
+    PairStore<T>::row(v, sign, stage + lane * Stage::PITCHB);
+    __syncwarp();
+    const int valid_elems = nvalid * 64;
+#pragma unroll
+    for (int k = 0; k < Stage::CPR; ++k) {
+        const int c = k * 32 + lane;
+        const uint4 q = *reinterpret_cast<const uint4*>(stage + (c / Stage::CPR) * Stage::PITCHB + (c % Stage::CPR) * 16);
+        if (c * Stage::EPC < valid_elems) stg_stream(reinterpret_cast<uint4*>(out) + c, q);
     }
-    WarpStage<T, 64>::store(out, nvalid * 64, true, stage, lane, x);
+    __syncwarp();
+}
+
+// float(code) for the 8 codes of a word without integer-to-float conversions: the code byte is
+// permuted into the mantissa of 2^23 (0x4B0000cc = 2^23 + code exactly), then 2^23 is subtracted.
+__device__ __forceinline__ void codes8_to_floats(uint32_t w, float (&f)[8]) {
+    const uint32_t even = w & 0x0F0F0F0Fu, odd = (w >> 4) & 0x0F0F0F0Fu;
+    f[0] = __uint_as_float(__byte_perm(even, 0x4B000000u, 0x7440)) - 8388608.0f;
+    f[1] = __uint_as_float(__byte_perm(odd, 0x4B000000u, 0x7440)) - 8388608.0f;
+    f[2] = __uint_as_float(__byte_perm(even, 0x4B000000u, 0x7441)) - 8388608.0f;
+    f[3] = __uint_as_float(__byte_perm(odd, 0x4B000000u, 0x7441)) - 8388608.0f;
+    f[4] = __uint_as_float(__byte_perm(even, 0x4B000000u, 0x7442)) - 8388608.0f;
+    f[5] = __uint_as_float(__byte_perm(odd, 0x4B000000u, 0x7442)) - 8388608.0f;
+    f[6] = __uint_as_float(__byte_perm(even, 0x4B000000u, 0x7443)) - 8388608.0f;
+    f[7] = __uint_as_float(__byte_perm(odd, 0x4B000000u, 0x7443)) - 8388608.0f;
 }
 
 // 32 tokens (d = 64, b = 4, all inside one group) per warp: lane = (token lane 0..3, slab 0..7).
@@ -62,8 +162,6 @@ __device__ __forceinline__ void channel64_decode_warp(const uint32_t* __restrict
                                                       const __half* __restrict__ group_ranges, T* __restrict__ out,
                                                       int nvalid, int lane) {
     const int slab = lane & 7, tok_lane = lane >> 3;
-    float lo[8], step[8];
-    load_slab_range(group_ranges, 0, 64, slab, 15.0f, lo, step);
     uint32_t w[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
@@ -71,17 +169,23 @@ __device__ __forceinline__ void channel64_decode_warp(const uint32_t* __restrict
         w[k] = 0;
         if (t < nvalid) w[k] = __ldg(codes + t * 8 + slab);
     }
+    float lo[8], step[8];
+    load_slab_range(group_ranges, 0, 64, slab, 15.0f, lo, step);
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
         const int t = 4 * k + tok_lane;
-        if (t < nvalid) decode_slab<4, T>(w[k], lo, step, out + t * 64 + slab * 8);
+        float f[8];
+        codes8_to_floats(w[k], f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = f[i] * step[i] + lo[i];
+        if (t < nvalid) store8<T>(out + t * 64 + slab * 8, f);
     }
 }
 
 struct Plane64 {
-    int kind;                 // PITCH_PLANE_TURBO or PITCH_PLANE_CHANNEL
-    int group_size;           // channel planes: multiple of 32
-    uint32_t neg_lo, neg_hi;  // sign diagonal of the rotation (turbo planes)
+    int kind;                 // 0 = TurboQuant, 1 = per-channel
+    int group_size;           // per-channel planes: multiple of 32
+    uint32_t neg_lo, neg_hi;  // rotation diagonal: bit i set when element i (resp. 32 + i) is negated
     const unsigned char* codes;
     int64_t codes_seg_stride;
     const unsigned char* side;
@@ -92,65 +196,66 @@ struct Plane64 {
 
 struct Cache64Params {
     int n_planes;
-    int tiles_per_seg;
+    int tiles_per_seg;        // warp tiles (32 tokens) per segment
     int64_t tokens;
+    int64_t total_tiles;      // segments * tiles_per_seg
     Plane64 plane[4];
     Book16 book;              // TurboQuant centroids for (64, 4)
 };
 
-// grid = segments * tiles_per_seg * n_planes; the plane index varies fastest so that CTAs
-// running side by side mix the two kinds of work.
 template <typename T>
-__global__ void __launch_bounds__(C64_THREADS)
+constexpr int cache64_smem_bytes() { return CD_TABLE_BYTES + 4 * 32 * 4 + CD_WARPS * WarpStage<T, 64>::BYTES; }
+
+// grid = number of SMs (persistent), CD_THREADS threads, cache64_smem_bytes<T>() dynamic shared memory.
+template <typename T>
+__global__ void __launch_bounds__(CD_THREADS, 1)
 cache_decode_d64b4_kernel(const __grid_constant__ Cache64Params p) {
-    __shared__ float s_book[16];
-    __shared__ __align__(16) unsigned char s_stage[C64_WARPS][WarpStage<T, 64>::BYTES];
+    extern __shared__ __align__(1024) unsigned char smem[];
+    unsigned char* table = smem;
+    uint32_t* s_sign = reinterpret_cast<uint32_t*>(smem + CD_TABLE_BYTES);           // [4][32]
+    unsigned char* stage_base = smem + CD_TABLE_BYTES + 4 * 32 * 4;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int pl = blockIdx.x % p.n_planes;
-    const int64_t rest = blockIdx.x / p.n_planes;
-    const int64_t seg = rest / p.tiles_per_seg;
-    const int tile = (int)(rest - seg * p.tiles_per_seg);
-    const Plane64& P = p.plane[pl];
 
-    const int64_t t0 = (int64_t)tile * C64_TILE + warp * 32;   // this warp's first token
-    if (P.kind == 0) {
-        if (threadIdx.x < 16) s_book[threadIdx.x] = p.book.c[threadIdx.x];
-        __syncthreads();
-        if (t0 >= p.tokens) return;
-        const int64_t left = p.tokens - t0;
-        const int nvalid = left < 32 ? (int)left : 32;
-        const unsigned char* codes = P.codes + seg * P.codes_seg_stride + t0 * 32;
-        const float* norms = reinterpret_cast<const float*>(P.side + seg * P.side_seg_stride) + t0;
-        T* out = reinterpret_cast<T*>(P.out + seg * P.out_seg_stride) + t0 * 64;
-        turbo64_decode_warp<T>(reinterpret_cast<const uint4*>(codes), norms, out, nvalid, s_book, P.neg_lo, P.neg_hi,
-                               s_stage[warp], lane);
-    } else {
-        if (t0 >= p.tokens) return;
-        const int64_t left = p.tokens - t0;
-        const int nvalid = left < 32 ? (int)left : 32;
-        const int64_t g = t0 / P.group_size;
-        const unsigned char* codes = P.codes + seg * P.codes_seg_stride + t0 * 32;
-        const __half* ranges = reinterpret_cast<const __half*>(P.side + seg * P.side_seg_stride) + g * 128;
-        T* out = reinterpret_cast<T*>(P.out + seg * P.out_seg_stride) + t0 * 64;
-        channel64_decode_warp<T>(reinterpret_cast<const uint32_t*>(codes), ranges, out, nvalid, lane);
+    bool any_turbo = false;
+    for (int pl = 0; pl < p.n_planes; ++pl) any_turbo |= p.plane[pl].kind == 0;
+    if (any_turbo) {
+        for (int idx = threadIdx.x; idx < 256 * 32; idx += CD_THREADS) {
+            const int e = idx >> 5;
+            const float a = p.book.c[e & 15], b = p.book.c[e >> 4];
+            *reinterpret_cast<float2*>(table + idx * 8) = make_float2(a + b, a - b);
+        }
+        if (threadIdx.x < 4 * 32) {
+            const int pl = threadIdx.x >> 5, i = threadIdx.x & 31;       // packed pair i = elements 2i, 2i+1
+            const uint32_t m = i < 16 ? p.plane[pl].neg_lo : p.plane[pl].neg_hi;
+            const int bit = (2 * i) & 31;
+            s_sign[threadIdx.x] = (((m >> bit) & 1u) << 15) | (((m >> (bit + 1)) & 1u) << 31);
+        }
     }
-}
-
-// Stand-alone TurboQuant decode, d = 64, b = 4, 16-byte aligned buffers: same warp routine.
-template <typename T>
-__global__ void __launch_bounds__(C64_THREADS)
-turbo64_decode_kernel(const uint4* __restrict__ codes, const float* __restrict__ norms, T* __restrict__ out,
-                      int64_t count, uint32_t neg_lo, uint32_t neg_hi, const Book16 book) {
-    __shared__ float s_book[16];
-    __shared__ __align__(16) unsigned char s_stage[C64_WARPS][WarpStage<T, 64>::BYTES];
-    if (threadIdx.x < 16) s_book[threadIdx.x] = book.c[threadIdx.x];
     __syncthreads();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int64_t v0 = ((int64_t)blockIdx.x * C64_WARPS + warp) * 32;
-    if (v0 >= count) return;
-    const int64_t left = count - v0;
-    turbo64_decode_warp<T>(codes + v0 * 2, norms + v0, out + v0 * 64, left < 32 ? (int)left : 32, s_book, neg_lo,
-                           neg_hi, s_stage[warp], lane);
+    unsigned char* stage = stage_base + warp * WarpStage<T, 64>::BYTES;
+
+    for (int64_t tile = (int64_t)blockIdx.x * CD_WARPS + warp; tile < p.total_tiles;
+         tile += (int64_t)gridDim.x * CD_WARPS) {
+        const int64_t seg = tile / p.tiles_per_seg;
+        const int64_t t0 = (tile - seg * p.tiles_per_seg) * 32;
+        const int64_t left = p.tokens - t0;
+        const int nvalid = left < 32 ? (int)left : 32;
+#pragma unroll 1
+        for (int pl = 0; pl < p.n_planes; ++pl) {
+            const Plane64& P = p.plane[pl];
+            const unsigned char* codes = P.codes + seg * P.codes_seg_stride + t0 * 32;
+            T* out = reinterpret_cast<T*>(P.out + seg * P.out_seg_stride) + t0 * 64;
+            if (P.kind == 0) {
+                const float* norms = reinterpret_cast<const float*>(P.side + seg * P.side_seg_stride) + t0;
+                turbo64_decode_warp<T>(reinterpret_cast<const uint4*>(codes), norms, out, nvalid, table,
+                                       s_sign + pl * 32, stage, lane);
+            } else {
+                const int64_t g = t0 / P.group_size;
+                const __half* ranges = reinterpret_cast<const __half*>(P.side + seg * P.side_seg_stride) + g * 128;
+                channel64_decode_warp<T>(reinterpret_cast<const uint32_t*>(codes), ranges, out, nvalid, lane);
+            }
+        }
+    }
 }
 
 // ------------------------------------------------------------------------------------------

@@ -164,6 +164,37 @@ unsigned vec_grid(int64_t count, int dim) {
     return (unsigned)ceil_div(ceil_div(count, vpw), VEC_WARPS);
 }
 
+// Persistent whole-cache decode: one CTA per SM, opt-in dynamic shared memory.
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+template <typename T>
+int launch_cache64(const Cache64Params& p, cudaStream_t s) {
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    constexpr int smem = cache64_smem_bytes<T>();
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        if (cudaFuncSetAttribute(cache_decode_d64b4_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return launch_status(false, "cache_decode (shared memory opt-in)");
+        configured[dev] = true;
+    }
+    int64_t ctas = ceil_div(p.total_tiles, CD_WARPS);
+    if (ctas > sm_count()) ctas = sm_count();
+    cache_decode_d64b4_kernel<T><<<(unsigned)ctas, CD_THREADS, smem, s>>>(p);
+    return PITCH_OK;
+}
+
 template <int BITS, typename T>
 int launch_turbo_encode(int dim, uint32_t seed, const void* in, void* codes, void* scales, int64_t count,
                         cudaStream_t s) {
@@ -183,12 +214,22 @@ int launch_turbo_decode(int dim, uint32_t seed, const void* codes, const void* s
     if (!fetch_book<BITS>(dim, book))
         return fail(PITCH_ERR_INVALID_INPUT, "no TurboQuant codebook for dim %d, bits %d", dim, BITS);
     if (BITS == 4 && dim == 64 && aligned16(codes) && aligned16(out)) {
-        Book16 b16;
-        memcpy(b16.c, book.c, sizeof b16.c);
-        turbo64_decode_kernel<T><<<(unsigned)ceil_div(count, C64_TILE), C64_THREADS, 0, s>>>(
-            static_cast<const uint4*>(codes), static_cast<const float*>(scales), static_cast<T*>(out), count,
-            negate_mask32(seed, 0), negate_mask32(seed, 32), b16);
-        return PITCH_OK;
+        Cache64Params p;
+        memset(&p, 0, sizeof p);
+        p.n_planes = 1;
+        p.tiles_per_seg = (int)ceil_div(count, 32);
+        if (ceil_div(count, 32) <= 0x7FFFFFFF) {
+            p.tokens = count;
+            p.total_tiles = p.tiles_per_seg;
+            p.plane[0].kind = 0;
+            p.plane[0].neg_lo = negate_mask32(seed, 0);
+            p.plane[0].neg_hi = negate_mask32(seed, 32);
+            p.plane[0].codes = static_cast<const unsigned char*>(codes);
+            p.plane[0].side = static_cast<const unsigned char*>(scales);
+            p.plane[0].out = static_cast<unsigned char*>(out);
+            memcpy(p.book.c, book.c, sizeof p.book.c);
+            return launch_cache64<T>(p, s);
+        }
     }
     turbo_decode_kernel<BITS, T><<<vec_grid(count, dim), VEC_THREADS, 0, s>>>(
         static_cast<const uint32_t*>(codes), static_cast<const float*>(scales), static_cast<T*>(out), count, dim, seed,
@@ -535,8 +576,9 @@ int pitch_enqueue_cache_decode(const pitch_cache_desc* d, void* stream) {
         Cache64Params p;
         memset(&p, 0, sizeof p);
         p.n_planes = d->n_planes;
-        p.tiles_per_seg = (int)ceil_div(d->tokens, C64_TILE);
+        p.tiles_per_seg = (int)ceil_div(d->tokens, 32);
         p.tokens = d->tokens;
+        p.total_tiles = d->segments * p.tiles_per_seg;
         bool need_book = false;
         for (int i = 0; i < d->n_planes; ++i) {
             const pitch_plane& pl = d->planes[i];
@@ -558,9 +600,9 @@ int pitch_enqueue_cache_decode(const pitch_cache_desc* d, void* stream) {
             if (!fetch_book<4>(64, book)) return fail(PITCH_ERR_INVALID_INPUT, "no TurboQuant codebook for dim 64, bits 4");
             memcpy(p.book.c, book.c, sizeof p.book.c);
         }
-        const int64_t grid = d->segments * p.tiles_per_seg * p.n_planes;
-        if (grid > 0x7FFFFFFFLL) return fail(PITCH_ERR_INVALID_INPUT, "cache too large for one launch");
-        PITCH_DISPATCH_DTYPE(d->out_dtype, (cache_decode_d64b4_kernel<T><<<(unsigned)grid, C64_THREADS, 0, s>>>(p)));
+        int st = 0;
+        PITCH_DISPATCH_DTYPE(d->out_dtype, st = (launch_cache64<T>(p, s)));
+        if (st) return st;
         return launch_status(false, "cache_decode");
     }
 
