@@ -33,9 +33,17 @@ constexpr int CD_TABLE_BYTES = 256 * 32 * 8;   // byte-pair table: 256 entries x
 struct Book16 { float c[16]; };
 
 // float2 arithmetic on the packed fp32x2 pipe; each component is one IEEE rounding.
+// Caution, measured on sm_100a: a packed multiply whose only use is a packed add is contracted
+// into one fused operation by the assembler even for the round-to-nearest forms and with
+// contraction disabled.  Where the two roundings matter (per-channel decode) the add is
+// therefore done per component with scalar round-to-nearest adds, which are never contracted.
 __device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
 __device__ __forceinline__ float2 sub2(float2 a, float2 b) { return __ffma2_rn(b, make_float2(-1.0f, -1.0f), a); }
 __device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 mul2_then_add(float2 a, float2 b, float2 c) {
+    const float2 m = __fmul2_rn(a, b);
+    return make_float2(__fadd_rn(m.x, c.x), __fadd_rn(m.y, c.y));
+}
 
 // Walsh-Hadamard stages h = 2, 4, ..., 32 on 64 values held as 32 adjacent pairs
 // (pair p = elements 2p, 2p+1); stage h = 1 is already folded into the table lookup.
@@ -97,23 +105,56 @@ template <> struct PairStore<__nv_bfloat16> {
     }
 };
 
-// 32 vectors (d = 64, b = 4) per warp, one per lane.  `codes`, `norms`, `out` point at the
-// warp's first vector; nvalid in 1...32.  `table` is the byte-pair table, `sign` 32 words whose
-// bit 15 / bit 31 say whether element 2p / 2p+1 is negated by the rotation's diagonal.
-template <typename T>
-__device__ __forceinline__ void turbo64_decode_warp(const uint4* __restrict__ codes, const float* __restrict__ norms,
-                                                    T* __restrict__ out, int nvalid, const unsigned char* table,
-                                                    const uint32_t* sign, unsigned char* stage, int lane) {
-    typedef WarpStage<T, 64> Stage;
-    const bool valid = lane < nvalid;
-    uint4 c0 = make_uint4(0, 0, 0, 0), c1 = c0;
-    float norm = 0.0f;
-    if (valid) {
-        c0 = ldg_stream(codes + 2 * lane);
-        c1 = ldg_stream(codes + 2 * lane + 1);
-        norm = __ldg(norms + lane);
+// What one lane needs from global memory to decode its share of a 32-token tile of one plane.
+// Fetched one work item ahead of its use, so the loads of item k+1 are in flight while item k
+// is being decoded.
+struct Prefetch64 {
+    uint4 a, b;   // TurboQuant: the lane's 32 code bytes.  Per-channel: code words of tokens 4k + (lane >> 3), k = 0..7
+    uint4 c, d;   // TurboQuant: c.x = norm bits.  Per-channel: fp16 minima (c) and maxima (d) of the lane's 8 channels
+};
+
+__device__ __forceinline__ uint32_t ldg_stream32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void prefetch_turbo64(Prefetch64& f, const uint4* __restrict__ codes,
+                                                 const float* __restrict__ norms, int nvalid, int lane) {
+    f.a = f.b = f.c = f.d = make_uint4(0, 0, 0, 0);
+    if (lane < nvalid) {
+        f.a = ldg_stream(codes + 2 * lane);
+        f.b = ldg_stream(codes + 2 * lane + 1);
+        f.c.x = ldg_stream32(reinterpret_cast<const uint32_t*>(norms) + lane);
     }
-    const uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+}
+
+__device__ __forceinline__ void prefetch_channel64(Prefetch64& f, const uint32_t* __restrict__ codes,
+                                                   const __half* __restrict__ group_ranges, int nvalid, int lane) {
+    const int slab = lane & 7, tok_lane = lane >> 3;
+    uint32_t w[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const int t = 4 * k + tok_lane;
+        w[k] = 0;
+        if (t < nvalid) w[k] = ldg_stream32(codes + t * 8 + slab);
+    }
+    f.a = make_uint4(w[0], w[1], w[2], w[3]);
+    f.b = make_uint4(w[4], w[5], w[6], w[7]);
+    f.c = __ldg(reinterpret_cast<const uint4*>(group_ranges + slab * 8));
+    f.d = __ldg(reinterpret_cast<const uint4*>(group_ranges + 64 + slab * 8));
+}
+
+// 32 vectors (d = 64, b = 4) per warp, one per lane; nvalid in 1...32.  `table` is the byte-pair
+// table, `sign` 32 words whose bit 15 / bit 31 say whether element 2p / 2p+1 is negated by the
+// rotation's diagonal.
+template <typename T>
+__device__ __forceinline__ void turbo64_decode_warp(const Prefetch64& f, T* __restrict__ out, int nvalid,
+                                                    const unsigned char* table, const uint32_t* sign,
+                                                    unsigned char* stage, int lane) {
+    typedef WarpStage<T, 64> Stage;
+    const uint32_t w[8] = {f.a.x, f.a.y, f.a.z, f.a.w, f.b.x, f.b.y, f.b.z, f.b.w};
+    const float norm = __uint_as_float(f.c.x);
     const uint32_t slot = (uint32_t)lane * 8u;
     float2 v[32];
 #pragma unroll
@@ -144,41 +185,65 @@ __device__ __forceinline__ void turbo64_decode_warp(const uint4* __restrict__ co
 
 // float(code) for the 8 codes of a word without integer-to-float conversions: the code byte is
 // permuted into the mantissa of 2^23 (0x4B0000cc = 2^23 + code exactly), then 2^23 is subtracted.
-__device__ __forceinline__ void codes8_to_floats(uint32_t w, float (&f)[8]) {
+// Returned as adjacent pairs for the packed pipe.
+__device__ __forceinline__ void codes8_to_pairs(uint32_t w, float2 (&f)[4]) {
     const uint32_t even = w & 0x0F0F0F0Fu, odd = (w >> 4) & 0x0F0F0F0Fu;
-    f[0] = __uint_as_float(__byte_perm(even, 0x4B000000u, 0x7440)) - 8388608.0f;
-    f[1] = __uint_as_float(__byte_perm(odd, 0x4B000000u, 0x7440)) - 8388608.0f;
-    f[2] = __uint_as_float(__byte_perm(even, 0x4B000000u, 0x7441)) - 8388608.0f;
-    f[3] = __uint_as_float(__byte_perm(odd, 0x4B000000u, 0x7441)) - 8388608.0f;
-    f[4] = __uint_as_float(__byte_perm(even, 0x4B000000u, 0x7442)) - 8388608.0f;
-    f[5] = __uint_as_float(__byte_perm(odd, 0x4B000000u, 0x7442)) - 8388608.0f;
-    f[6] = __uint_as_float(__byte_perm(even, 0x4B000000u, 0x7443)) - 8388608.0f;
-    f[7] = __uint_as_float(__byte_perm(odd, 0x4B000000u, 0x7443)) - 8388608.0f;
+    const float2 magic = make_float2(8388608.0f, 8388608.0f);
+    f[0] = sub2(make_float2(__uint_as_float(__byte_perm(even, 0x4B000000u, 0x7440)),
+                            __uint_as_float(__byte_perm(odd, 0x4B000000u, 0x7440))), magic);
+    f[1] = sub2(make_float2(__uint_as_float(__byte_perm(even, 0x4B000000u, 0x7441)),
+                            __uint_as_float(__byte_perm(odd, 0x4B000000u, 0x7441))), magic);
+    f[2] = sub2(make_float2(__uint_as_float(__byte_perm(even, 0x4B000000u, 0x7442)),
+                            __uint_as_float(__byte_perm(odd, 0x4B000000u, 0x7442))), magic);
+    f[3] = sub2(make_float2(__uint_as_float(__byte_perm(even, 0x4B000000u, 0x7443)),
+                            __uint_as_float(__byte_perm(odd, 0x4B000000u, 0x7443))), magic);
 }
 
-// 32 tokens (d = 64, b = 4, all inside one group) per warp: lane = (token lane 0..3, slab 0..7).
-template <typename T>
-__device__ __forceinline__ void channel64_decode_warp(const uint32_t* __restrict__ codes,
-                                                      const __half* __restrict__ group_ranges, T* __restrict__ out,
-                                                      int nvalid, int lane) {
-    const int slab = lane & 7, tok_lane = lane >> 3;
-    uint32_t w[8];
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        const int t = 4 * k + tok_lane;
-        w[k] = 0;
-        if (t < nvalid) w[k] = __ldg(codes + t * 8 + slab);
+template <typename T> struct Pairs8;   // 4 float2 -> 8 elements of T, stored as one or two 16-byte pieces
+template <> struct Pairs8<float> {
+    static __device__ __forceinline__ void store(float* p, const float2 (&v)[4]) {
+        stg_stream(reinterpret_cast<uint4*>(p), make_uint4(__float_as_uint(v[0].x), __float_as_uint(v[0].y),
+                                                           __float_as_uint(v[1].x), __float_as_uint(v[1].y)));
+        stg_stream(reinterpret_cast<uint4*>(p) + 1, make_uint4(__float_as_uint(v[2].x), __float_as_uint(v[2].y),
+                                                               __float_as_uint(v[3].x), __float_as_uint(v[3].y)));
     }
-    float lo[8], step[8];
-    load_slab_range(group_ranges, 0, 64, slab, 15.0f, lo, step);
+};
+template <> struct Pairs8<__half> {
+    static __device__ __forceinline__ void store(__half* p, const float2 (&v)[4]) {
+        stg_stream(reinterpret_cast<uint4*>(p), make_uint4(PairStore<__half>::cvt(v[0]), PairStore<__half>::cvt(v[1]),
+                                                           PairStore<__half>::cvt(v[2]), PairStore<__half>::cvt(v[3])));
+    }
+};
+template <> struct Pairs8<__nv_bfloat16> {
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float2 (&v)[4]) {
+        stg_stream(reinterpret_cast<uint4*>(p),
+                   make_uint4(PairStore<__nv_bfloat16>::cvt(v[0]), PairStore<__nv_bfloat16>::cvt(v[1]),
+                              PairStore<__nv_bfloat16>::cvt(v[2]), PairStore<__nv_bfloat16>::cvt(v[3])));
+    }
+};
+
+// 32 tokens (d = 64, b = 4, all inside one group) per warp: lane = (token lane 0..3, slab 0..7).
+// code * step + lo with one rounding per operation.
+template <typename T>
+__device__ __forceinline__ void channel64_decode_warp(const Prefetch64& f, T* __restrict__ out, int nvalid, int lane) {
+    const int slab = lane & 7, tok_lane = lane >> 3;
+    const uint32_t w[8] = {f.a.x, f.a.y, f.a.z, f.a.w, f.b.x, f.b.y, f.b.z, f.b.w};
+    const uint32_t lo16[4] = {f.c.x, f.c.y, f.c.z, f.c.w}, hi16[4] = {f.d.x, f.d.y, f.d.z, f.d.w};
+    float2 lo[4], step[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        lo[i] = __half22float2(*reinterpret_cast<const __half2*>(&lo16[i]));
+        const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&hi16[i]));
+        step[i] = make_float2(step_of(lo[i].x, hi.x, 15.0f), step_of(lo[i].y, hi.y, 15.0f));
+    }
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
         const int t = 4 * k + tok_lane;
-        float f[8];
-        codes8_to_floats(w[k], f);
+        float2 v[4];
+        codes8_to_pairs(w[k], v);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] = f[i] * step[i] + lo[i];
-        if (t < nvalid) store8<T>(out + t * 64 + slab * 8, f);
+        for (int i = 0; i < 4; ++i) v[i] = mul2_then_add(v[i], step[i], lo[i]);
+        if (t < nvalid) Pairs8<T>::store(out + t * 64 + slab * 8, v);
     }
 }
 
@@ -234,27 +299,56 @@ cache_decode_d64b4_kernel(const __grid_constant__ Cache64Params p) {
     __syncthreads();
     unsigned char* stage = stage_base + warp * WarpStage<T, 64>::BYTES;
 
-    for (int64_t tile = (int64_t)blockIdx.x * CD_WARPS + warp; tile < p.total_tiles;
-         tile += (int64_t)gridDim.x * CD_WARPS) {
-        const int64_t seg = tile / p.tiles_per_seg;
-        const int64_t t0 = (tile - seg * p.tiles_per_seg) * 32;
-        const int64_t left = p.tokens - t0;
-        const int nvalid = left < 32 ? (int)left : 32;
+    // Work items of this warp: (tile, plane) pairs, tiles round-robin over all warps of the grid,
+    // planes innermost.  Item k+1 is fetched before item k is decoded.
+    const int64_t warp_id = (int64_t)blockIdx.x * CD_WARPS + warp;
+    const int64_t warp_stride = (int64_t)gridDim.x * CD_WARPS;
+    if (warp_id >= p.total_tiles) return;
+    const int64_t my_tiles = (p.total_tiles - warp_id + warp_stride - 1) / warp_stride;
+    const int64_t items = my_tiles * p.n_planes;
+
+    struct Item { int pl; int nvalid; int64_t seg, t0; };
+    auto locate = [&](int64_t k) {
+        Item it;
+        const int64_t tile = warp_id + (k / p.n_planes) * warp_stride;
+        it.pl = (int)(k % p.n_planes);
+        it.seg = tile / p.tiles_per_seg;
+        it.t0 = (tile - it.seg * p.tiles_per_seg) * 32;
+        const int64_t left = p.tokens - it.t0;
+        it.nvalid = left < 32 ? (int)left : 32;
+        return it;
+    };
+    auto fetch = [&](const Item& it, Prefetch64& f) {
+        const Plane64& P = p.plane[it.pl];
+        const unsigned char* codes = P.codes + it.seg * P.codes_seg_stride + it.t0 * 32;
+        const unsigned char* side = P.side + it.seg * P.side_seg_stride;
+        if (P.kind == 0)
+            prefetch_turbo64(f, reinterpret_cast<const uint4*>(codes), reinterpret_cast<const float*>(side) + it.t0,
+                             it.nvalid, lane);
+        else
+            prefetch_channel64(f, reinterpret_cast<const uint32_t*>(codes),
+                               reinterpret_cast<const __half*>(side) + (it.t0 / P.group_size) * 128, it.nvalid, lane);
+    };
+
+    Item cur = locate(0);
+    Prefetch64 fcur;
+    fetch(cur, fcur);
 #pragma unroll 1
-        for (int pl = 0; pl < p.n_planes; ++pl) {
-            const Plane64& P = p.plane[pl];
-            const unsigned char* codes = P.codes + seg * P.codes_seg_stride + t0 * 32;
-            T* out = reinterpret_cast<T*>(P.out + seg * P.out_seg_stride) + t0 * 64;
-            if (P.kind == 0) {
-                const float* norms = reinterpret_cast<const float*>(P.side + seg * P.side_seg_stride) + t0;
-                turbo64_decode_warp<T>(reinterpret_cast<const uint4*>(codes), norms, out, nvalid, table,
-                                       s_sign + pl * 32, stage, lane);
-            } else {
-                const int64_t g = t0 / P.group_size;
-                const __half* ranges = reinterpret_cast<const __half*>(P.side + seg * P.side_seg_stride) + g * 128;
-                channel64_decode_warp<T>(reinterpret_cast<const uint32_t*>(codes), ranges, out, nvalid, lane);
-            }
+    for (int64_t k = 0; k < items; ++k) {
+        Item nxt = cur;
+        Prefetch64 fnxt = fcur;
+        if (k + 1 < items) {
+            nxt = locate(k + 1);
+            fetch(nxt, fnxt);
         }
+        const Plane64& P = p.plane[cur.pl];
+        T* out = reinterpret_cast<T*>(P.out + cur.seg * P.out_seg_stride) + cur.t0 * 64;
+        if (P.kind == 0)
+            turbo64_decode_warp<T>(fcur, out, cur.nvalid, table, s_sign + cur.pl * 32, stage, lane);
+        else
+            channel64_decode_warp<T>(fcur, out, cur.nvalid, lane);
+        cur = nxt;
+        fcur = fnxt;
     }
 }
 
