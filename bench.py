@@ -369,10 +369,10 @@ def run_ours(args) -> None:
             peak, peak_src = float(json.loads(mp.read_text())["hbm_gbs"]), "measured"
         else:
             peak = 6650.0
-        traffic = None
-        tf = ROOT / "profiles" / "cache_decode_traffic.json"
-        if tf.exists():
-            traffic = json.loads(tf.read_text()).get("dram_bytes_per_launch_full_size")
+        # dram__bytes_read.sum + dram__bytes_write.sum per launch at full size, from the ncu capture
+        # summarised in profiles/cache_decode_d64b4_config4.md (part of the output is still dirty in L2
+        # when the kernel ends, so it is below the algorithmic bytes); only valid for the full workload
+        traffic = 455.6e6 if segments == SEGMENTS else None
         cpu = cpu_baseline_sample() if (n_gpus == 1 and not args.kernel_only) else None
         out = {
             "metric": "kv_cache_decode_throughput", "value": round(value, 2), "unit": "GB/s", "n_gpus": n_gpus,
