@@ -390,7 +390,7 @@ def run_ours(args) -> None:
                 "value": round(e2e_bytes / e2e_steps * n_gpus / (e2e_ms * 1e-3) / 1e9, 3), "unit": "GB/s",
                 "h2d_bytes_per_step": int(2 * segments * DIM * 4), "d2h_bytes_per_step": int(d2h),
                 "ms_per_step": round(e2e_ms, 4), "steps": e2e_steps},
-            "gpu_launches": 3 * args.steps,
+            "gpu_launches": 2 * args.steps,   # per step: one append launch, one whole-cache decode launch
             "clocks": clocks,
             "parity_gate": gate,
             "checksums": all_sums,

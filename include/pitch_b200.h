@@ -173,16 +173,17 @@ int pitch_enqueue_cache_decode(const pitch_cache_desc* desc, void* stream);
  * README.md:62-71 (enqueueEncode of the new token at codesOffset = t*h*codeStride) and, for
  * per-channel planes, README.md:85 ("the newest, partial group can be ... re-encoded as it
  * grows").  desc->tokens is the number of tokens held BEFORE the call; the codes and side
- * information of tokens [tokens, tokens + n_new) are written, for all segments, by one launch
- * per plane.  Per-channel planes keep the newest group of each segment in float32 in
- * `residual` ([segments][group_size][dim]); the new tokens are copied there and the whole group
- * is re-encoded, so codes and ranges always equal a bulk encode of the tokens seen so far.
+ * information of tokens [tokens, tokens + n_new) are written, for all segments and planes, by
+ * one launch.  Per-channel planes keep the newest group of each segment in float32 in
+ * `residual` ([segments][group_size + 2][dim]: the group's tokens, then the running per-channel
+ * minimum and maximum); the new tokens are copied there and the whole group is re-encoded, so
+ * codes and ranges always equal a bulk encode of the tokens seen so far.
  * All new tokens of a call must fall into one group: (tokens % group_size) + n_new <= group_size. */
 typedef struct pitch_append_src {
     const void* input;            /* [segments][n_new][dim] elements of in_dtype */
     int64_t input_seg_stride;     /* bytes between segments */
     void*   residual;             /* per-channel planes only, else NULL */
-    int64_t residual_seg_stride;  /* bytes between segments, >= group_size*dim*4 */
+    int64_t residual_seg_stride;  /* bytes between segments, >= (group_size+2)*dim*4 */
 } pitch_append_src;
 
 int pitch_enqueue_cache_append(const pitch_cache_desc* desc, const pitch_append_src* src, int in_dtype,

@@ -9,7 +9,7 @@ newest partial group being re-encoded as it grows.  ``KVCache`` packages that pa
   contiguous range of segments and no rank ever touches another rank's memory;
 * a *plane* is one tensor of the cache (keys or values) with its codec: per-channel
   (``ChannelQuantConfig``) or per-vector (``QuantConfig``, TurboQuant or PolarQuant);
-* ``append`` encodes new tokens for all segments (one launch per plane);
+* ``append`` encodes new tokens for all segments and planes (one launch);
 * ``decode`` reconstructs every token of every segment and plane (one launch).
 
 Layout in device memory, per plane, segment-major and token-major:
@@ -40,7 +40,7 @@ class _Plane:
     codes: object            # uint8 [segments, capacity * stride]
     side: object             # float32 [segments, capacity] | float16 [segments, groups, 2, dim]
     out: object              # out_dtype [segments, capacity, dim]
-    residual: object | None  # float32 [segments, group_size, dim] for per-channel planes
+    residual: object | None  # float32 [segments, group_size + 2, dim] for per-channel planes (tokens, running min, max)
 
     @property
     def is_channel(self) -> bool:
@@ -82,7 +82,7 @@ class KVCache:
         if isinstance(cfg, ChannelQuantConfig):
             groups = cfg.group_count(C)
             side = torch.zeros((S, groups, 2, d), dtype=torch.float16, device=dev)
-            residual = torch.zeros((S, cfg.group_size, d), dtype=torch.float32, device=dev)
+            residual = torch.zeros((S, cfg.group_size + 2, d), dtype=torch.float32, device=dev)
         else:
             side = torch.zeros((S, C), dtype=torch.float32, device=dev)
             residual = None

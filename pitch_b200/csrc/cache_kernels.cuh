@@ -119,25 +119,30 @@ __device__ __forceinline__ uint32_t ldg_stream32(const uint32_t* p) {
     return v;
 }
 
+// FULL: all 32 tokens of the tile exist (no bounds checks); otherwise nvalid in 1...31.
+template <bool FULL>
 __device__ __forceinline__ void prefetch_turbo64(Prefetch64& f, const uint4* __restrict__ codes,
                                                  const float* __restrict__ norms, int nvalid, int lane) {
-    f.a = f.b = f.c = f.d = make_uint4(0, 0, 0, 0);
-    if (lane < nvalid) {
+    if (FULL || lane < nvalid) {
         f.a = ldg_stream(codes + 2 * lane);
         f.b = ldg_stream(codes + 2 * lane + 1);
         f.c.x = ldg_stream32(reinterpret_cast<const uint32_t*>(norms) + lane);
+    } else {
+        f.a = f.b = make_uint4(0, 0, 0, 0);
+        f.c.x = 0;
     }
 }
 
+template <bool FULL>
 __device__ __forceinline__ void prefetch_channel64(Prefetch64& f, const uint32_t* __restrict__ codes,
                                                    const __half* __restrict__ group_ranges, int nvalid, int lane) {
     const int slab = lane & 7, tok_lane = lane >> 3;
+    const uint32_t* mine = codes + tok_lane * 8 + slab;      // token 4k + tok_lane is 32k words further
     uint32_t w[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
-        const int t = 4 * k + tok_lane;
         w[k] = 0;
-        if (t < nvalid) w[k] = ldg_stream32(codes + t * 8 + slab);
+        if (FULL || 4 * k + tok_lane < nvalid) w[k] = ldg_stream32(mine + 32 * k);
     }
     f.a = make_uint4(w[0], w[1], w[2], w[3]);
     f.b = make_uint4(w[4], w[5], w[6], w[7]);
@@ -145,10 +150,9 @@ __device__ __forceinline__ void prefetch_channel64(Prefetch64& f, const uint32_t
     f.d = __ldg(reinterpret_cast<const uint4*>(group_ranges + 64 + slab * 8));
 }
 
-// 32 vectors (d = 64, b = 4) per warp, one per lane; nvalid in 1...32.  `table` is the byte-pair
-// table, `sign` 32 words whose bit 15 / bit 31 say whether element 2p / 2p+1 is negated by the
-// rotation's diagonal.
-template <typename T>
+// 32 vectors (d = 64, b = 4) per warp, one per lane.  `table` is the byte-pair table, `sign` 32
+// words whose bit 15 / bit 31 say whether element 2p / 2p+1 is negated by the rotation's diagonal.
+template <typename T, bool FULL>
 __device__ __forceinline__ void turbo64_decode_warp(const Prefetch64& f, T* __restrict__ out, int nvalid,
                                                     const unsigned char* table, const uint32_t* sign,
                                                     unsigned char* stage, int lane) {
@@ -173,12 +177,14 @@ __device__ __forceinline__ void turbo64_decode_warp(const Prefetch64& f, T* __re
     for (int i = 0; i < 32; ++i) v[i] = mul2(v[i], scale);
     PairStore<T>::row(v, sign, stage + lane * Stage::PITCHB);
     __syncwarp();
-    const int valid_elems = nvalid * 64;
+    // transposed read-out: chunk c = k*32 + lane of the tile's contiguous output
+    const unsigned char* src = stage + (lane / Stage::CPR) * Stage::PITCHB + (lane % Stage::CPR) * 16;
+    uint4* dst = reinterpret_cast<uint4*>(out) + lane;
+    const int valid_chunks = nvalid * Stage::CPR;
 #pragma unroll
     for (int k = 0; k < Stage::CPR; ++k) {
-        const int c = k * 32 + lane;
-        const uint4 q = *reinterpret_cast<const uint4*>(stage + (c / Stage::CPR) * Stage::PITCHB + (c % Stage::CPR) * 16);
-        if (c * Stage::EPC < valid_elems) stg_stream(reinterpret_cast<uint4*>(out) + c, q);
+        const uint4 q = *reinterpret_cast<const uint4*>(src + k * (32 / Stage::CPR) * Stage::PITCHB);
+        if (FULL || k * 32 + lane < valid_chunks) stg_stream(dst + k * 32, q);
     }
     __syncwarp();
 }
@@ -222,9 +228,21 @@ template <> struct Pairs8<__nv_bfloat16> {
     }
 };
 
+// (hi - lo) / 15, correctly rounded, as a multiply by the rounded reciprocal and two fused
+// corrections (q = x*r; q += fma(-15, q, x) * r).  Checked against the IEEE quotient for every
+// non-negative float32 x, subnormals included; the result is then forced to 1 when it is 0,
+// as the specification does for a constant channel.
+__device__ __forceinline__ float step15(float lo, float hi) {
+    const float x = hi - lo;
+    const float r = 1.0f / 15.0f;
+    const float q = x * r;
+    const float s = __fmaf_rn(__fmaf_rn(-15.0f, q, x), r, q);
+    return s == 0.0f ? 1.0f : s;
+}
+
 // 32 tokens (d = 64, b = 4, all inside one group) per warp: lane = (token lane 0..3, slab 0..7).
 // code * step + lo with one rounding per operation.
-template <typename T>
+template <typename T, bool FULL>
 __device__ __forceinline__ void channel64_decode_warp(const Prefetch64& f, T* __restrict__ out, int nvalid, int lane) {
     const int slab = lane & 7, tok_lane = lane >> 3;
     const uint32_t w[8] = {f.a.x, f.a.y, f.a.z, f.a.w, f.b.x, f.b.y, f.b.z, f.b.w};
@@ -234,22 +252,22 @@ __device__ __forceinline__ void channel64_decode_warp(const Prefetch64& f, T* __
     for (int i = 0; i < 4; ++i) {
         lo[i] = __half22float2(*reinterpret_cast<const __half2*>(&lo16[i]));
         const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&hi16[i]));
-        step[i] = make_float2(step_of(lo[i].x, hi.x, 15.0f), step_of(lo[i].y, hi.y, 15.0f));
+        step[i] = make_float2(step15(lo[i].x, hi.x), step15(lo[i].y, hi.y));
     }
+    T* mine = out + tok_lane * 64 + slab * 8;                // token 4k + tok_lane is 256k elements further
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
-        const int t = 4 * k + tok_lane;
         float2 v[4];
         codes8_to_pairs(w[k], v);
 #pragma unroll
         for (int i = 0; i < 4; ++i) v[i] = mul2_then_add(v[i], step[i], lo[i]);
-        if (t < nvalid) Pairs8<T>::store(out + t * 64 + slab * 8, v);
+        if (FULL || 4 * k + tok_lane < nvalid) Pairs8<T>::store(mine + 256 * k, v);
     }
 }
 
 struct Plane64 {
     int kind;                 // 0 = TurboQuant, 1 = per-channel
-    int group_size;           // per-channel planes: multiple of 32
+    int group_tiles;          // per-channel planes: group size / 32
     uint32_t neg_lo, neg_hi;  // rotation diagonal: bit i set when element i (resp. 32 + i) is negated
     const unsigned char* codes;
     int64_t codes_seg_stride;
@@ -261,15 +279,20 @@ struct Plane64 {
 
 struct Cache64Params {
     int n_planes;
-    int tiles_per_seg;        // warp tiles (32 tokens) per segment
-    int64_t tokens;
-    int64_t total_tiles;      // segments * tiles_per_seg
+    int segments;
+    int full_tiles;           // whole 32-token tiles per segment (tokens / 32)
+    int tail;                 // tokens in the partial last tile of every segment (tokens % 32)
     Plane64 plane[4];
     Book16 book;              // TurboQuant centroids for (64, 4)
 };
 
 template <typename T>
 constexpr int cache64_smem_bytes() { return CD_TABLE_BYTES + 4 * 32 * 4 + CD_WARPS * WarpStage<T, 64>::BYTES; }
+
+// A work item: one 32-token tile of one plane of one segment.
+struct Cursor64 {
+    int pl, seg, tile;
+};
 
 // grid = number of SMs (persistent), CD_THREADS threads, cache64_smem_bytes<T>() dynamic shared memory.
 template <typename T>
@@ -298,232 +321,87 @@ cache_decode_d64b4_kernel(const __grid_constant__ Cache64Params p) {
     }
     __syncthreads();
     unsigned char* stage = stage_base + warp * WarpStage<T, 64>::BYTES;
+    const int warp_id = blockIdx.x * CD_WARPS + warp;
+    const int warp_stride = gridDim.x * CD_WARPS;
 
-    // Work items of this warp: (tile, plane) pairs, tiles round-robin over all warps of the grid,
-    // planes innermost.  Item k+1 is fetched before item k is decoded.
-    const int64_t warp_id = (int64_t)blockIdx.x * CD_WARPS + warp;
-    const int64_t warp_stride = (int64_t)gridDim.x * CD_WARPS;
-    if (warp_id >= p.total_tiles) return;
-    const int64_t my_tiles = (p.total_tiles - warp_id + warp_stride - 1) / warp_stride;
-    const int64_t items = my_tiles * p.n_planes;
-
-    struct Item { int pl; int nvalid; int64_t seg, t0; };
-    auto locate = [&](int64_t k) {
-        Item it;
-        const int64_t tile = warp_id + (k / p.n_planes) * warp_stride;
-        it.pl = (int)(k % p.n_planes);
-        it.seg = tile / p.tiles_per_seg;
-        it.t0 = (tile - it.seg * p.tiles_per_seg) * 32;
-        const int64_t left = p.tokens - it.t0;
-        it.nvalid = left < 32 ? (int)left : 32;
-        return it;
-    };
-    auto fetch = [&](const Item& it, Prefetch64& f) {
-        const Plane64& P = p.plane[it.pl];
-        const unsigned char* codes = P.codes + it.seg * P.codes_seg_stride + it.t0 * 32;
-        const unsigned char* side = P.side + it.seg * P.side_seg_stride;
+    // Addresses of an item.  Whole tiles take the FULL (unchecked) paths.
+    auto fetch = [&](const Cursor64& c, Prefetch64& f) {
+        const Plane64& P = p.plane[c.pl];
+        const unsigned char* codes = P.codes + c.seg * P.codes_seg_stride + (int64_t)c.tile * 1024;
+        const unsigned char* side = P.side + c.seg * P.side_seg_stride;
         if (P.kind == 0)
-            prefetch_turbo64(f, reinterpret_cast<const uint4*>(codes), reinterpret_cast<const float*>(side) + it.t0,
-                             it.nvalid, lane);
+            prefetch_turbo64<true>(f, reinterpret_cast<const uint4*>(codes),
+                                   reinterpret_cast<const float*>(side) + c.tile * 32, 32, lane);
         else
-            prefetch_channel64(f, reinterpret_cast<const uint32_t*>(codes),
-                               reinterpret_cast<const __half*>(side) + (it.t0 / P.group_size) * 128, it.nvalid, lane);
+            prefetch_channel64<true>(f, reinterpret_cast<const uint32_t*>(codes),
+                                     reinterpret_cast<const __half*>(side) + (c.tile / P.group_tiles) * 128, 32, lane);
+    };
+    auto decode = [&](const Cursor64& c, const Prefetch64& f) {
+        const Plane64& P = p.plane[c.pl];
+        T* out = reinterpret_cast<T*>(P.out + c.seg * P.out_seg_stride) + (int64_t)c.tile * 2048;
+        if (P.kind == 0)
+            turbo64_decode_warp<T, true>(f, out, 32, table, s_sign + c.pl * 32, stage, lane);
+        else
+            channel64_decode_warp<T, true>(f, out, 32, lane);
+    };
+    // Next item of this warp: planes innermost, then the warp's next tile (round-robin over the grid).
+    auto advance = [&](Cursor64& c) {
+        if (++c.pl < p.n_planes) return true;
+        c.pl = 0;
+        c.tile += warp_stride;
+        if (c.tile >= p.full_tiles) {
+            const int q = c.tile / p.full_tiles;
+            c.seg += q;
+            c.tile -= q * p.full_tiles;
+        }
+        return c.seg < p.segments;
     };
 
-    Item cur = locate(0);
-    Prefetch64 fcur;
-    fetch(cur, fcur);
+    // ---- whole tiles, software pipelined with two register buffers used alternately
+    if (p.full_tiles > 0) {
+        Cursor64 cur;
+        cur.pl = 0;
+        cur.seg = warp_id / p.full_tiles;
+        cur.tile = warp_id - cur.seg * p.full_tiles;
+        if (cur.seg < p.segments) {
+            Prefetch64 fa, fb;
+            fetch(cur, fa);
 #pragma unroll 1
-    for (int64_t k = 0; k < items; ++k) {
-        Item nxt = cur;
-        Prefetch64 fnxt = fcur;
-        if (k + 1 < items) {
-            nxt = locate(k + 1);
-            fetch(nxt, fnxt);
-        }
-        const Plane64& P = p.plane[cur.pl];
-        T* out = reinterpret_cast<T*>(P.out + cur.seg * P.out_seg_stride) + cur.t0 * 64;
-        if (P.kind == 0)
-            turbo64_decode_warp<T>(fcur, out, cur.nvalid, table, s_sign + cur.pl * 32, stage, lane);
-        else
-            channel64_decode_warp<T>(fcur, out, cur.nvalid, lane);
-        cur = nxt;
-        fcur = fnxt;
-    }
-}
-
-// ------------------------------------------------------------------------------------------
-// Appending tokens to a cache.  The work is tiny (one vector per segment and plane per step),
-// so these kernels favour one launch for all segments over throughput: one CTA per vector,
-// one thread per coordinate, Walsh-Hadamard stages through shared memory.  The arithmetic
-// (operation order included) is that of the bulk encoders, so an appended token has the
-// same codes as the same token encoded in bulk.
-// ------------------------------------------------------------------------------------------
-struct Book256 { float c[256]; };
-
-// blockDim.x = max(dim, 32) threads; grid = (n_new, segments).
-// kind 0 = TurboQuant, 1 = PolarQuant variant.
-template <typename T>
-__global__ void __launch_bounds__(1024)
-cache_append_vector_kernel(const unsigned char* __restrict__ in, int64_t in_seg_stride,
-                           unsigned char* __restrict__ codes, int64_t codes_seg_stride,
-                           unsigned char* __restrict__ side, int64_t side_seg_stride, int64_t first_token,
-                           int dim, int bits, int kind, uint32_t seed, float rs, const Book256 book) {
-    __shared__ float s[1024];
-    __shared__ float s_edges[256];
-    __shared__ uint32_t s_codes[1024];
-    __shared__ float s_red[32];
-    const int tid = threadIdx.x;
-    const int64_t seg = blockIdx.y, j = blockIdx.x, tok = first_token + j;
-    const int wpv = words_per_vector(dim, bits);
-    const T* x_in = reinterpret_cast<const T*>(in + seg * in_seg_stride) + j * dim;
-    uint32_t* out_codes = reinterpret_cast<uint32_t*>(codes + seg * codes_seg_stride) + tok * wpv;
-    float* out_scale = reinterpret_cast<float*>(side + seg * side_seg_stride) + tok;
-    const bool active = tid < dim;
-    const float x = active ? Elem<T>::to_f32(x_in[tid]) : 0.0f;
-    const float sign = (pcg_hash(seed + (uint32_t)tid) & 1u) ? 1.0f : -1.0f;
-    if (kind == 0)
-        for (int k = tid; k < (1 << bits) - 1; k += blockDim.x) s_edges[k] = 0.5f * (book.c[k] + book.c[k + 1]);
-
-    float norm = 0.0f, inv = 1.0f;
-    if (kind == 0) {
-        // balanced adjacent-pair tree, as tree_sum_regs + lanes_sum
-        if (active) s[tid] = x * x;
-        __syncthreads();
-        for (int n = dim; n > 1; n >>= 1) {
-            float t = 0.0f;
-            if (tid < n / 2) t = s[2 * tid] + s[2 * tid + 1];
-            __syncthreads();
-            if (tid < n / 2) s[tid] = t;
-            __syncthreads();
-        }
-        norm = sqrtf(s[0]);
-        inv = norm > 0.0f ? 1.0f / norm : 0.0f;
-        __syncthreads();
-    }
-    if (active) s[tid] = kind == 0 ? sign * x * inv : sign * x;
-    __syncthreads();
-    for (int len = 1; len < dim; len <<= 1) {
-        float v = 0.0f;
-        if (active) {
-            const float lo = s[tid & ~len], hi = s[tid | len];
-            v = (tid & len) ? (lo - hi) : (lo + hi);
-        }
-        __syncthreads();
-        if (active) s[tid] = v;
-        __syncthreads();
-    }
-    uint32_t code = 0;
-    float scale = norm;
-    if (kind == 0) {
-        if (active) {
-            const float u = s[tid] * rs;
-            for (int step = (1 << bits) >> 1; step > 0; step >>= 1) {
-                const uint32_t cand = code + step;
-                if (u > s_edges[cand - 1]) code = cand;
+            while (true) {
+                Cursor64 nxt = cur;
+                bool more = advance(nxt);
+                if (more) fetch(nxt, fb);
+                decode(cur, fa);
+                if (!more) break;
+                cur = nxt;
+                more = advance(nxt);
+                if (more) fetch(nxt, fa);
+                decode(cur, fb);
+                if (!more) break;
+                cur = nxt;
             }
         }
-    } else {
-        float a = 0.0f, c = 0.0f, r = 0.0f;
-        if (active) {
-            a = s[tid & ~1] * rs;
-            c = s[(tid & ~1) + 1] * rs;
-            const float aa = a * a, cc = c * c;
-            r = sqrtf(aa + cc);
-        }
-        float m = r;
-        for (int k = 16; k > 0; k >>= 1) m = fmaxf(m, __shfl_xor_sync(FULL, m, k));
-        if ((tid & 31) == 0) s_red[tid >> 5] = m;
-        __syncthreads();
-        float rmax = 0.0f;
-        for (int k = 0; k < (int)((blockDim.x + 31) >> 5); ++k) rmax = fmaxf(rmax, s_red[k]);
-        const float safe = rmax > 0.0f ? rmax : 1.0f;
-        const float RL = (float)((1u << bits) - 1u), NB = (float)(1u << bits);
-        if (active) {
-            if ((tid & 1) == 0) {
-                float q = floorf(r / safe * RL + 0.5f);
-                q = fminf(fmaxf(q, 0.0f), RL);
-                code = (uint32_t)q;
+    }
+
+    // ---- the partial last tile of every segment (at most one per segment and plane)
+    if (p.tail > 0) {
+        for (int item = warp_id; item < p.segments * p.n_planes; item += warp_stride) {
+            const int seg = item / p.n_planes, pl = item - seg * p.n_planes;
+            const Plane64& P = p.plane[pl];
+            const unsigned char* codes = P.codes + seg * P.codes_seg_stride + (int64_t)p.full_tiles * 1024;
+            const unsigned char* side = P.side + seg * P.side_seg_stride;
+            T* out = reinterpret_cast<T*>(P.out + seg * P.out_seg_stride) + (int64_t)p.full_tiles * 2048;
+            Prefetch64 f;
+            if (P.kind == 0) {
+                prefetch_turbo64<false>(f, reinterpret_cast<const uint4*>(codes),
+                                        reinterpret_cast<const float*>(side) + p.full_tiles * 32, p.tail, lane);
+                turbo64_decode_warp<T, false>(f, out, p.tail, table, s_sign + pl * 32, stage, lane);
             } else {
-                float theta = atan2f(c, a);
-                if (theta < 0.0f) theta += TWO_PI_F;
-                code = (uint32_t)floorf(theta / TWO_PI_F * NB + 0.5f) & ((1u << bits) - 1u);
+                prefetch_channel64<false>(f, reinterpret_cast<const uint32_t*>(codes),
+                                          reinterpret_cast<const __half*>(side) + (p.full_tiles / P.group_tiles) * 128,
+                                          p.tail, lane);
+                channel64_decode_warp<T, false>(f, out, p.tail, lane);
             }
-        }
-        scale = rmax;
-    }
-    if (active) s_codes[tid] = code;
-    __syncthreads();
-    for (int w = tid; w < wpv; w += blockDim.x) {
-        const int bit0 = w * 32;
-        const int i0 = bit0 / bits;
-        int i1 = (bit0 + 31) / bits;
-        if (i1 > dim - 1) i1 = dim - 1;
-        uint32_t word = 0;
-        for (int i = i0; i <= i1; ++i) {
-            const int shift = i * bits - bit0;
-            word |= shift >= 0 ? (s_codes[i] << shift) : (s_codes[i] >> (-shift));
-        }
-        out_codes[w] = word;
-    }
-    if (tid == 0) *out_scale = scale;
-}
-
-// Per-channel plane: the newest, still growing group of every segment is kept in float32 in
-// `residual` ([segments][group_size][dim]) and re-encoded from there each time tokens arrive,
-// so the stored codes always equal a bulk encode of the tokens seen so far.
-// grid = segments, 256 threads.  All new tokens must fall into one group.
-template <typename T>
-__global__ void __launch_bounds__(256)
-cache_append_channel_kernel(const unsigned char* __restrict__ in, int64_t in_seg_stride, float* __restrict__ residual,
-                            int64_t residual_seg_elems, unsigned char* __restrict__ codes, int64_t codes_seg_stride,
-                            unsigned char* __restrict__ ranges, int64_t ranges_seg_stride, int64_t first_token,
-                            int n_new, int dim, int bits, int group_size) {
-    __shared__ float s_lo[1024], s_step[1024];
-    const int64_t seg = blockIdx.x;
-    const int64_t g = first_token / group_size;
-    const int pos = (int)(first_token - g * group_size);
-    const int n = pos + n_new;
-    const float levels = (float)((1u << bits) - 1u);
-    const int wpv = words_per_vector(dim, bits);
-    const T* x_in = reinterpret_cast<const T*>(in + seg * in_seg_stride);
-    float* res = residual + seg * residual_seg_elems;
-    uint32_t* out_codes = reinterpret_cast<uint32_t*>(codes + seg * codes_seg_stride) + g * group_size * wpv;
-    __half* out_ranges = reinterpret_cast<__half*>(ranges + seg * ranges_seg_stride) + g * 2 * dim;
-
-    for (int e = threadIdx.x; e < n_new * dim; e += blockDim.x) res[pos * dim + e] = Elem<T>::to_f32(x_in[e]);
-    __syncthreads();
-
-    for (int ch = threadIdx.x; ch < dim; ch += blockDim.x) {
-        float lo = res[ch], hi = lo;
-        for (int t = 1; t < n; ++t) {
-            const float x = res[t * dim + ch];
-            lo = fminf(lo, x);
-            hi = fmaxf(hi, x);
-        }
-        const __half lo16 = __float2half_rn(lo), hi16 = __float2half_rn(hi);
-        out_ranges[ch] = lo16;
-        out_ranges[dim + ch] = hi16;
-        const float base = __half2float(lo16);
-        s_lo[ch] = base;
-        s_step[ch] = step_of(base, __half2float(hi16), levels);
-    }
-    __syncthreads();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    for (int t = warp; t < n; t += nwarps) {
-        const float* row = res + t * dim;
-        for (int w = lane; w < wpv; w += 32) {
-            const int bit0 = w * 32;
-            const int i0 = bit0 / bits;
-            int i1 = (bit0 + 31) / bits;
-            if (i1 > dim - 1) i1 = dim - 1;
-            uint32_t word = 0;
-            for (int i = i0; i <= i1; ++i) {
-                const uint32_t c = quantise(row[i], s_lo[i], s_step[i], levels);
-                const int shift = i * bits - bit0;
-                word |= shift >= 0 ? (c << shift) : (c >> (-shift));
-            }
-            out_codes[t * wpv + w] = word;
         }
     }
 }

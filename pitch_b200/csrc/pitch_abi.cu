@@ -14,6 +14,7 @@
 #include <mutex>
 #include <string>
 
+#include "append_kernels.cuh"
 #include "cache_kernels.cuh"
 #include "channel_kernels.cuh"
 #include "common.cuh"
@@ -189,7 +190,8 @@ int launch_cache64(const Cache64Params& p, cudaStream_t s) {
             return launch_status(false, "cache_decode (shared memory opt-in)");
         configured[dev] = true;
     }
-    int64_t ctas = ceil_div(p.total_tiles, CD_WARPS);
+    const int64_t work = (int64_t)p.segments * (p.full_tiles > 0 ? p.full_tiles : 1);
+    int64_t ctas = ceil_div(work, CD_WARPS);
     if (ctas > sm_count()) ctas = sm_count();
     cache_decode_d64b4_kernel<T><<<(unsigned)ctas, CD_THREADS, smem, s>>>(p);
     return PITCH_OK;
@@ -217,11 +219,12 @@ int launch_turbo_decode(int dim, uint32_t seed, const void* codes, const void* s
         Cache64Params p;
         memset(&p, 0, sizeof p);
         p.n_planes = 1;
-        p.tiles_per_seg = (int)ceil_div(count, 32);
-        if (ceil_div(count, 32) <= 0x7FFFFFFF) {
-            p.tokens = count;
-            p.total_tiles = p.tiles_per_seg;
+        if (count / 32 <= 0x3FFFFFFF) {
+            p.segments = 1;
+            p.full_tiles = (int)(count / 32);
+            p.tail = (int)(count % 32);
             p.plane[0].kind = 0;
+            p.plane[0].group_tiles = 1;
             p.plane[0].neg_lo = negate_mask32(seed, 0);
             p.plane[0].neg_hi = negate_mask32(seed, 32);
             p.plane[0].codes = static_cast<const unsigned char*>(codes);
@@ -561,6 +564,7 @@ int pitch_enqueue_cache_decode(const pitch_cache_desc* d, void* stream) {
         if (pl.bits != 4) fused = false;
         if (pl.kind == PITCH_PLANE_POLAR) fused = false;
         if (pl.kind == PITCH_PLANE_CHANNEL && pl.group_size % 32 != 0) fused = false;
+        if (d->segments > 0x7FFFFFFF / (d->tokens / 32 + 1)) fused = false;      // 32-bit tile indices in the kernel
     }
     cudaPointerAttributes attr;
     if (cudaPointerGetAttributes(&attr, d->planes[0].out) != cudaSuccess ||
@@ -576,15 +580,15 @@ int pitch_enqueue_cache_decode(const pitch_cache_desc* d, void* stream) {
         Cache64Params p;
         memset(&p, 0, sizeof p);
         p.n_planes = d->n_planes;
-        p.tiles_per_seg = (int)ceil_div(d->tokens, 32);
-        p.tokens = d->tokens;
-        p.total_tiles = d->segments * p.tiles_per_seg;
+        p.segments = (int)d->segments;
+        p.full_tiles = (int)(d->tokens / 32);
+        p.tail = (int)(d->tokens % 32);
         bool need_book = false;
         for (int i = 0; i < d->n_planes; ++i) {
             const pitch_plane& pl = d->planes[i];
             Plane64& q = p.plane[i];
             q.kind = pl.kind == PITCH_PLANE_CHANNEL ? 1 : 0;
-            q.group_size = pl.group_size;
+            q.group_tiles = pl.kind == PITCH_PLANE_CHANNEL ? pl.group_size / 32 : 1;
             q.neg_lo = negate_mask32(pl.seed, 0);
             q.neg_hi = negate_mask32(pl.seed, 32);
             q.codes = static_cast<const unsigned char*>(pl.codes);
@@ -640,7 +644,7 @@ int pitch_enqueue_cache_append(const pitch_cache_desc* d, const pitch_append_src
         if (pl.kind == PITCH_PLANE_CHANNEL) {
             if ((st = check_channel_config(dim, pl.bits, pl.group_size, in_dtype))) return st;
             if (src[i].residual == nullptr) return fail(PITCH_ERR_INVALID_INPUT, "plane %d: residual buffer is null", i);
-            if (src[i].residual_seg_stride < (int64_t)pl.group_size * dim * 4 || (src[i].residual_seg_stride & 3))
+            if (src[i].residual_seg_stride < ((int64_t)pl.group_size + 2) * dim * 4 || (src[i].residual_seg_stride & 3))
                 return fail(PITCH_ERR_INVALID_INPUT, "plane %d: residual segment stride too small", i);
             if (d->tokens % pl.group_size + n_new > pl.group_size)
                 return fail(PITCH_ERR_INVALID_INPUT, "plane %d: new tokens must fall into one group of %d", i, pl.group_size);
@@ -663,37 +667,40 @@ int pitch_enqueue_cache_append(const pitch_cache_desc* d, const pitch_append_src
     }
     DeviceGuard guard(attr.device);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // one launch for every segment and plane; the descriptor (with the codebooks) travels as the kernel parameter
+    static thread_local AppendParams p;
+    p.n_planes = d->n_planes;
+    p.dim = dim;
+    p.n_new = (int)n_new;
+    p.rs = rsqrt_dim(dim);
+    p.first_token = d->tokens;
     for (int i = 0; i < d->n_planes; ++i) {
         const pitch_plane& pl = d->planes[i];
-        const unsigned char* in = static_cast<const unsigned char*>(src[i].input);
-        if (pl.kind == PITCH_PLANE_CHANNEL) {
-            PITCH_DISPATCH_DTYPE(in_dtype, (cache_append_channel_kernel<T><<<(unsigned)d->segments, 256, 0, s>>>(
-                                               in, src[i].input_seg_stride, static_cast<float*>(src[i].residual),
-                                               src[i].residual_seg_stride / 4, static_cast<unsigned char*>(pl.codes),
-                                               pl.codes_seg_stride, static_cast<unsigned char*>(pl.side),
-                                               pl.side_seg_stride, d->tokens, (int)n_new, dim, pl.bits, pl.group_size)));
-        } else {
-            Book256 book;
-            memset(&book, 0, sizeof book);
-            if (pl.kind == PITCH_PLANE_TURBO) {
-                std::lock_guard<std::mutex> guardb(g_books.lock);
-                const int l = log2_exact(dim);
-                if (!g_books.present[l][pl.bits])
-                    return fail(PITCH_ERR_INVALID_INPUT, "no TurboQuant codebook for dim %d, bits %d", dim, pl.bits);
-                memcpy(book.c, g_books.values[l][pl.bits], sizeof(float) << pl.bits);
-            }
-            const dim3 grid((unsigned)n_new, (unsigned)d->segments);
-            const unsigned threads = dim < 32 ? 32 : dim;
-            PITCH_DISPATCH_DTYPE(in_dtype, (cache_append_vector_kernel<T><<<grid, threads, 0, s>>>(
-                                               in, src[i].input_seg_stride, static_cast<unsigned char*>(pl.codes),
-                                               pl.codes_seg_stride, static_cast<unsigned char*>(pl.side),
-                                               pl.side_seg_stride, d->tokens, dim, pl.bits,
-                                               pl.kind == PITCH_PLANE_TURBO ? 0 : 1, pl.seed, rsqrt_dim(dim), book)));
+        AppendPlane& q = p.plane[i];
+        q.kind = pl.kind == PITCH_PLANE_CHANNEL ? 2 : (pl.kind == PITCH_PLANE_TURBO ? 0 : 1);
+        q.bits = pl.bits;
+        q.group_size = pl.group_size;
+        q.seed = pl.seed;
+        q.in = static_cast<const unsigned char*>(src[i].input);
+        q.in_seg_stride = src[i].input_seg_stride;
+        q.codes = static_cast<unsigned char*>(pl.codes);
+        q.codes_seg_stride = pl.codes_seg_stride;
+        q.side = static_cast<unsigned char*>(pl.side);
+        q.side_seg_stride = pl.side_seg_stride;
+        q.residual = static_cast<float*>(src[i].residual);
+        q.residual_seg_elems = src[i].residual_seg_stride / 4;
+        if (pl.kind == PITCH_PLANE_TURBO) {
+            std::lock_guard<std::mutex> guardb(g_books.lock);
+            const int l = log2_exact(dim);
+            if (!g_books.present[l][pl.bits])
+                return fail(PITCH_ERR_INVALID_INPUT, "no TurboQuant codebook for dim %d, bits %d", dim, pl.bits);
+            memcpy(p.book[i], g_books.values[l][pl.bits], sizeof(float) << pl.bits);
         }
-        const int st = launch_status(true, "cache_append");
-        if (st) return st;
     }
-    return PITCH_OK;
+    const dim3 grid((unsigned)d->segments, (unsigned)d->n_planes);
+    const unsigned threads = dim < APPEND_MIN_THREADS ? APPEND_MIN_THREADS : dim;
+    PITCH_DISPATCH_DTYPE(in_dtype, (cache_append_kernel<T><<<grid, threads, 0, s>>>(p)));
+    return launch_status(true, "cache_append");
 }
 
 // --------------------------------------------------------------------------------- checksum
