@@ -1,0 +1,154 @@
+"""Throughput of the stand-alone codec kernels at the benchmark configurations' shapes.
+
+    python -m pitch_b200.bench_configs [--only cfg1,cfg2,cfg3,sweep,cfg5] [--reps 50]
+
+Prints one JSON line per measurement: encode vectors/s, decode output GB/s and the fraction of
+the HBM roofline, counting algorithmic bytes (full-precision tensor + packed codes + side
+information, each once).  Inputs are synthetic (seeded, generated on the device).  Working sets
+smaller than the 126 MB L2 are rotated over several distinct buffers so that every launch
+streams from HBM; timing is by CUDA events on the launching stream after warm-up.
+The whole-cache step (configuration 4) is measured by ``bench.py`` at the repository root.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+from pathlib import Path
+
+import torch
+
+from . import ChannelQuantConfig, KVCache, PITCH, QuantConfig
+
+L2_BYTES = 126 << 20
+
+
+def hbm_peak() -> tuple[float, str]:
+    f = Path(__file__).resolve().parent.parent / "MEASURED_PEAKS.json"
+    if f.exists():
+        return float(json.loads(f.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def time_launches(fn, n_sets: int, reps: int) -> float:
+    """Mean seconds per call of fn(i), i cycling over n_sets buffer sets."""
+    for i in range(max(3, n_sets)):
+        fn(i % n_sets)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(reps):
+        fn(i % n_sets)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e-3 / reps
+
+
+def report(name, what, seconds, units, unit_name, nbytes, extra):
+    peak, src = hbm_peak()
+    gbs = nbytes / seconds / 1e9
+    print(json.dumps({"config": name, "op": what, "us_per_launch": round(seconds * 1e6, 2),
+                      f"{unit_name}_per_s": round(units / seconds, 1), "algorithmic_GB_per_s": round(gbs, 1),
+                      "frac_of_hbm_peak": round(gbs / peak, 4), "peak": peak, "peak_source": src,
+                      "frac_of_nominal_8000": round(gbs / 8000.0, 4), **extra}), flush=True)
+
+
+def lognormal_vectors(n, d, seed, dev):
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed)
+    x = torch.randn((n, d), generator=g, device=dev)
+    s = torch.exp(0.5 * torch.randn((n, 1), generator=g, device=dev))
+    return x * s
+
+
+def bench_vector(q, name, method, n, d, bits, reps, out_dtype=torch.float32):
+    cfg = QuantConfig(method, d, bits)
+    dev = q.device
+    in_bytes, code_bytes = n * d * 4, n * cfg.code_stride + n * 4
+    n_sets = max(1, -(-2 * L2_BYTES // (in_bytes + code_bytes)))
+    xs = [lognormal_vectors(n, d, 100 + i, dev) for i in range(n_sets)]
+    codes = [torch.empty(n * cfg.code_stride, dtype=torch.uint8, device=dev) for _ in range(n_sets)]
+    scales = [torch.empty(n, dtype=torch.float32, device=dev) for _ in range(n_sets)]
+    outs = [torch.empty((n, d), dtype=out_dtype, device=dev) for _ in range(n_sets)]
+    t = time_launches(lambda i: q.enqueue_encode(xs[i], codes[i], scales[i], n, cfg), n_sets, reps)
+    extra = {"method": method, "dim": d, "bits": bits, "count": n, "buffer_sets": n_sets}
+    report(name, "encode", t, n, "vectors", in_bytes + code_bytes, extra)
+    t = time_launches(lambda i: q.enqueue_decode(codes[i], scales[i], outs[i], n, cfg), n_sets, reps)
+    out_bytes = n * d * outs[0].element_size()
+    report(name, "decode", t, n, "vectors", out_bytes + code_bytes,
+           {**extra, "out_dtype": str(out_dtype).replace("torch.", ""), "decode_output_GB_per_s": round(out_bytes / t / 1e9, 1)})
+
+
+def bench_channel(q, name, n, d, bits, G, reps):
+    cfg = ChannelQuantConfig(d, bits, G)
+    dev = q.device
+    groups = cfg.group_count(n)
+    in_bytes, code_bytes = n * d * 4, n * cfg.code_stride + groups * cfg.range_stride
+    n_sets = max(1, -(-2 * L2_BYTES // (in_bytes + code_bytes)))
+    xs = []
+    for i in range(n_sets):
+        g = torch.Generator(device=dev)
+        g.manual_seed(200 + i)
+        x = torch.randn((n, d), generator=g, device=dev) + 2.0 * torch.randn((1, d), generator=g, device=dev)
+        x[:, torch.randperm(d, generator=g, device=dev)[:4]] *= 20.0
+        xs.append(x)
+    codes = [torch.empty(n * cfg.code_stride, dtype=torch.uint8, device=dev) for _ in range(n_sets)]
+    ranges = [torch.empty(groups * 2 * d, dtype=torch.float16, device=dev) for _ in range(n_sets)]
+    outs = [torch.empty((n, d), dtype=torch.float32, device=dev) for _ in range(n_sets)]
+    extra = {"method": "perChannel", "dim": d, "bits": bits, "group": G, "count": n, "buffer_sets": n_sets}
+    t = time_launches(lambda i: q.enqueue_per_channel_encode(xs[i], codes[i], ranges[i], n, cfg), n_sets, reps)
+    report(name, "encode", t, n, "tokens", in_bytes + code_bytes, extra)
+    t = time_launches(lambda i: q.enqueue_per_channel_decode(codes[i], ranges[i], outs[i], n, cfg), n_sets, reps)
+    report(name, "decode", t, n, "tokens", in_bytes + code_bytes,
+           {**extra, "out_dtype": "float32", "decode_output_GB_per_s": round(in_bytes / t / 1e9, 1)})
+
+
+def bench_cfg5(q, bits, reps, segments=80, tokens=131072):
+    """One GPU's shard of the Llama-3-70B-shaped cache: 80 of 640 (layer, head) segments."""
+    d = 128
+    cfg = QuantConfig("turboQuant", d, bits)
+    cache = KVCache(segments, d, tokens, cfg, cfg, out_dtype="float16", pitch=q)
+    chunk = 8                                           # prefill a few segments at a time (inputs are 64 MB each)
+    for s0 in range(0, segments, chunk):
+        k = lognormal_vectors(chunk * tokens, d, 500 + s0, q.device).reshape(chunk, tokens, d)
+        v = lognormal_vectors(chunk * tokens, d, 900 + s0, q.device).reshape(chunk, tokens, d)
+        for pl, x in zip(cache.planes, (k, v)):
+            for j in range(chunk):
+                q.enqueue_encode(x[j], pl.codes[s0 + j], pl.side[s0 + j], tokens, cfg)
+        torch.cuda.synchronize()
+        del k, v
+    cache.tokens = tokens
+    t = time_launches(lambda i: cache.decode(), 1, reps)
+    nbytes = cache.stored_bytes() + cache.decoded_bytes()
+    report("cfg5-shard", "whole-cache decode", t, 2 * segments * tokens, "vectors", nbytes,
+           {"method": "turboQuant", "dim": d, "bits": bits, "segments": segments, "tokens": tokens, "out_dtype": "float16",
+            "decode_output_GB_per_s": round(cache.decoded_bytes() / t / 1e9, 1)})
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--only", default="cfg1,cfg2,cfg3,sweep")
+    ap.add_argument("--reps", type=int, default=50)
+    args = ap.parse_args()
+    which = set(args.only.split(","))
+    q = PITCH()
+    if "cfg1" in which:
+        bench_vector(q, "cfg1", "turboQuant", 65536, 64, 4, args.reps)
+        bench_vector(q, "cfg1 x64 batch", "turboQuant", 65536 * 64, 64, 4, max(5, args.reps // 5))
+        bench_vector(q, "cfg1 x64 batch", "turboQuant", 65536 * 64, 64, 4, max(5, args.reps // 5), torch.bfloat16)
+    if "cfg2" in which:
+        bench_channel(q, "cfg2", 32768, 64, 4, 64, args.reps)
+        bench_channel(q, "cfg2 x48 heads", 32768 * 48, 64, 4, 64, max(5, args.reps // 5))
+    if "cfg3" in which:
+        for bits in (3, 4):
+            bench_vector(q, "cfg3", "polarQuant", 1 << 20, 128, bits, max(5, args.reps // 5))
+    if "sweep" in which:
+        for method in ("turboQuant", "polarQuant"):
+            for d in (64, 128, 256, 512, 1024):
+                bench_vector(q, "cfg3 sweep", method, (1 << 27) // d, d, 4, max(5, args.reps // 5))
+    if "cfg5" in which:
+        for bits in (4, 3):
+            bench_cfg5(q, bits, max(3, args.reps // 10))
+
+
+if __name__ == "__main__":
+    main()
