@@ -189,6 +189,32 @@ typedef struct pitch_append_src {
 int pitch_enqueue_cache_append(const pitch_cache_desc* desc, const pitch_append_src* src, int in_dtype,
                                int64_t n_new, void* stream);
 
+/* Same as pitch_enqueue_cache_append for callers that cannot provide the residual buffer.
+ * No counterpart in the reference.  Two kinds of caller are meant: a serving process that hands
+ * all device memory to its own arena at start-up and forbids driver allocations afterwards
+ * (cudaMalloc synchronises the whole device and can fail on a fragmented heap in the middle of
+ * generation), and a host runtime that reaches this library through a foreign-function binding,
+ * owns only the cache buffers it passes in, and has no device allocator with which to size a
+ * residual buffer and keep it alive between steps.  For them the residual of the per-channel
+ * planes lives in a fixed array inside the library image: src[i].residual and
+ * src[i].residual_seg_stride are ignored, everything else is as in pitch_enqueue_cache_append.
+ *   - Limit: the per-channel planes together may need at most PITCH_NOALLOC_RESIDUAL_FLOATS
+ *     floats, counted as segments * (group_size + 2) * dim per plane (8 MiB; the 48-segment,
+ *     dim 64, group 64 cache of the benchmark needs 0.8 MiB).  Larger requests fail with
+ *     PITCH_ERR_INVALID_INPUT.  Every GPU that loads the library holds the array until exit.
+ *   - The call itself allocates nothing: no cudaMalloc, cudaFree or allocating library routine.
+ *     The first call on a GPU looks the array's device address up once (with that GPU current);
+ *     make that first call before starting any stream capture.
+ *   - One array serves every call.  It keeps the newest group of ONE cache per GPU: feed every
+ *     token of that group through this entry point, and switch to another cache only when
+ *     tokens is a multiple of the group size (otherwise PITCH_ERR_CONFIGURATION_MISMATCH).
+ *     Nothing in it needs to start at zero: a group's running range and rows are written before
+ *     they are read.  Two calls that overlap on the GPU (different streams, or two host threads)
+ *     race on the array; keep calls on one GPU stream-ordered. */
+#define PITCH_NOALLOC_RESIDUAL_FLOATS (2 * 1024 * 1024)
+int pitch_enqueue_cache_append_noalloc(const pitch_cache_desc* desc, const pitch_append_src* src, int in_dtype,
+                                       int64_t n_new, void* stream);
+
 /* 64-bit checksum of `bytes` bytes (multiple of 4) at buf: sum over 32-bit words w_i of
  * (w_i + 1) * (2*i + 1) mod 2^64, ADDED onto *result (a device uint64 the caller zeroes).
  * Used to compare shards across GPUs without moving them; no counterpart in the reference. */

@@ -61,6 +61,7 @@ PROTOTYPES = {
     "pitch_enqueue_unpack_codes": (c_int, [c_int, c_int, Buffer, Buffer, c_int64, c_void_p]),
     "pitch_enqueue_cache_decode": (c_int, [POINTER(CacheDesc), c_void_p]),
     "pitch_enqueue_cache_append": (c_int, [POINTER(CacheDesc), POINTER(AppendSrc), c_int, c_int64, c_void_p]),
+    "pitch_enqueue_cache_append_noalloc": (c_int, [POINTER(CacheDesc), POINTER(AppendSrc), c_int, c_int64, c_void_p]),
     "pitch_enqueue_checksum": (c_int, [Buffer, c_int64, c_void_p, c_void_p]),
 }
 

@@ -703,6 +703,94 @@ int pitch_enqueue_cache_append(const pitch_cache_desc* d, const pitch_append_src
     return launch_status(true, "cache_append");
 }
 
+// ------------------------------------------------------------------ append without allocations
+// Residual scratch of pitch_enqueue_cache_append_noalloc: lives in the library image, so every
+// GPU that loads the library holds these bytes until the process exits.
+static __device__ __align__(256) float g_noalloc_residual[PITCH_NOALLOC_RESIDUAL_FLOATS];
+
+namespace {
+struct NoallocDevice {
+    float* base = nullptr;        // device address of g_noalloc_residual on this GPU
+    const void* owner = nullptr;  // codes pointer of plane 0 of the cache whose newest group is held
+    int64_t tokens = -1;          // tokens that cache held after its last call
+};
+std::mutex g_noalloc_lock;
+NoallocDevice g_noalloc[64];
+}  // namespace
+
+int pitch_enqueue_cache_append_noalloc(const pitch_cache_desc* d, const pitch_append_src* src, int in_dtype,
+                                       int64_t n_new, void* stream) {
+    if (d == nullptr || src == nullptr) return fail(PITCH_ERR_INVALID_INPUT, "descriptor is null");
+    if (d->n_planes < 1 || d->n_planes > 4) return fail(PITCH_ERR_INVALID_INPUT, "n_planes %d must be in 1...4", d->n_planes);
+    if (d->segments < 1 || d->tokens < 0) return fail(PITCH_ERR_INVALID_INPUT, "segments must be at least 1 and tokens not negative");
+    if (d->planes[0].codes == nullptr) return fail(PITCH_ERR_INVALID_INPUT, "plane 0: null pointer");
+    // how much of the static array this cache needs, and whether every per-channel plane starts a new group
+    int64_t need = 0;
+    bool fresh_group = true;
+    for (int i = 0; i < d->n_planes; ++i) {
+        const pitch_plane& pl = d->planes[i];
+        if (pl.kind != PITCH_PLANE_CHANNEL) continue;
+        if (pl.group_size < 1 || d->dim < 1) return fail(PITCH_ERR_INVALID_INPUT, "plane %d: bad group size or dimension", i);
+        need += d->segments * ((int64_t)pl.group_size + 2) * d->dim;
+        if (d->tokens % pl.group_size != 0) fresh_group = false;
+    }
+    if (need > (int64_t)PITCH_NOALLOC_RESIDUAL_FLOATS)
+        return fail(PITCH_ERR_INVALID_INPUT,
+                    "the per-channel planes need %lld floats of residual; the built-in buffer holds %lld "
+                    "(segments * (group_size + 2) * dim per plane): use pitch_enqueue_cache_append with your own buffer",
+                    (long long)need, (long long)PITCH_NOALLOC_RESIDUAL_FLOATS);
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, d->planes[0].codes) != cudaSuccess ||
+        (attr.type != cudaMemoryTypeDevice && attr.type != cudaMemoryTypeManaged)) {
+        cudaGetLastError();
+        return fail(PITCH_ERR_INVALID_INPUT, "plane 0: codes is not device memory");
+    }
+    const int dev = attr.device;
+    if (dev < 0 || dev >= 64) return fail(PITCH_ERR_DEVICE_NOT_SUPPORTED, "device ordinal %d is out of range", dev);
+    DeviceGuard guard(dev);
+    float* base;
+    {
+        std::lock_guard<std::mutex> lock(g_noalloc_lock);
+        NoallocDevice& nd = g_noalloc[dev];
+        if (nd.base == nullptr) {
+            // once per GPU, with that GPU current: the array's name is only a host-side handle
+            float* ptr = nullptr;
+            const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_residual);
+            if (e != cudaSuccess || ptr == nullptr) {
+                cudaGetLastError();
+                return fail(PITCH_ERR_KERNEL_UNAVAILABLE, "cannot locate the built-in residual buffer on GPU %d: %s", dev,
+                            cudaGetErrorString(e));
+            }
+            nd.base = ptr;
+        }
+        if (!fresh_group && (nd.owner != d->planes[0].codes || nd.tokens != d->tokens))
+            return fail(PITCH_ERR_CONFIGURATION_MISMATCH,
+                        "the built-in residual buffer does not hold the newest group of this cache at %lld tokens "
+                        "(it serves one cache at a time; switch caches only on a group boundary)", (long long)d->tokens);
+        base = nd.base;
+    }
+    pitch_append_src mine[4];
+    int64_t at_float = 0;
+    for (int i = 0; i < d->n_planes; ++i) {
+        mine[i] = src[i];
+        mine[i].residual = nullptr;
+        mine[i].residual_seg_stride = 0;
+        if (d->planes[i].kind == PITCH_PLANE_CHANNEL) {
+            const int64_t seg_floats = ((int64_t)d->planes[i].group_size + 2) * d->dim;
+            mine[i].residual = base + at_float;
+            mine[i].residual_seg_stride = seg_floats * 4;
+            at_float += d->segments * seg_floats;
+        }
+    }
+    const int st = pitch_enqueue_cache_append(d, mine, in_dtype, n_new, stream);
+    if (st == PITCH_OK) {
+        std::lock_guard<std::mutex> lock(g_noalloc_lock);
+        g_noalloc[dev].owner = d->planes[0].codes;
+        g_noalloc[dev].tokens = d->tokens + n_new;
+    }
+    return st;
+}
+
 // --------------------------------------------------------------------------------- checksum
 int pitch_enqueue_checksum(pitch_buffer buf, int64_t bytes, uint64_t* result_device, void* stream) {
     if (bytes < 0 || (bytes & 3)) return fail(PITCH_ERR_INVALID_INPUT, "bytes %lld must be a non-negative multiple of 4", (long long)bytes);
