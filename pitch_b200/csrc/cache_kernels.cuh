@@ -207,22 +207,38 @@ __device__ __forceinline__ void codes8_to_pairs(uint32_t w, float2 (&f)[4]) {
 
 template <typename T> struct Pairs8;   // 4 float2 -> 8 elements of T, stored as one or two 16-byte pieces
 template <> struct Pairs8<float> {
-    static __device__ __forceinline__ void store(float* p, const float2 (&v)[4]) {
-        stg_stream(reinterpret_cast<uint4*>(p), make_uint4(__float_as_uint(v[0].x), __float_as_uint(v[0].y),
-                                                           __float_as_uint(v[1].x), __float_as_uint(v[1].y)));
-        stg_stream(reinterpret_cast<uint4*>(p) + 1, make_uint4(__float_as_uint(v[2].x), __float_as_uint(v[2].y),
-                                                               __float_as_uint(v[3].x), __float_as_uint(v[3].y)));
+    // A lane's 8 floats are 32 bytes.  Adjacent lanes (slabs 2j, 2j+1) swap 16-byte halves first, so
+    // that each store instruction fills whole 32-byte sectors (lane pair -> 32 contiguous bytes)
+    // instead of half of every sector.  Must be called by all lanes of the warp.
+    static __device__ __forceinline__ void store(float* p, const float2 (&v)[4], bool write = true) {
+        const bool odd = threadIdx.x & 1;
+        // even lane gives away its second half, odd lane its first half
+        const float2 g0 = odd ? v[0] : v[2], g1 = odd ? v[1] : v[3];
+        float2 r0, r1;
+        r0.x = __shfl_xor_sync(FULL, g0.x, 1); r0.y = __shfl_xor_sync(FULL, g0.y, 1);
+        r1.x = __shfl_xor_sync(FULL, g1.x, 1); r1.y = __shfl_xor_sync(FULL, g1.y, 1);
+        // even lane: own first half at +0, partner's first half at +32 (partner's slab base is +32 bytes)
+        // odd lane: partner's second half at partner's +16, own second half at own +16
+        const float2 a0 = odd ? r0 : v[0], a1 = odd ? r1 : v[1];      // goes to the lower 32-byte sector of the pair
+        const float2 b0 = odd ? v[2] : r0, b1 = odd ? v[3] : r1;      // goes to the upper 32-byte sector of the pair
+        float* pair_base = p - (odd ? 8 : 0);                         // first float of the even lane's slab
+        if (write) {
+            stg_stream(reinterpret_cast<uint4*>(pair_base) + (odd ? 1 : 0),
+                       make_uint4(__float_as_uint(a0.x), __float_as_uint(a0.y), __float_as_uint(a1.x), __float_as_uint(a1.y)));
+            stg_stream(reinterpret_cast<uint4*>(pair_base) + (odd ? 3 : 2),
+                       make_uint4(__float_as_uint(b0.x), __float_as_uint(b0.y), __float_as_uint(b1.x), __float_as_uint(b1.y)));
+        }
     }
 };
 template <> struct Pairs8<__half> {
-    static __device__ __forceinline__ void store(__half* p, const float2 (&v)[4]) {
-        stg_stream(reinterpret_cast<uint4*>(p), make_uint4(PairStore<__half>::cvt(v[0]), PairStore<__half>::cvt(v[1]),
+    static __device__ __forceinline__ void store(__half* p, const float2 (&v)[4], bool write = true) {
+        if (write) stg_stream(reinterpret_cast<uint4*>(p), make_uint4(PairStore<__half>::cvt(v[0]), PairStore<__half>::cvt(v[1]),
                                                            PairStore<__half>::cvt(v[2]), PairStore<__half>::cvt(v[3])));
     }
 };
 template <> struct Pairs8<__nv_bfloat16> {
-    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float2 (&v)[4]) {
-        stg_stream(reinterpret_cast<uint4*>(p),
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float2 (&v)[4], bool write = true) {
+        if (write) stg_stream(reinterpret_cast<uint4*>(p),
                    make_uint4(PairStore<__nv_bfloat16>::cvt(v[0]), PairStore<__nv_bfloat16>::cvt(v[1]),
                               PairStore<__nv_bfloat16>::cvt(v[2]), PairStore<__nv_bfloat16>::cvt(v[3])));
     }
@@ -261,7 +277,7 @@ __device__ __forceinline__ void channel64_decode_warp(const Prefetch64& f, T* __
         codes8_to_pairs(w[k], v);
 #pragma unroll
         for (int i = 0; i < 4; ++i) v[i] = mul2_then_add(v[i], step[i], lo[i]);
-        if (FULL || 4 * k + tok_lane < nvalid) Pairs8<T>::store(mine + 256 * k, v);
+        Pairs8<T>::store(mine + 256 * k, v, FULL || 4 * k + tok_lane < nvalid);
     }
 }
 
@@ -321,7 +337,9 @@ cache_decode_d64b4_kernel(const __grid_constant__ Cache64Params p) {
     }
     __syncthreads();
     unsigned char* stage = stage_base + warp * WarpStage<T, 64>::BYTES;
-    const int warp_id = blockIdx.x * CD_WARPS + warp;
+    // warp w of CTA c is worker w * gridDim + c: when the tile count is not a multiple of the worker
+    // count, the workers that take one tile more are spread evenly over the SMs
+    const int warp_id = warp * gridDim.x + blockIdx.x;
     const int warp_stride = gridDim.x * CD_WARPS;
 
     // Addresses of an item.  Whole tiles take the FULL (unchecked) paths.

@@ -451,6 +451,23 @@ int pitch_enqueue_channel_decode(int dim, int bits, int group_size, int dtype, p
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool slab = slab_ok(dim, bits) && aligned16(at(output)) && aligned16(at(ranges)) &&
                       (reinterpret_cast<uintptr_t>(at(codes)) % (bits == 8 ? 8 : 4)) == 0;
+    if (slab && dim == 64 && bits == 4 && group_size % 32 == 0 && aligned16(at(codes)) && count / 32 <= 0x3FFFFFFF) {
+        // the persistent whole-cache kernel with a single per-channel plane
+        Cache64Params p;
+        memset(&p, 0, sizeof p);
+        p.n_planes = 1;
+        p.segments = 1;
+        p.full_tiles = (int)(count / 32);
+        p.tail = (int)(count % 32);
+        p.plane[0].kind = 1;
+        p.plane[0].group_tiles = group_size / 32;
+        p.plane[0].codes = at(codes);
+        p.plane[0].side = at(ranges);
+        p.plane[0].out = at(output);
+        PITCH_DISPATCH_DTYPE(dtype, st = (launch_cache64<T>(p, s)));
+        if (st) return st;
+        return launch_status(false, "channel_decode");
+    }
     if (slab) {
         const int l2 = log2_exact(dim / 8);
         const int chunks = (int)ceil_div(group_size, CH_CHUNK);
