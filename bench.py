@@ -296,18 +296,25 @@ def run_ours(args) -> None:
         cache.decode()
     barrier()
     bytes_total = 0
+    # The decode launch is timed on its own in every 8th step only: an event between the append and
+    # the decode keeps the decode from starting its prologue under the append (programmatic
+    # dependent launch), which the other steps are allowed to do.
+    sampled = [i for i in range(args.steps) if i % 8 == 0]
     for i in range(args.steps):
-        ev[i][0].record(stream)
+        if i == 0:
+            ev[0][0].record(stream)
         cache.append(new_k[args.warmup + i], new_v[args.warmup + i])
-        ev[i][1].record(stream)
+        if i % 8 == 0:
+            ev[i][1].record(stream)
         cache.decode()
-        ev[i][2].record(stream)
+        if i % 8 == 0 or i == args.steps - 1:
+            ev[i][2].record(stream)
         rd, wr = step_bytes(segments, cache.tokens)
         bytes_total += rd + wr
     barrier()
     assert cache.tokens == TOKENS
     step_ms = ev[0][0].elapsed_time(ev[-1][2]) / args.steps
-    decode_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
+    decode_ms = sum(ev[i][1].elapsed_time(ev[i][2]) for i in sampled) / len(sampled)
     sums = cache.checksums()
 
     # ---- end to end through the public API with host buffers: every step the new token comes from
@@ -385,7 +392,7 @@ def run_ours(args) -> None:
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "traffic": traffic, "peak_source": peak_src,
                          "frac_of_nominal_8000": round(achieved / 8000.0, 4), "kernel": "cache_decode_d64b4_kernel",
-                         "kernel_ms": round(decode_ms, 5)},
+                         "kernel_ms": round(decode_ms, 5), "kernel_launches_timed": len(sampled)},
             "e2e": None if not e2e_steps else {
                 "value": round(e2e_bytes / e2e_steps * n_gpus / (e2e_ms * 1e-3) / 1e9, 3), "unit": "GB/s",
                 "h2d_bytes_per_step": int(2 * segments * DIM * 4), "d2h_bytes_per_step": int(d2h),

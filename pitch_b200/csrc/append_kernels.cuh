@@ -201,6 +201,12 @@ cache_append_kernel(const __grid_constant__ AppendParams p) {
     __shared__ float s_b[1024];        // vector: codes (as words) | per-channel: step
     __shared__ float s_edges[256];
     __shared__ float s_red[32];
+    // Programmatic dependent launch on both sides: wait for the previous kernel of the stream (the
+    // decode of the previous step reads the codes this grid rewrites), then let the next kernel (the
+    // decode of this step) start its prologue; it still waits for this grid to finish before it
+    // reads what is written here.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
     const int64_t seg = blockIdx.x;
     const AppendPlane& P = p.plane[blockIdx.y];
     const int dim = p.dim;

@@ -336,6 +336,10 @@ cache_decode_d64b4_kernel(const __grid_constant__ Cache64Params p) {
         }
     }
     __syncthreads();
+    // Everything above touched only kernel parameters and shared memory.  Under programmatic
+    // dependent launch this grid may have started before the previous kernel of the stream ended:
+    // wait for it (and for its memory to be visible) before reading the cache.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     unsigned char* stage = stage_base + warp * WarpStage<T, 64>::BYTES;
     // warp w of CTA c is worker w * gridDim + c: when the tile count is not a multiple of the worker
     // count, the workers that take one tile more are spread evenly over the SMs

@@ -193,7 +193,20 @@ int launch_cache64(const Cache64Params& p, cudaStream_t s) {
     const int64_t work = (int64_t)p.segments * (p.full_tiles > 0 ? p.full_tiles : 1);
     int64_t ctas = ceil_div(work, CD_WARPS);
     if (ctas > sm_count()) ctas = sm_count();
-    cache_decode_d64b4_kernel<T><<<(unsigned)ctas, CD_THREADS, smem, s>>>(p);
+    // Programmatic dependent launch: the kernel may start while the previous kernel of the stream
+    // (typically the append of the same step) is still running; it builds its lookup table, then
+    // waits for that kernel to complete before it reads any cache memory.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)ctas);
+    cfg.blockDim = dim3(CD_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, cache_decode_d64b4_kernel<T>, p);
     return PITCH_OK;
 }
 
@@ -716,7 +729,18 @@ int pitch_enqueue_cache_append(const pitch_cache_desc* d, const pitch_append_src
     }
     const dim3 grid((unsigned)d->segments, (unsigned)d->n_planes);
     const unsigned threads = dim < APPEND_MIN_THREADS ? APPEND_MIN_THREADS : dim;
-    PITCH_DISPATCH_DTYPE(in_dtype, (cache_append_kernel<T><<<grid, threads, 0, s>>>(p)));
+    // programmatic dependent launch: the grid may be scheduled while the previous kernel of the stream
+    // drains; it waits for that kernel before it touches memory (first statement of the kernel)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(threads);
+    cfg.stream = s;
+    cudaLaunchAttribute pdl[1];
+    pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    pdl[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = pdl;
+    cfg.numAttrs = 1;
+    PITCH_DISPATCH_DTYPE(in_dtype, (cudaLaunchKernelEx(&cfg, cache_append_kernel<T>, p)));
     return launch_status(true, "cache_append");
 }
 
