@@ -1,24 +1,27 @@
-// Whole-cache decode for head dimension 64 at 4 bits: the per-step bottleneck of a
-// compressed KV cache (all tokens of every layer and KV head are decoded each step).
+// Whole-cache decode for head dimensions 64 and 128 at 3 or 4 bits: the per-step bottleneck
+// of a compressed KV cache (all tokens of every layer and KV head are decoded each step).
 //
 // One persistent launch covers every plane (K, V) and every segment (layer x KV head): one CTA
-// of 16 warps per SM; a warp takes tiles of 32 consecutive tokens of one segment round-robin and
-// decodes that tile for every plane before moving on.  Per token the kernel reads 32 code bytes
-// plus 4 bytes of side information and writes 64 elements, so it is bound by HBM traffic as
-// long as the instruction count per token stays low; the two paths are built around that:
+// of 16 warps per SM; a warp takes work items round-robin - an item is 2048 consecutive
+// coordinates of one plane of one segment (32 tokens at dim 64, 16 at dim 128) - and the loads
+// of the next item are in flight while the current one is decoded.  Per token the kernel reads
+// dim*bits/8 code bytes plus 4 bytes of side information and writes dim elements, so it is bound
+// by HBM traffic as long as the instruction count per token stays low; the two paths are built
+// around that:
 //
-//   * TurboQuant plane - one vector per lane.  Two 128-bit loads bring the lane's 32 code
-//     bytes.  Each byte holds two codes (a, b); a 256-entry table in shared memory maps the byte
-//     to (c[a] + c[b], c[a] - c[b]), i.e. centroid lookup and the first Walsh-Hadamard stage in
-//     one 64-bit load.  The table is replicated over 32 lane slots (entry e, slot l at byte
-//     e*256 + l*8), so a lookup is bank-conflict free for any codes and its address is a single
-//     byte permute of the code word.  The remaining five stages run on float2 pairs with packed
-//     fp32x2 instructions, the result is scaled, rounded, sign-flipped as packed words, and
-//     leaves through a padded warp-private shared tile so that every global store instruction
-//     writes 512 contiguous bytes per warp.
-//   * per-channel plane - a lane owns 8 channels ("slab") of 4 of the 32 tokens per step; codes
-//     become floats by byte permutes into the mantissa of 2^23; loads are 4 bytes and stores 16
-//     bytes per lane, both contiguous across the warp.
+//   * TurboQuant plane - a lane owns 64 consecutive coordinates (a whole vector at dim 64, half
+//     of one at dim 128).  Each pair of adjacent codes (a, b) - one byte at 4 bits, a 6-bit field
+//     at 3 bits - indexes a table in shared memory that holds (c[a] + c[b], c[a] - c[b]), i.e.
+//     centroid lookup and the first Walsh-Hadamard stage in one 64-bit load.  The table is
+//     replicated over 32 lane slots (entry e, slot l at byte e*256 + l*8), so a lookup is
+//     bank-conflict free for any codes and, at 4 bits, its address is a single byte permute of the
+//     code word.  Stages 2...32 run on float2 pairs with packed fp32x2 instructions; at dim 128
+//     the last stage is one exchange between the two lanes of a vector.  The result is scaled,
+//     rounded, sign-flipped as packed words, and leaves through a padded warp-private shared tile
+//     so that every global store instruction writes 512 contiguous bytes per warp.
+//   * per-channel plane (4 bits) - a lane owns 8 channels ("slab") of every 4th (dim 64) or 2nd
+//     (dim 128) token of the item; codes become floats by byte permutes into the mantissa of
+//     2^23; loads are 4 bytes and stores 16 bytes per lane, both contiguous across the warp.
 #pragma once
 
 #include "channel_kernels.cuh"
@@ -30,7 +33,7 @@ constexpr int CD_THREADS = 512;
 constexpr int CD_WARPS = CD_THREADS / 32;
 constexpr int CD_TABLE_BYTES = 256 * 32 * 8;   // byte-pair table: 256 entries x 32 lane slots x float2
 
-struct Book16 { float c[16]; };
+struct Book16 { float c[16]; };     // TurboQuant centroids, 2^bits of them used
 
 // float2 arithmetic on the packed fp32x2 pipe; each component is one IEEE rounding.
 // Caution, measured on sm_100a: a packed multiply whose only use is a packed add is contracted
@@ -105,11 +108,10 @@ template <> struct PairStore<__nv_bfloat16> {
     }
 };
 
-// What one lane needs from global memory to decode its share of a 32-token tile of one plane.
-// Fetched one work item ahead of its use, so the loads of item k+1 are in flight while item k
-// is being decoded.
+// What one lane needs from global memory to decode its share of one work item.  Fetched one
+// item ahead of its use, so the loads of item k+1 are in flight while item k is being decoded.
 struct Prefetch64 {
-    uint4 a, b;   // TurboQuant: the lane's 32 code bytes.  Per-channel: code words of tokens 4k + (lane >> 3), k = 0..7
+    uint4 a, b;   // TurboQuant: the lane's code bytes (32 at 4 bits, 24 at 3).  Per-channel: code words of tokens k*TOK_LANES + tok_lane, k = 0..7
     uint4 c, d;   // TurboQuant: c.x = norm bits.  Per-channel: fp16 minima (c) and maxima (d) of the lane's 8 channels
 };
 
@@ -118,69 +120,118 @@ __device__ __forceinline__ uint32_t ldg_stream32(const uint32_t* p) {
     asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
     return v;
 }
+__device__ __forceinline__ uint2 ldg_stream64(const uint2* p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
 
-// FULL: all 32 tokens of the tile exist (no bounds checks); otherwise nvalid in 1...31.
-template <bool FULL>
-__device__ __forceinline__ void prefetch_turbo64(Prefetch64& f, const uint4* __restrict__ codes,
+// Geometry of a work item for head dimension D.
+template <int D> struct Item64 {
+    static constexpr int LPV = D / 64;          // lanes per vector (TurboQuant)
+    static constexpr int TOKENS = 32 / LPV;     // tokens per item
+    static constexpr int SLABS = D / 8;         // 8-channel slabs per token (per-channel)
+    static constexpr int TOK_LANES = 32 / SLABS;
+};
+
+// FULL: all tokens of the item exist (no bounds checks); otherwise nvalid in 1...TOKENS-1.
+// `codes` points at the item's first code byte, `norms` at its first norm.
+template <int D, int BITS, bool FULL>
+__device__ __forceinline__ void prefetch_turbo64(Prefetch64& f, const unsigned char* __restrict__ codes,
                                                  const float* __restrict__ norms, int nvalid, int lane) {
-    if (FULL || lane < nvalid) {
-        f.a = ldg_stream(codes + 2 * lane);
-        f.b = ldg_stream(codes + 2 * lane + 1);
-        f.c.x = ldg_stream32(reinterpret_cast<const uint32_t*>(norms) + lane);
-    } else {
-        f.a = f.b = make_uint4(0, 0, 0, 0);
-        f.c.x = 0;
+    constexpr int LPV = Item64<D>::LPV;
+    f.a = f.b = make_uint4(0, 0, 0, 0);
+    f.c.x = 0;
+    if (FULL || lane / LPV < nvalid) {
+        if (BITS == 4) {
+            f.a = ldg_stream(reinterpret_cast<const uint4*>(codes) + 2 * lane);
+            f.b = ldg_stream(reinterpret_cast<const uint4*>(codes) + 2 * lane + 1);
+        } else {
+            const uint2* q = reinterpret_cast<const uint2*>(codes) + 3 * lane;      // 24 bytes per lane
+            const uint2 q0 = ldg_stream64(q), q1 = ldg_stream64(q + 1), q2 = ldg_stream64(q + 2);
+            f.a = make_uint4(q0.x, q0.y, q1.x, q1.y);
+            f.b = make_uint4(q2.x, q2.y, 0, 0);
+        }
+        f.c.x = ldg_stream32(reinterpret_cast<const uint32_t*>(norms) + lane / LPV);
     }
 }
 
-template <bool FULL>
+template <int D, bool FULL>
 __device__ __forceinline__ void prefetch_channel64(Prefetch64& f, const uint32_t* __restrict__ codes,
                                                    const __half* __restrict__ group_ranges, int nvalid, int lane) {
-    const int slab = lane & 7, tok_lane = lane >> 3;
-    const uint32_t* mine = codes + tok_lane * 8 + slab;      // token 4k + tok_lane is 32k words further
+    constexpr int SLABS = Item64<D>::SLABS, TOK_LANES = Item64<D>::TOK_LANES;
+    const int slab = lane & (SLABS - 1), tok_lane = lane / SLABS;
+    const uint32_t* mine = codes + lane;      // token k*TOK_LANES + tok_lane, slab: word k*32 + lane
     uint32_t w[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
         w[k] = 0;
-        if (FULL || 4 * k + tok_lane < nvalid) w[k] = ldg_stream32(mine + 32 * k);
+        if (FULL || TOK_LANES * k + tok_lane < nvalid) w[k] = ldg_stream32(mine + 32 * k);
     }
     f.a = make_uint4(w[0], w[1], w[2], w[3]);
     f.b = make_uint4(w[4], w[5], w[6], w[7]);
     f.c = __ldg(reinterpret_cast<const uint4*>(group_ranges + slab * 8));
-    f.d = __ldg(reinterpret_cast<const uint4*>(group_ranges + 64 + slab * 8));
+    f.d = __ldg(reinterpret_cast<const uint4*>(group_ranges + D + slab * 8));
 }
 
-// 32 vectors (d = 64, b = 4) per warp, one per lane.  `table` is the byte-pair table, `sign` 32
-// words whose bit 15 / bit 31 say whether element 2p / 2p+1 is negated by the rotation's diagonal.
-template <typename T, bool FULL>
+// Byte offset into the pair table of code pair p (codes 2p, 2p+1 of the lane's 64), lane slot included.
+template <int BITS>
+__device__ __forceinline__ uint32_t pair_offset(const uint32_t (&w)[8], int p, uint32_t slot) {
+    if (BITS == 4) {
+        // byte p of the code words -> (byte << 8) | slot with one permute
+        return __byte_perm(w[p >> 2], slot, 0x5504 | ((p & 3) << 4));
+    } else {
+        const int bit = 6 * p, word = bit >> 5, off = bit & 31;       // 6-bit field, may straddle two words
+        uint32_t x;
+        if (off + 6 <= 32) x = off >= 8 ? (w[word] >> (off - 8)) : (w[word] << (8 - off));
+        else x = __funnelshift_r(w[word], w[word + 1], off - 8);
+        return (x & 0x3F00u) | slot;
+    }
+}
+
+// 64 coordinates per lane (BITS-bit codes): a whole vector at D = 64, half of one at D = 128.
+// `table` is the pair table, `sign` 32 words for this lane's 64 coordinates whose bit 15 / bit 31 say
+// whether coordinate 2p / 2p+1 is negated by the rotation's diagonal.  `out` points at the item's
+// first output element.
+template <typename T, int D, int BITS, bool FULL>
 __device__ __forceinline__ void turbo64_decode_warp(const Prefetch64& f, T* __restrict__ out, int nvalid,
                                                     const unsigned char* table, const uint32_t* sign,
-                                                    unsigned char* stage, int lane) {
+                                                    unsigned char* stage, int lane, float rs) {
     typedef WarpStage<T, 64> Stage;
     const uint32_t w[8] = {f.a.x, f.a.y, f.a.z, f.a.w, f.b.x, f.b.y, f.b.z, f.b.w};
     const float norm = __uint_as_float(f.c.x);
     const uint32_t slot = (uint32_t)lane * 8u;
     float2 v[32];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        // byte k of the word -> table offset (byte << 8) | slot, one permute each
-        v[4 * j + 0] = *reinterpret_cast<const float2*>(table + __byte_perm(w[j], slot, 0x5504));
-        v[4 * j + 1] = *reinterpret_cast<const float2*>(table + __byte_perm(w[j], slot, 0x5514));
-        v[4 * j + 2] = *reinterpret_cast<const float2*>(table + __byte_perm(w[j], slot, 0x5524));
-        v[4 * j + 3] = *reinterpret_cast<const float2*>(table + __byte_perm(w[j], slot, 0x5534));
-    }
+    for (int p = 0; p < 32; ++p) v[p] = *reinterpret_cast<const float2*>(table + pair_offset<BITS>(w, p, slot));
     wht64_pairs_from_stage2(v);
-    // 1/sqrt(64) is a power of two, so (x * rs) * norm == x * (rs * norm) in float32.
-    const float sc = 0.125f * norm;
-    const float2 scale = make_float2(sc, sc);
+    if (D == 128) {
+        // stage 64: coordinate i of the even lane pairs with coordinate i of the odd lane
+        const float sg = (lane & 1) ? -1.0f : 1.0f;
+        const float2 sgn = make_float2(sg, sg);
 #pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = mul2(v[i], scale);
+        for (int i = 0; i < 32; ++i) {
+            float2 o;
+            o.x = __shfl_xor_sync(0xFFFFFFFFu, v[i].x, 1);
+            o.y = __shfl_xor_sync(0xFFFFFFFFu, v[i].y, 1);
+            v[i] = __ffma2_rn(v[i], sgn, o);          // even: v + o, odd: o - v
+        }
+        const float2 r2 = make_float2(rs, rs), n2 = make_float2(norm, norm);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = mul2(mul2(v[i], r2), n2);
+    } else {
+        // 1/sqrt(64) is a power of two, so (x * rs) * norm == x * (rs * norm) in float32.
+        const float sc = 0.125f * norm;
+        const float2 scale = make_float2(sc, sc);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = mul2(v[i], scale);
+    }
     PairStore<T>::row(v, sign, stage + lane * Stage::PITCHB);
     __syncwarp();
-    // transposed read-out: chunk c = k*32 + lane of the tile's contiguous output
+    // transposed read-out: chunk c = k*32 + lane of the item's contiguous output
     const unsigned char* src = stage + (lane / Stage::CPR) * Stage::PITCHB + (lane % Stage::CPR) * 16;
     uint4* dst = reinterpret_cast<uint4*>(out) + lane;
-    const int valid_chunks = nvalid * Stage::CPR;
+    const int valid_chunks = nvalid * (D / Stage::EPC);
 #pragma unroll
     for (int k = 0; k < Stage::CPR; ++k) {
         const uint4 q = *reinterpret_cast<const uint4*>(src + k * (32 / Stage::CPR) * Stage::PITCHB);
@@ -256,11 +307,12 @@ __device__ __forceinline__ float step15(float lo, float hi) {
     return s == 0.0f ? 1.0f : s;
 }
 
-// 32 tokens (d = 64, b = 4, all inside one group) per warp: lane = (token lane 0..3, slab 0..7).
+// TOKENS tokens (4-bit codes, all inside one group) per warp: lane = (token lane, slab).
 // code * step + lo with one rounding per operation.
-template <typename T, bool FULL>
+template <typename T, int D, bool FULL>
 __device__ __forceinline__ void channel64_decode_warp(const Prefetch64& f, T* __restrict__ out, int nvalid, int lane) {
-    const int slab = lane & 7, tok_lane = lane >> 3;
+    constexpr int SLABS = Item64<D>::SLABS, TOK_LANES = Item64<D>::TOK_LANES;
+    const int tok_lane = lane / SLABS;
     const uint32_t w[8] = {f.a.x, f.a.y, f.a.z, f.a.w, f.b.x, f.b.y, f.b.z, f.b.w};
     const uint32_t lo16[4] = {f.c.x, f.c.y, f.c.z, f.c.w}, hi16[4] = {f.d.x, f.d.y, f.d.z, f.d.w};
     float2 lo[4], step[4];
@@ -270,21 +322,21 @@ __device__ __forceinline__ void channel64_decode_warp(const Prefetch64& f, T* __
         const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&hi16[i]));
         step[i] = make_float2(step15(lo[i].x, hi.x), step15(lo[i].y, hi.y));
     }
-    T* mine = out + tok_lane * 64 + slab * 8;                // token 4k + tok_lane is 256k elements further
+    T* mine = out + lane * 8;                 // token k*TOK_LANES + tok_lane, slab: element k*256 + lane*8
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
         float2 v[4];
         codes8_to_pairs(w[k], v);
 #pragma unroll
         for (int i = 0; i < 4; ++i) v[i] = mul2_then_add(v[i], step[i], lo[i]);
-        Pairs8<T>::store(mine + 256 * k, v, FULL || 4 * k + tok_lane < nvalid);
+        Pairs8<T>::store(mine + 256 * k, v, FULL || TOK_LANES * k + tok_lane < nvalid);
     }
 }
 
 struct Plane64 {
     int kind;                 // 0 = TurboQuant, 1 = per-channel
-    int group_tiles;          // per-channel planes: group size / 32
-    uint32_t neg_lo, neg_hi;  // rotation diagonal: bit i set when element i (resp. 32 + i) is negated
+    int group_items;          // per-channel planes: group size / tokens per item
+    uint32_t neg[4];          // rotation diagonal: bit i of word j set when coordinate 32j + i is negated
     const unsigned char* codes;
     int64_t codes_seg_stride;
     const unsigned char* side;
@@ -296,41 +348,48 @@ struct Plane64 {
 struct Cache64Params {
     int n_planes;
     int segments;
-    int full_tiles;           // whole 32-token tiles per segment (tokens / 32)
-    int tail;                 // tokens in the partial last tile of every segment (tokens % 32)
+    int full_items;           // whole items per segment (tokens / tokens per item)
+    int tail;                 // tokens in the partial last item of every segment
+    float rs;                 // 1/sqrt(dim), correctly rounded
     Plane64 plane[4];
-    Book16 book;              // TurboQuant centroids for (64, 4)
+    Book16 book;              // TurboQuant centroids for (dim, bits)
 };
 
+constexpr int CD_SIGN_BYTES = 4 * 64 * 4;      // [plane][pair of the vector] sign words
 template <typename T>
-constexpr int cache64_smem_bytes() { return CD_TABLE_BYTES + 4 * 32 * 4 + CD_WARPS * WarpStage<T, 64>::BYTES; }
+constexpr int cache64_smem_bytes() { return CD_TABLE_BYTES + CD_SIGN_BYTES + CD_WARPS * WarpStage<T, 64>::BYTES; }
 
-// A work item: one 32-token tile of one plane of one segment.
+// A work item: 2048 coordinates of one plane of one segment.
 struct Cursor64 {
-    int pl, seg, tile;
+    int pl, seg, item;
 };
 
 // grid = number of SMs (persistent), CD_THREADS threads, cache64_smem_bytes<T>() dynamic shared memory.
-template <typename T>
+// D in {64, 128}; BITS in {3, 4} is the width of the TurboQuant planes (per-channel planes are 4-bit).
+template <typename T, int D, int BITS>
 __global__ void __launch_bounds__(CD_THREADS, 1)
-cache_decode_d64b4_kernel(const __grid_constant__ Cache64Params p) {
+cache_decode_kernel(const __grid_constant__ Cache64Params p) {
+    constexpr int TOKENS = Item64<D>::TOKENS, LPV = Item64<D>::LPV;
+    constexpr int ITEM_CODE_BYTES = 32 * 8 * BITS;          // TurboQuant: 32 lanes x 64 codes
+    constexpr int CH_ITEM_CODE_BYTES = 1024;                // per-channel, 4 bits: 2048 codes
     extern __shared__ __align__(1024) unsigned char smem[];
     unsigned char* table = smem;
-    uint32_t* s_sign = reinterpret_cast<uint32_t*>(smem + CD_TABLE_BYTES);           // [4][32]
-    unsigned char* stage_base = smem + CD_TABLE_BYTES + 4 * 32 * 4;
+    uint32_t* s_sign = reinterpret_cast<uint32_t*>(smem + CD_TABLE_BYTES);           // [4][64]
+    unsigned char* stage_base = smem + CD_TABLE_BYTES + CD_SIGN_BYTES;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
     bool any_turbo = false;
     for (int pl = 0; pl < p.n_planes; ++pl) any_turbo |= p.plane[pl].kind == 0;
     if (any_turbo) {
-        for (int idx = threadIdx.x; idx < 256 * 32; idx += CD_THREADS) {
+        constexpr int ENTRIES = 1 << (2 * BITS);
+        for (int idx = threadIdx.x; idx < ENTRIES * 32; idx += CD_THREADS) {
             const int e = idx >> 5;
-            const float a = p.book.c[e & 15], b = p.book.c[e >> 4];
+            const float a = p.book.c[e & ((1 << BITS) - 1)], b = p.book.c[e >> BITS];
             *reinterpret_cast<float2*>(table + idx * 8) = make_float2(a + b, a - b);
         }
-        if (threadIdx.x < 4 * 32) {
-            const int pl = threadIdx.x >> 5, i = threadIdx.x & 31;       // packed pair i = elements 2i, 2i+1
-            const uint32_t m = i < 16 ? p.plane[pl].neg_lo : p.plane[pl].neg_hi;
+        if (threadIdx.x < 4 * 64) {
+            const int pl = threadIdx.x >> 6, i = threadIdx.x & 63;       // packed pair i = coordinates 2i, 2i+1
+            const uint32_t m = p.plane[pl].neg[i >> 4];
             const int bit = (2 * i) & 31;
             s_sign[threadIdx.x] = (((m >> bit) & 1u) << 15) | (((m >> (bit + 1)) & 1u) << 31);
         }
@@ -341,50 +400,51 @@ cache_decode_d64b4_kernel(const __grid_constant__ Cache64Params p) {
     // wait for it (and for its memory to be visible) before reading the cache.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     unsigned char* stage = stage_base + warp * WarpStage<T, 64>::BYTES;
-    // warp w of CTA c is worker w * gridDim + c: when the tile count is not a multiple of the worker
-    // count, the workers that take one tile more are spread evenly over the SMs
+    // warp w of CTA c is worker w * gridDim + c: when the item count is not a multiple of the worker
+    // count, the workers that take one item more are spread evenly over the SMs
     const int warp_id = warp * gridDim.x + blockIdx.x;
     const int warp_stride = gridDim.x * CD_WARPS;
+    const uint32_t* my_sign_base = s_sign + (LPV == 2 ? (lane & 1) * 32 : 0);
 
-    // Addresses of an item.  Whole tiles take the FULL (unchecked) paths.
+    // Addresses of an item.  Whole items take the FULL (unchecked) paths.
     auto fetch = [&](const Cursor64& c, Prefetch64& f) {
         const Plane64& P = p.plane[c.pl];
-        const unsigned char* codes = P.codes + c.seg * P.codes_seg_stride + (int64_t)c.tile * 1024;
         const unsigned char* side = P.side + c.seg * P.side_seg_stride;
         if (P.kind == 0)
-            prefetch_turbo64<true>(f, reinterpret_cast<const uint4*>(codes),
-                                   reinterpret_cast<const float*>(side) + c.tile * 32, 32, lane);
+            prefetch_turbo64<D, BITS, true>(f, P.codes + c.seg * P.codes_seg_stride + (int64_t)c.item * ITEM_CODE_BYTES,
+                                            reinterpret_cast<const float*>(side) + c.item * TOKENS, TOKENS, lane);
         else
-            prefetch_channel64<true>(f, reinterpret_cast<const uint32_t*>(codes),
-                                     reinterpret_cast<const __half*>(side) + (c.tile / P.group_tiles) * 128, 32, lane);
+            prefetch_channel64<D, true>(
+                f, reinterpret_cast<const uint32_t*>(P.codes + c.seg * P.codes_seg_stride + (int64_t)c.item * CH_ITEM_CODE_BYTES),
+                reinterpret_cast<const __half*>(side) + (c.item / P.group_items) * (2 * D), TOKENS, lane);
     };
     auto decode = [&](const Cursor64& c, const Prefetch64& f) {
         const Plane64& P = p.plane[c.pl];
-        T* out = reinterpret_cast<T*>(P.out + c.seg * P.out_seg_stride) + (int64_t)c.tile * 2048;
+        T* out = reinterpret_cast<T*>(P.out + c.seg * P.out_seg_stride) + (int64_t)c.item * 2048;
         if (P.kind == 0)
-            turbo64_decode_warp<T, true>(f, out, 32, table, s_sign + c.pl * 32, stage, lane);
+            turbo64_decode_warp<T, D, BITS, true>(f, out, TOKENS, table, my_sign_base + c.pl * 64, stage, lane, p.rs);
         else
-            channel64_decode_warp<T, true>(f, out, 32, lane);
+            channel64_decode_warp<T, D, true>(f, out, TOKENS, lane);
     };
-    // Next item of this warp: planes innermost, then the warp's next tile (round-robin over the grid).
+    // Next item of this warp: planes innermost, then the warp's next position (round-robin over the grid).
     auto advance = [&](Cursor64& c) {
         if (++c.pl < p.n_planes) return true;
         c.pl = 0;
-        c.tile += warp_stride;
-        if (c.tile >= p.full_tiles) {
-            const int q = c.tile / p.full_tiles;
+        c.item += warp_stride;
+        if (c.item >= p.full_items) {
+            const int q = c.item / p.full_items;
             c.seg += q;
-            c.tile -= q * p.full_tiles;
+            c.item -= q * p.full_items;
         }
         return c.seg < p.segments;
     };
 
-    // ---- whole tiles, software pipelined with two register buffers used alternately
-    if (p.full_tiles > 0) {
+    // ---- whole items, software pipelined with two register buffers used alternately
+    if (p.full_items > 0) {
         Cursor64 cur;
         cur.pl = 0;
-        cur.seg = warp_id / p.full_tiles;
-        cur.tile = warp_id - cur.seg * p.full_tiles;
+        cur.seg = warp_id / p.full_items;
+        cur.item = warp_id - cur.seg * p.full_items;
         if (cur.seg < p.segments) {
             Prefetch64 fa, fb;
             fetch(cur, fa);
@@ -405,24 +465,23 @@ cache_decode_d64b4_kernel(const __grid_constant__ Cache64Params p) {
         }
     }
 
-    // ---- the partial last tile of every segment (at most one per segment and plane)
+    // ---- the partial last item of every segment (at most one per segment and plane)
     if (p.tail > 0) {
-        for (int item = warp_id; item < p.segments * p.n_planes; item += warp_stride) {
-            const int seg = item / p.n_planes, pl = item - seg * p.n_planes;
+        for (int work = warp_id; work < p.segments * p.n_planes; work += warp_stride) {
+            const int seg = work / p.n_planes, pl = work - seg * p.n_planes;
             const Plane64& P = p.plane[pl];
-            const unsigned char* codes = P.codes + seg * P.codes_seg_stride + (int64_t)p.full_tiles * 1024;
             const unsigned char* side = P.side + seg * P.side_seg_stride;
-            T* out = reinterpret_cast<T*>(P.out + seg * P.out_seg_stride) + (int64_t)p.full_tiles * 2048;
+            T* out = reinterpret_cast<T*>(P.out + seg * P.out_seg_stride) + (int64_t)p.full_items * 2048;
             Prefetch64 f;
             if (P.kind == 0) {
-                prefetch_turbo64<false>(f, reinterpret_cast<const uint4*>(codes),
-                                        reinterpret_cast<const float*>(side) + p.full_tiles * 32, p.tail, lane);
-                turbo64_decode_warp<T, false>(f, out, p.tail, table, s_sign + pl * 32, stage, lane);
+                prefetch_turbo64<D, BITS, false>(f, P.codes + seg * P.codes_seg_stride + (int64_t)p.full_items * ITEM_CODE_BYTES,
+                                                 reinterpret_cast<const float*>(side) + p.full_items * TOKENS, p.tail, lane);
+                turbo64_decode_warp<T, D, BITS, false>(f, out, p.tail, table, my_sign_base + pl * 64, stage, lane, p.rs);
             } else {
-                prefetch_channel64<false>(f, reinterpret_cast<const uint32_t*>(codes),
-                                          reinterpret_cast<const __half*>(side) + (p.full_tiles / P.group_tiles) * 128,
-                                          p.tail, lane);
-                channel64_decode_warp<T, false>(f, out, p.tail, lane);
+                prefetch_channel64<D, false>(
+                    f, reinterpret_cast<const uint32_t*>(P.codes + seg * P.codes_seg_stride + (int64_t)p.full_items * CH_ITEM_CODE_BYTES),
+                    reinterpret_cast<const __half*>(side) + (p.full_items / P.group_items) * (2 * D), p.tail, lane);
+                channel64_decode_warp<T, D, false>(f, out, p.tail, lane);
             }
         }
     }

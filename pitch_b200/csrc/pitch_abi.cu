@@ -179,18 +179,18 @@ int sm_count() {
     return cached[dev];
 }
 
-template <typename T>
-int launch_cache64(const Cache64Params& p, cudaStream_t s) {
+template <typename T, int D, int BITS>
+int launch_cache64_impl(const Cache64Params& p, cudaStream_t s) {
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     constexpr int smem = cache64_smem_bytes<T>();
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        if (cudaFuncSetAttribute(cache_decode_d64b4_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(cache_decode_kernel<T, D, BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
             return launch_status(false, "cache_decode (shared memory opt-in)");
         configured[dev] = true;
     }
-    const int64_t work = (int64_t)p.segments * (p.full_tiles > 0 ? p.full_tiles : 1);
+    const int64_t work = (int64_t)p.segments * (p.full_items > 0 ? p.full_items : 1);
     int64_t ctas = ceil_div(work, CD_WARPS);
     if (ctas > sm_count()) ctas = sm_count();
     // Programmatic dependent launch: the kernel may start while the previous kernel of the stream
@@ -206,8 +206,28 @@ int launch_cache64(const Cache64Params& p, cudaStream_t s) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaLaunchKernelEx(&cfg, cache_decode_d64b4_kernel<T>, p);
+    cudaLaunchKernelEx(&cfg, cache_decode_kernel<T, D, BITS>, p);
     return PITCH_OK;
+}
+
+// dim in {64, 128}, bits (of the TurboQuant planes) in {3, 4}
+template <typename T>
+int launch_cache64(const Cache64Params& p, int dim, int bits, cudaStream_t s) {
+    if (dim == 64) return bits == 4 ? launch_cache64_impl<T, 64, 4>(p, s) : launch_cache64_impl<T, 64, 3>(p, s);
+    return bits == 4 ? launch_cache64_impl<T, 128, 4>(p, s) : launch_cache64_impl<T, 128, 3>(p, s);
+}
+
+// Fills the geometry of a fast-path launch: `tokens` tokens per segment at head dimension `dim`.
+void cache64_geometry(Cache64Params& p, int dim, int64_t segments, int64_t tokens) {
+    const int per_item = 2048 / dim;
+    p.segments = (int)segments;
+    p.full_items = (int)(tokens / per_item);
+    p.tail = (int)(tokens % per_item);
+    p.rs = rsqrt_dim(dim);
+}
+
+void cache64_signs(Plane64& q, uint32_t seed) {
+    for (int j = 0; j < 4; ++j) q.neg[j] = negate_mask32(seed, 32u * j);
 }
 
 template <int BITS, typename T>
@@ -228,24 +248,21 @@ int launch_turbo_decode(int dim, uint32_t seed, const void* codes, const void* s
     Codebook<BITS> book;
     if (!fetch_book<BITS>(dim, book))
         return fail(PITCH_ERR_INVALID_INPUT, "no TurboQuant codebook for dim %d, bits %d", dim, BITS);
-    if (BITS == 4 && dim == 64 && aligned16(codes) && aligned16(out)) {
+    if ((BITS == 4 || BITS == 3) && (dim == 64 || dim == 128) && aligned16(codes) && aligned16(out) &&
+        count / (2048 / dim) <= 0x3FFFFFFF) {
+        // the persistent whole-cache kernel with a single TurboQuant plane
         Cache64Params p;
         memset(&p, 0, sizeof p);
         p.n_planes = 1;
-        if (count / 32 <= 0x3FFFFFFF) {
-            p.segments = 1;
-            p.full_tiles = (int)(count / 32);
-            p.tail = (int)(count % 32);
-            p.plane[0].kind = 0;
-            p.plane[0].group_tiles = 1;
-            p.plane[0].neg_lo = negate_mask32(seed, 0);
-            p.plane[0].neg_hi = negate_mask32(seed, 32);
-            p.plane[0].codes = static_cast<const unsigned char*>(codes);
-            p.plane[0].side = static_cast<const unsigned char*>(scales);
-            p.plane[0].out = static_cast<unsigned char*>(out);
-            memcpy(p.book.c, book.c, sizeof p.book.c);
-            return launch_cache64<T>(p, s);
-        }
+        cache64_geometry(p, dim, 1, count);
+        p.plane[0].kind = 0;
+        p.plane[0].group_items = 1;
+        cache64_signs(p.plane[0], seed);
+        p.plane[0].codes = static_cast<const unsigned char*>(codes);
+        p.plane[0].side = static_cast<const unsigned char*>(scales);
+        p.plane[0].out = static_cast<unsigned char*>(out);
+        memcpy(p.book.c, book.c, sizeof(float) << BITS);
+        return launch_cache64<T>(p, dim, BITS, s);
     }
     turbo_decode_kernel<BITS, T><<<vec_grid(count, dim), VEC_THREADS, 0, s>>>(
         static_cast<const uint32_t*>(codes), static_cast<const float*>(scales), static_cast<T*>(out), count, dim, seed,
@@ -464,20 +481,19 @@ int pitch_enqueue_channel_decode(int dim, int bits, int group_size, int dtype, p
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool slab = slab_ok(dim, bits) && aligned16(at(output)) && aligned16(at(ranges)) &&
                       (reinterpret_cast<uintptr_t>(at(codes)) % (bits == 8 ? 8 : 4)) == 0;
-    if (slab && dim == 64 && bits == 4 && group_size % 32 == 0 && aligned16(at(codes)) && count / 32 <= 0x3FFFFFFF) {
+    if (slab && (dim == 64 || dim == 128) && bits == 4 && group_size % (2048 / dim) == 0 && aligned16(at(codes)) &&
+        count / (2048 / dim) <= 0x3FFFFFFF) {
         // the persistent whole-cache kernel with a single per-channel plane
         Cache64Params p;
         memset(&p, 0, sizeof p);
         p.n_planes = 1;
-        p.segments = 1;
-        p.full_tiles = (int)(count / 32);
-        p.tail = (int)(count % 32);
+        cache64_geometry(p, dim, 1, count);
         p.plane[0].kind = 1;
-        p.plane[0].group_tiles = group_size / 32;
+        p.plane[0].group_items = group_size / (2048 / dim);
         p.plane[0].codes = at(codes);
         p.plane[0].side = at(ranges);
         p.plane[0].out = at(output);
-        PITCH_DISPATCH_DTYPE(dtype, st = (launch_cache64<T>(p, s)));
+        PITCH_DISPATCH_DTYPE(dtype, st = (launch_cache64<T>(p, dim, 4, s)));
         if (st) return st;
         return launch_status(false, "channel_decode");
     }
@@ -571,7 +587,8 @@ int pitch_enqueue_cache_decode(const pitch_cache_desc* d, void* stream) {
     if (d->segments < 1 || d->tokens < 1) return fail(PITCH_ERR_INVALID_INPUT, "segments and tokens must be at least 1");
     if (d->out_dtype < PITCH_F32 || d->out_dtype > PITCH_BF16) return fail(PITCH_ERR_INVALID_INPUT, "unknown dtype %d", d->out_dtype);
     const int dim = d->dim;
-    bool fused = dim == 64;
+    bool fused = dim == 64 || dim == 128;
+    int turbo_bits = 0;                       // all TurboQuant planes of a fast-path launch share one width
     for (int i = 0; i < d->n_planes; ++i) {
         const pitch_plane& pl = d->planes[i];
         int st;
@@ -591,10 +608,15 @@ int pitch_enqueue_cache_decode(const pitch_cache_desc* d, void* stream) {
                                 pl.side_seg_stride < plane_side_bytes(pl, dim, d->tokens) ||
                                 pl.out_seg_stride < d->tokens * dim * elem_size(d->out_dtype)))
             return fail(PITCH_ERR_INVALID_INPUT, "plane %d: a segment stride is smaller than one segment", i);
-        if (pl.bits != 4) fused = false;
         if (pl.kind == PITCH_PLANE_POLAR) fused = false;
-        if (pl.kind == PITCH_PLANE_CHANNEL && pl.group_size % 32 != 0) fused = false;
-        if (d->segments > 0x7FFFFFFF / (d->tokens / 32 + 1)) fused = false;      // 32-bit tile indices in the kernel
+        if (pl.kind == PITCH_PLANE_CHANNEL && (pl.bits != 4 || dim > 128 || pl.group_size % (2048 / (dim > 128 ? 128 : dim)) != 0))
+            fused = false;
+        if (pl.kind == PITCH_PLANE_TURBO) {
+            if (pl.bits != 3 && pl.bits != 4) fused = false;
+            if (turbo_bits != 0 && turbo_bits != pl.bits) fused = false;
+            turbo_bits = pl.bits;
+        }
+        if (d->segments > 0x7FFFFFFF / (d->tokens / 16 + 1)) fused = false;      // 32-bit item indices in the kernel
     }
     cudaPointerAttributes attr;
     if (cudaPointerGetAttributes(&attr, d->planes[0].out) != cudaSuccess ||
@@ -610,32 +632,30 @@ int pitch_enqueue_cache_decode(const pitch_cache_desc* d, void* stream) {
         Cache64Params p;
         memset(&p, 0, sizeof p);
         p.n_planes = d->n_planes;
-        p.segments = (int)d->segments;
-        p.full_tiles = (int)(d->tokens / 32);
-        p.tail = (int)(d->tokens % 32);
-        bool need_book = false;
+        cache64_geometry(p, dim, d->segments, d->tokens);
+        if (turbo_bits == 0) turbo_bits = 4;
         for (int i = 0; i < d->n_planes; ++i) {
             const pitch_plane& pl = d->planes[i];
             Plane64& q = p.plane[i];
             q.kind = pl.kind == PITCH_PLANE_CHANNEL ? 1 : 0;
-            q.group_tiles = pl.kind == PITCH_PLANE_CHANNEL ? pl.group_size / 32 : 1;
-            q.neg_lo = negate_mask32(pl.seed, 0);
-            q.neg_hi = negate_mask32(pl.seed, 32);
+            q.group_items = pl.kind == PITCH_PLANE_CHANNEL ? pl.group_size / (2048 / dim) : 1;
+            cache64_signs(q, pl.seed);
             q.codes = static_cast<const unsigned char*>(pl.codes);
             q.codes_seg_stride = pl.codes_seg_stride;
             q.side = static_cast<const unsigned char*>(pl.side);
             q.side_seg_stride = pl.side_seg_stride;
             q.out = static_cast<unsigned char*>(pl.out);
             q.out_seg_stride = pl.out_seg_stride;
-            need_book |= q.kind == 0;
-        }
-        if (need_book) {
-            Codebook<4> book;
-            if (!fetch_book<4>(64, book)) return fail(PITCH_ERR_INVALID_INPUT, "no TurboQuant codebook for dim 64, bits 4");
-            memcpy(p.book.c, book.c, sizeof p.book.c);
+            if (q.kind == 0) {
+                std::lock_guard<std::mutex> guardb(g_books.lock);
+                const int l = log2_exact(dim);
+                if (!g_books.present[l][turbo_bits])
+                    return fail(PITCH_ERR_INVALID_INPUT, "no TurboQuant codebook for dim %d, bits %d", dim, turbo_bits);
+                memcpy(p.book.c, g_books.values[l][turbo_bits], sizeof(float) << turbo_bits);
+            }
         }
         int st = 0;
-        PITCH_DISPATCH_DTYPE(d->out_dtype, st = (launch_cache64<T>(p, s)));
+        PITCH_DISPATCH_DTYPE(d->out_dtype, st = (launch_cache64<T>(p, dim, turbo_bits, s)));
         if (st) return st;
         return launch_status(false, "cache_decode");
     }
