@@ -236,9 +236,14 @@ int launch_turbo_encode(int dim, uint32_t seed, const void* in, void* codes, voi
     Codebook<BITS> book;
     if (!fetch_book<BITS>(dim, book))
         return fail(PITCH_ERR_INVALID_INPUT, "no TurboQuant codebook for dim %d, bits %d", dim, BITS);
-    turbo_encode_kernel<BITS, T><<<vec_grid(count, dim), VEC_THREADS, 0, s>>>(
-        static_cast<const T*>(in), static_cast<uint32_t*>(codes), static_cast<float*>(scales), count, dim, seed,
-        rsqrt_dim(dim), aligned16(in) ? 1 : 0, book);
+    if (dim < 32)
+        turbo_encode_kernel<BITS, T, true><<<vec_grid(count, dim), VEC_THREADS, 0, s>>>(
+            static_cast<const T*>(in), static_cast<uint32_t*>(codes), static_cast<float*>(scales), count, dim, seed,
+            rsqrt_dim(dim), aligned16(in) ? 1 : 0, book);
+    else
+        turbo_encode_kernel<BITS, T, false><<<vec_grid(count, dim), VEC_THREADS, 0, s>>>(
+            static_cast<const T*>(in), static_cast<uint32_t*>(codes), static_cast<float*>(scales), count, dim, seed,
+            rsqrt_dim(dim), aligned16(in) ? 1 : 0, book);
     return PITCH_OK;
 }
 
@@ -264,9 +269,14 @@ int launch_turbo_decode(int dim, uint32_t seed, const void* codes, const void* s
         memcpy(p.book.c, book.c, sizeof(float) << BITS);
         return launch_cache64<T>(p, dim, BITS, s);
     }
-    turbo_decode_kernel<BITS, T><<<vec_grid(count, dim), VEC_THREADS, 0, s>>>(
-        static_cast<const uint32_t*>(codes), static_cast<const float*>(scales), static_cast<T*>(out), count, dim, seed,
-        rsqrt_dim(dim), aligned16(out) ? 1 : 0, book);
+    if (dim < 32)
+        turbo_decode_kernel<BITS, T, true><<<vec_grid(count, dim), VEC_THREADS, 0, s>>>(
+            static_cast<const uint32_t*>(codes), static_cast<const float*>(scales), static_cast<T*>(out), count, dim, seed,
+            rsqrt_dim(dim), aligned16(out) ? 1 : 0, book);
+    else
+        turbo_decode_kernel<BITS, T, false><<<vec_grid(count, dim), VEC_THREADS, 0, s>>>(
+            static_cast<const uint32_t*>(codes), static_cast<const float*>(scales), static_cast<T*>(out), count, dim, seed,
+            rsqrt_dim(dim), aligned16(out) ? 1 : 0, book);
     return PITCH_OK;
 }
 
@@ -388,11 +398,19 @@ int pitch_enqueue_encode(int method, int dim, int bits, uint32_t seed, int dtype
                                                                   dim, seed, at(input), at(codes), at(scales), count, s))));
         if (st) return st;
     } else {
-        PITCH_DISPATCH_BITS(bits, PITCH_DISPATCH_DTYPE(dtype, (polar_encode_kernel<BITS, T><<<vec_grid(count, dim), VEC_THREADS, 0, s>>>(
-                                                                  reinterpret_cast<const T*>(at(input)),
-                                                                  reinterpret_cast<uint32_t*>(at(codes)),
-                                                                  reinterpret_cast<float*>(at(scales)), count, dim, seed, rs,
-                                                                  aligned16(at(input)) ? 1 : 0))));
+        if (dim < 32) {
+            PITCH_DISPATCH_BITS(bits, PITCH_DISPATCH_DTYPE(dtype, (polar_encode_kernel<BITS, T, true><<<vec_grid(count, dim), VEC_THREADS, 0, s>>>(
+                                                                      reinterpret_cast<const T*>(at(input)),
+                                                                      reinterpret_cast<uint32_t*>(at(codes)),
+                                                                      reinterpret_cast<float*>(at(scales)), count, dim, seed, rs,
+                                                                      aligned16(at(input)) ? 1 : 0))));
+        } else {
+            PITCH_DISPATCH_BITS(bits, PITCH_DISPATCH_DTYPE(dtype, (polar_encode_kernel<BITS, T, false><<<vec_grid(count, dim), VEC_THREADS, 0, s>>>(
+                                                                      reinterpret_cast<const T*>(at(input)),
+                                                                      reinterpret_cast<uint32_t*>(at(codes)),
+                                                                      reinterpret_cast<float*>(at(scales)), count, dim, seed, rs,
+                                                                      aligned16(at(input)) ? 1 : 0))));
+        }
     }
     return launch_status(true, method == PITCH_TURBO_QUANT ? "turbo_encode" : "polar_encode");
 }
@@ -418,11 +436,19 @@ int pitch_enqueue_decode(int method, int dim, int bits, uint32_t seed, int dtype
                                                                   dim, seed, at(codes), at(scales), at(output), count, s))));
         if (st) return st;
     } else {
-        PITCH_DISPATCH_BITS(bits, PITCH_DISPATCH_DTYPE(dtype, (polar_decode_kernel<BITS, T><<<vec_grid(count, dim), VEC_THREADS, 0, s>>>(
-                                                                  reinterpret_cast<const uint32_t*>(at(codes)),
-                                                                  reinterpret_cast<const float*>(at(scales)),
-                                                                  reinterpret_cast<T*>(at(output)), count, dim, seed, rs,
-                                                                  aligned16(at(output)) ? 1 : 0))));
+        if (dim < 32) {
+            PITCH_DISPATCH_BITS(bits, PITCH_DISPATCH_DTYPE(dtype, (polar_decode_kernel<BITS, T, true><<<vec_grid(count, dim), VEC_THREADS, 0, s>>>(
+                                                                      reinterpret_cast<const uint32_t*>(at(codes)),
+                                                                      reinterpret_cast<const float*>(at(scales)),
+                                                                      reinterpret_cast<T*>(at(output)), count, dim, seed, rs,
+                                                                      aligned16(at(output)) ? 1 : 0))));
+        } else {
+            PITCH_DISPATCH_BITS(bits, PITCH_DISPATCH_DTYPE(dtype, (polar_decode_kernel<BITS, T, false><<<vec_grid(count, dim), VEC_THREADS, 0, s>>>(
+                                                                      reinterpret_cast<const uint32_t*>(at(codes)),
+                                                                      reinterpret_cast<const float*>(at(scales)),
+                                                                      reinterpret_cast<T*>(at(output)), count, dim, seed, rs,
+                                                                      aligned16(at(output)) ? 1 : 0))));
+        }
     }
     return launch_status(false, method == PITCH_TURBO_QUANT ? "turbo_decode" : "polar_decode");
 }
@@ -535,9 +561,14 @@ int pitch_enqueue_rotate(int mode, int dim, uint32_t seed, pitch_buffer input, p
     int dev;
     if ((st = check_same_device(bufs, names, 2, &dev))) return st;
     DeviceGuard guard(dev);
-    rotate_kernel<<<vec_grid(count, dim), VEC_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
-        reinterpret_cast<const float*>(at(input)), reinterpret_cast<float*>(at(output)), count, dim, seed,
-        rsqrt_dim(dim), mode, aligned16(at(input)) ? 1 : 0, aligned16(at(output)) ? 1 : 0);
+    if (dim < 32)
+        rotate_kernel<true><<<vec_grid(count, dim), VEC_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+            reinterpret_cast<const float*>(at(input)), reinterpret_cast<float*>(at(output)), count, dim, seed,
+            rsqrt_dim(dim), mode, aligned16(at(input)) ? 1 : 0, aligned16(at(output)) ? 1 : 0);
+    else
+        rotate_kernel<false><<<vec_grid(count, dim), VEC_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+            reinterpret_cast<const float*>(at(input)), reinterpret_cast<float*>(at(output)), count, dim, seed,
+            rsqrt_dim(dim), mode, aligned16(at(input)) ? 1 : 0, aligned16(at(output)) ? 1 : 0);
     return launch_status(true, "rotate");
 }
 

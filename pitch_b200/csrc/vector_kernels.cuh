@@ -23,24 +23,27 @@ constexpr int VEC_THREADS = VEC_WARPS * 32;
 template <int BITS> struct Codebook { float c[1 << BITS]; };
 
 // Geometry of a warp tile for a given dim.
-struct TileGeom {
-    int e;        // coordinates per lane
+// SMALL selects the dim < 32 variant (one vector per lane, dim coordinates in use); for dim >= 32
+// the per-lane count is the compile-time constant 32, so all per-coordinate guards fold away.
+template <bool SMALL> struct TileGeom {
+    int e_small;  // coordinates per lane when SMALL
     int tpv;      // lanes per vector
     int vpw;      // vectors per warp tile
     int wpv;      // packed words per vector
     __device__ __forceinline__ TileGeom(int dim, int bits) {
-        e = dim < 32 ? dim : 32;
-        tpv = dim < 32 ? 1 : dim >> 5;
+        e_small = dim;
+        tpv = SMALL ? 1 : dim >> 5;
         vpw = 32 / tpv;
         wpv = words_per_vector(dim, bits);
     }
+    __device__ __forceinline__ int e() const { return SMALL ? e_small : 32; }
 };
 
-template <typename T>
+template <typename T, bool SMALL>
 __device__ __forceinline__ void load_lane_coords(const T* __restrict__ in, int64_t v0, int64_t count, int dim,
-                                                 const TileGeom& g, bool vec_ok, unsigned char* stage,
+                                                 const TileGeom<SMALL>& g, bool vec_ok, unsigned char* stage,
                                                  int lane, bool valid, int64_t v, float (&x)[32]) {
-    if (dim >= 32) {
+    if (!SMALL) {
         const int64_t left = count - v0;
         const int valid_elems = (int)(left < g.vpw ? left : g.vpw) * dim;
         WarpStage<T, 32>::load(in + v0 * dim, valid_elems, vec_ok, stage, lane, x);
@@ -50,11 +53,11 @@ __device__ __forceinline__ void load_lane_coords(const T* __restrict__ in, int64
     }
 }
 
-template <typename T>
+template <typename T, bool SMALL>
 __device__ __forceinline__ void store_lane_coords(T* __restrict__ out, int64_t v0, int64_t count, int dim,
-                                                  const TileGeom& g, bool vec_ok, unsigned char* stage,
+                                                  const TileGeom<SMALL>& g, bool vec_ok, unsigned char* stage,
                                                   int lane, bool valid, int64_t v, const float (&x)[32]) {
-    if (dim >= 32) {
+    if (!SMALL) {
         const int64_t left = count - v0;
         const int valid_elems = (int)(left < g.vpw ? left : g.vpw) * dim;
         WarpStage<T, 32>::store(out + v0 * dim, valid_elems, vec_ok, stage, lane, x);
@@ -65,22 +68,22 @@ __device__ __forceinline__ void store_lane_coords(T* __restrict__ out, int64_t v
     }
 }
 
-template <int BITS>
+template <int BITS, bool SMALL>
 __device__ __forceinline__ void load_lane_words(const uint32_t* __restrict__ codes, int64_t v, int sub, int dim,
-                                                const TileGeom& g, bool valid, uint32_t (&w)[BITS]) {
+                                                const TileGeom<SMALL>& g, bool valid, uint32_t (&w)[BITS]) {
 #pragma unroll
     for (int k = 0; k < BITS; ++k) {
         w[k] = 0;
-        if (valid && (dim >= 32 || k < g.wpv)) w[k] = __ldg(codes + v * g.wpv + sub * BITS + k);
+        if (valid && (!SMALL || k < g.wpv)) w[k] = __ldg(codes + v * g.wpv + sub * BITS + k);
     }
 }
 
-template <int BITS>
+template <int BITS, bool SMALL>
 __device__ __forceinline__ void store_lane_words(uint32_t* __restrict__ codes, int64_t v, int sub, int dim,
-                                                 const TileGeom& g, bool valid, const uint32_t (&w)[BITS]) {
+                                                 const TileGeom<SMALL>& g, bool valid, const uint32_t (&w)[BITS]) {
 #pragma unroll
     for (int k = 0; k < BITS; ++k)
-        if (valid && (dim >= 32 || k < g.wpv)) codes[v * g.wpv + sub * BITS + k] = w[k];
+        if (valid && (!SMALL || k < g.wpv)) codes[v * g.wpv + sub * BITS + k] = w[k];
 }
 
 __device__ __forceinline__ void init_negate_masks(uint32_t* s_neg, uint32_t seed, int dim, int tid, int nthreads) {
@@ -93,7 +96,7 @@ __device__ __forceinline__ void init_negate_masks(uint32_t* s_neg, uint32_t seed
 // Follows reference/pitch_reference.py:92-102 in float32 (PITCHKernels.metal:114-152).
 // A code is the number of decision boundaries strictly below the rotated coordinate.
 // ------------------------------------------------------------------------------------------
-template <int BITS, typename T>
+template <int BITS, typename T, bool SMALL>
 __global__ void __launch_bounds__(VEC_THREADS)
 turbo_encode_kernel(const T* __restrict__ in, uint32_t* __restrict__ codes, float* __restrict__ norms,
                     int64_t count, int dim, uint32_t seed, float rs, int vec_ok, const Codebook<BITS> book) {
@@ -105,7 +108,7 @@ turbo_encode_kernel(const T* __restrict__ in, uint32_t* __restrict__ codes, floa
     __syncthreads();
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const TileGeom g(dim, BITS);
+    const TileGeom<SMALL> g(dim, BITS);
     const int64_t v0 = ((int64_t)blockIdx.x * VEC_WARPS + warp) * g.vpw;
     if (v0 >= count) return;
     const int sub = lane & (g.tpv - 1);
@@ -113,7 +116,7 @@ turbo_encode_kernel(const T* __restrict__ in, uint32_t* __restrict__ codes, floa
     const bool valid = v < count;
 
     float x[32];
-    load_lane_coords<T>(in, v0, count, dim, g, vec_ok != 0, s_stage[warp], lane, valid, v, x);
+    load_lane_coords<T, SMALL>(in, v0, count, dim, g, vec_ok != 0, s_stage[warp], lane, valid, v, x);
 
     float t[32];
 #pragma unroll
@@ -123,7 +126,7 @@ turbo_encode_kernel(const T* __restrict__ in, uint32_t* __restrict__ codes, floa
     const uint32_t neg = s_neg[sub];
 #pragma unroll
     for (int i = 0; i < 32; ++i) x[i] = flip_if(x[i], neg, i) * inv;
-    wht_regs(x, g.e);
+    wht_regs(x, g.e());
     wht_lanes(x, g.tpv, lane);
 
     uint32_t w[BITS];
@@ -131,7 +134,7 @@ turbo_encode_kernel(const T* __restrict__ in, uint32_t* __restrict__ codes, floa
     for (int k = 0; k < BITS; ++k) w[k] = 0;
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
-        if (i < g.e) {
+        if (i < g.e()) {
             const float u = x[i] * rs;
             uint32_t code = 0;
 #pragma unroll
@@ -142,7 +145,7 @@ turbo_encode_kernel(const T* __restrict__ in, uint32_t* __restrict__ codes, floa
             insert_code<BITS>(w, i, code);
         }
     }
-    store_lane_words<BITS>(codes, v, sub, dim, g, valid, w);
+    store_lane_words<BITS, SMALL>(codes, v, sub, dim, g, valid, w);
     if (valid && sub == 0) norms[v] = norm;
 }
 
@@ -150,7 +153,7 @@ turbo_encode_kernel(const T* __restrict__ in, uint32_t* __restrict__ codes, floa
 // TurboQuant decode: centroid lookup, WHT, sign, 1/sqrt(d), norm.
 // reference/pitch_reference.py:104-107, PITCHKernels.metal:154-174.
 // ------------------------------------------------------------------------------------------
-template <int BITS, typename T>
+template <int BITS, typename T, bool SMALL>
 __global__ void __launch_bounds__(VEC_THREADS)
 turbo_decode_kernel(const uint32_t* __restrict__ codes, const float* __restrict__ norms, T* __restrict__ out,
                     int64_t count, int dim, uint32_t seed, float rs, int vec_ok, const Codebook<BITS> book) {
@@ -162,7 +165,7 @@ turbo_decode_kernel(const uint32_t* __restrict__ codes, const float* __restrict_
     __syncthreads();
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const TileGeom g(dim, BITS);
+    const TileGeom<SMALL> g(dim, BITS);
     const int64_t v0 = ((int64_t)blockIdx.x * VEC_WARPS + warp) * g.vpw;
     if (v0 >= count) return;
     const int sub = lane & (g.tpv - 1);
@@ -170,18 +173,18 @@ turbo_decode_kernel(const uint32_t* __restrict__ codes, const float* __restrict_
     const bool valid = v < count;
 
     uint32_t w[BITS];
-    load_lane_words<BITS>(codes, v, sub, dim, g, valid, w);
+    load_lane_words<BITS, SMALL>(codes, v, sub, dim, g, valid, w);
     const float norm = valid ? __ldg(norms + v) : 0.0f;
 
     float x[32];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) x[i] = (i < g.e) ? s_book[extract_code<BITS>(w, i)] : 0.0f;
-    wht_regs(x, g.e);
+    for (int i = 0; i < 32; ++i) x[i] = (i < g.e()) ? s_book[extract_code<BITS>(w, i)] : 0.0f;
+    wht_regs(x, g.e());
     wht_lanes(x, g.tpv, lane);
     const uint32_t neg = s_neg[sub];
 #pragma unroll
     for (int i = 0; i < 32; ++i) x[i] = flip_if(x[i], neg, i) * rs * norm;
-    store_lane_coords<T>(out, v0, count, dim, g, vec_ok != 0, s_stage[warp], lane, valid, v, x);
+    store_lane_coords<T, SMALL>(out, v0, count, dim, g, vec_ok != 0, s_stage[warp], lane, valid, v, x);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -189,7 +192,7 @@ turbo_decode_kernel(const uint32_t* __restrict__ codes, const float* __restrict_
 // radius code on 2^b - 1 steps of [0, rmax], angle code on 2^b circular bins.
 // reference/pitch_reference.py:109-121, PITCHKernels.metal:178-222.
 // ------------------------------------------------------------------------------------------
-template <int BITS, typename T>
+template <int BITS, typename T, bool SMALL>
 __global__ void __launch_bounds__(VEC_THREADS)
 polar_encode_kernel(const T* __restrict__ in, uint32_t* __restrict__ codes, float* __restrict__ scales,
                     int64_t count, int dim, uint32_t seed, float rs, int vec_ok) {
@@ -199,7 +202,7 @@ polar_encode_kernel(const T* __restrict__ in, uint32_t* __restrict__ codes, floa
     __syncthreads();
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const TileGeom g(dim, BITS);
+    const TileGeom<SMALL> g(dim, BITS);
     const int64_t v0 = ((int64_t)blockIdx.x * VEC_WARPS + warp) * g.vpw;
     if (v0 >= count) return;
     const int sub = lane & (g.tpv - 1);
@@ -207,11 +210,11 @@ polar_encode_kernel(const T* __restrict__ in, uint32_t* __restrict__ codes, floa
     const bool valid = v < count;
 
     float x[32];
-    load_lane_coords<T>(in, v0, count, dim, g, vec_ok != 0, s_stage[warp], lane, valid, v, x);
+    load_lane_coords<T, SMALL>(in, v0, count, dim, g, vec_ok != 0, s_stage[warp], lane, valid, v, x);
     const uint32_t neg = s_neg[sub];
 #pragma unroll
     for (int i = 0; i < 32; ++i) x[i] = flip_if(x[i], neg, i);
-    wht_regs(x, g.e);
+    wht_regs(x, g.e());
     wht_lanes(x, g.tpv, lane);
 
     float r[16];
@@ -222,7 +225,7 @@ polar_encode_kernel(const T* __restrict__ in, uint32_t* __restrict__ codes, floa
         x[2 * p + 1] = x[2 * p + 1] * rs;
         const float aa = x[2 * p] * x[2 * p], cc = x[2 * p + 1] * x[2 * p + 1];
         r[p] = sqrtf(aa + cc);
-        if (2 * p < g.e) rmax = fmaxf(rmax, r[p]);
+        if (2 * p < g.e()) rmax = fmaxf(rmax, r[p]);
     }
     rmax = lanes_max(rmax, g.tpv);
     const float safe = rmax > 0.0f ? rmax : 1.0f;
@@ -234,7 +237,7 @@ polar_encode_kernel(const T* __restrict__ in, uint32_t* __restrict__ codes, floa
     for (int k = 0; k < BITS; ++k) w[k] = 0;
 #pragma unroll
     for (int p = 0; p < 16; ++p) {
-        if (2 * p < g.e) {
+        if (2 * p < g.e()) {
             float q = floorf(r[p] / safe * RL + 0.5f);
             q = fminf(fmaxf(q, 0.0f), RL);
             insert_code<BITS>(w, 2 * p, (uint32_t)q);
@@ -244,7 +247,7 @@ polar_encode_kernel(const T* __restrict__ in, uint32_t* __restrict__ codes, floa
             insert_code<BITS>(w, 2 * p + 1, tq);
         }
     }
-    store_lane_words<BITS>(codes, v, sub, dim, g, valid, w);
+    store_lane_words<BITS, SMALL>(codes, v, sub, dim, g, valid, w);
     if (valid && sub == 0) scales[v] = rmax;
 }
 
@@ -252,7 +255,7 @@ polar_encode_kernel(const T* __restrict__ in, uint32_t* __restrict__ codes, floa
 // PolarQuant variant decode.  reference/pitch_reference.py:123-129, PITCHKernels.metal:224-246.
 // The 2^b angles are tabulated once per CTA.
 // ------------------------------------------------------------------------------------------
-template <int BITS, typename T>
+template <int BITS, typename T, bool SMALL>
 __global__ void __launch_bounds__(VEC_THREADS)
 polar_decode_kernel(const uint32_t* __restrict__ codes, const float* __restrict__ scales, T* __restrict__ out,
                     int64_t count, int dim, uint32_t seed, float rs, int vec_ok) {
@@ -268,7 +271,7 @@ polar_decode_kernel(const uint32_t* __restrict__ codes, const float* __restrict_
     __syncthreads();
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const TileGeom g(dim, BITS);
+    const TileGeom<SMALL> g(dim, BITS);
     const int64_t v0 = ((int64_t)blockIdx.x * VEC_WARPS + warp) * g.vpw;
     if (v0 >= count) return;
     const int sub = lane & (g.tpv - 1);
@@ -276,14 +279,14 @@ polar_decode_kernel(const uint32_t* __restrict__ codes, const float* __restrict_
     const bool valid = v < count;
 
     uint32_t w[BITS];
-    load_lane_words<BITS>(codes, v, sub, dim, g, valid, w);
+    load_lane_words<BITS, SMALL>(codes, v, sub, dim, g, valid, w);
     const float scale = valid ? __ldg(scales + v) : 0.0f;
     constexpr float RL = (float)((1 << BITS) - 1);
 
     float x[32];
 #pragma unroll
     for (int p = 0; p < 16; ++p) {
-        if (2 * p < g.e) {
+        if (2 * p < g.e()) {
             const float r = (float)extract_code<BITS>(w, 2 * p) / RL * scale;
             const uint32_t tq = extract_code<BITS>(w, 2 * p + 1);
             x[2 * p] = r * s_cos[tq];
@@ -293,12 +296,12 @@ polar_decode_kernel(const uint32_t* __restrict__ codes, const float* __restrict_
             x[2 * p + 1] = 0.0f;
         }
     }
-    wht_regs(x, g.e);
+    wht_regs(x, g.e());
     wht_lanes(x, g.tpv, lane);
     const uint32_t neg = s_neg[sub];
 #pragma unroll
     for (int i = 0; i < 32; ++i) x[i] = flip_if(x[i], neg, i) * rs;
-    store_lane_coords<T>(out, v0, count, dim, g, vec_ok != 0, s_stage[warp], lane, valid, v, x);
+    store_lane_coords<T, SMALL>(out, v0, count, dim, g, vec_ok != 0, s_stage[warp], lane, valid, v, x);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -306,6 +309,7 @@ polar_decode_kernel(const uint32_t* __restrict__ codes, const float* __restrict_
 // rotate = WHT(x * signs) / sqrt(d); mode 2: unrotate = WHT(y) * signs / sqrt(d).
 // reference/pitch_reference.py:21-34.
 // ------------------------------------------------------------------------------------------
+template <bool SMALL>
 __global__ void __launch_bounds__(VEC_THREADS)
 rotate_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t count, int dim, uint32_t seed,
               float rs, int mode, int vec_in_ok, int vec_out_ok) {
@@ -314,20 +318,20 @@ rotate_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t cou
     init_negate_masks(s_neg, seed, dim, threadIdx.x, VEC_THREADS);
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const TileGeom g(dim, 8);
+    const TileGeom<SMALL> g(dim, 8);
     const int64_t v0 = ((int64_t)blockIdx.x * VEC_WARPS + warp) * g.vpw;
     if (v0 >= count) return;
     const int sub = lane & (g.tpv - 1);
     const int64_t v = v0 + lane / g.tpv;
     const bool valid = v < count;
     float x[32];
-    load_lane_coords<float>(in, v0, count, dim, g, vec_in_ok != 0, s_stage[warp], lane, valid, v, x);
+    load_lane_coords<float, SMALL>(in, v0, count, dim, g, vec_in_ok != 0, s_stage[warp], lane, valid, v, x);
     const uint32_t neg = s_neg[sub];
     if (mode == 1) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) x[i] = flip_if(x[i], neg, i);
     }
-    wht_regs(x, g.e);
+    wht_regs(x, g.e());
     wht_lanes(x, g.tpv, lane);
     if (mode == 2) {
 #pragma unroll
@@ -337,7 +341,7 @@ rotate_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t cou
 #pragma unroll
         for (int i = 0; i < 32; ++i) x[i] = x[i] * rs;
     }
-    store_lane_coords<float>(out, v0, count, dim, g, vec_out_ok != 0, s_stage[warp], lane, valid, v, x);
+    store_lane_coords<float, SMALL>(out, v0, count, dim, g, vec_out_ok != 0, s_stage[warp], lane, valid, v, x);
 }
 
 }  // namespace pitch
