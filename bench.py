@@ -377,7 +377,7 @@ def run_ours(args) -> None:
         else:
             peak = 6650.0
         # dram__bytes_read.sum + dram__bytes_write.sum per launch at full size, from the ncu capture
-        # summarised in profiles/cache_decode_d64b4_config4.md (part of the output is still dirty in L2
+        # summarised in profiles/cache_decode_kernel_config4.md (part of the output is still dirty in L2
         # when the kernel ends, so it is below the algorithmic bytes); only valid for the full workload
         traffic = 455.6e6 if segments == SEGMENTS else None
         cpu = cpu_baseline_sample() if (n_gpus == 1 and not args.kernel_only) else None
@@ -391,7 +391,7 @@ def run_ours(args) -> None:
                        "parallelism": f"{'one cache per gpu' if args.scaling == 'weak' else 'layers sharded'} x{n_gpus}, no data-path collective"},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "traffic": traffic, "peak_source": peak_src,
-                         "frac_of_nominal_8000": round(achieved / 8000.0, 4), "kernel": "cache_decode_d64b4_kernel",
+                         "frac_of_nominal_8000": round(achieved / 8000.0, 4), "kernel": "cache_decode_kernel<bf16,64,4>",
                          "kernel_ms": round(decode_ms, 5), "kernel_launches_timed": len(sampled)},
             "e2e": None if not e2e_steps else {
                 "value": round(e2e_bytes / e2e_steps * n_gpus / (e2e_ms * 1e-3) / 1e9, 3), "unit": "GB/s",
