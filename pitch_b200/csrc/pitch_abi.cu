@@ -230,20 +230,73 @@ void cache64_signs(Plane64& q, uint32_t seed) {
     for (int j = 0; j < 4; ++j) q.neg[j] = negate_mask32(seed, 32u * j);
 }
 
+// Picks the quantiser grid for a codebook: the smallest power-of-two cell count (16...8192) whose
+// cells each hold at most one decision boundary, verified with the very formula the kernel uses.
+// Returns false when no such grid exists (the binary-search kernel is used instead).
+bool quant_grid_for(const float* centroids, int bits, QuantGrid& g) {
+    const int nedges = (1 << bits) - 1;
+    float edges[255];
+    float mingap = 4.0f;
+    for (int k = 0; k < nedges; ++k) {
+        edges[k] = 0.5f * (centroids[k] + centroids[k + 1]);
+        if (!(std::fabs(edges[k]) <= 1.0f)) return false;
+        if (k > 0) mingap = std::fmin(mingap, edges[k] - edges[k - 1]);
+    }
+    if (!(mingap > 0.0f)) return false;
+    for (int cells = 16; cells <= 8192; cells <<= 1) {
+        if (2.25f / cells >= 0.9f * mingap) continue;
+        g.cells = cells;
+        g.scale8 = 8.0f * cells / 2.25f;
+        g.magic8 = 12582912.0f + 4.0f * cells;
+        const uint32_t mask8 = (uint32_t)(cells - 1) << 3;
+        bool ok = true;
+        uint32_t prev = 0;
+        for (int k = 0; k < nedges && ok; ++k) {
+            const uint32_t c = quant_cell8(edges[k], g.scale8, g.magic8, mask8);
+            if (k > 0 && c <= prev) ok = false;       // two boundaries in one cell, or not monotone
+            prev = c;
+        }
+        if (ok) return true;
+    }
+    return false;
+}
+
 template <int BITS, typename T>
 int launch_turbo_encode(int dim, uint32_t seed, const void* in, void* codes, void* scales, int64_t count,
                         cudaStream_t s) {
     Codebook<BITS> book;
     if (!fetch_book<BITS>(dim, book))
         return fail(PITCH_ERR_INVALID_INPUT, "no TurboQuant codebook for dim %d, bits %d", dim, BITS);
-    if (dim < 32)
+    if (dim < 32) {
         turbo_encode_kernel<BITS, T, true><<<vec_grid(count, dim), VEC_THREADS, 0, s>>>(
             static_cast<const T*>(in), static_cast<uint32_t*>(codes), static_cast<float*>(scales), count, dim, seed,
             rsqrt_dim(dim), aligned16(in) ? 1 : 0, book);
-    else
-        turbo_encode_kernel<BITS, T, false><<<vec_grid(count, dim), VEC_THREADS, 0, s>>>(
+        return PITCH_OK;
+    }
+    QuantGrid grid;
+    if (quant_grid_for(book.c, BITS, grid)) {
+        // table-driven quantiser, CTAs loop over warp tiles
+        int64_t ctas = vec_grid(count, dim);
+        const int64_t cap = (int64_t)sm_count() * 8;
+        if (ctas > cap) ctas = cap;
+        const int smem = grid.cells * 8;
+        if (smem > 16 * 1024) {
+            static bool configured[64] = {false};
+            int dev = 0;
+            cudaGetDevice(&dev);
+            if (dev >= 0 && dev < 64 && !configured[dev]) {
+                cudaFuncSetAttribute(turbo_encode_grid_kernel<BITS, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+                configured[dev] = true;
+            }
+        }
+        turbo_encode_grid_kernel<BITS, T><<<(unsigned)ctas, VEC_THREADS, smem, s>>>(
             static_cast<const T*>(in), static_cast<uint32_t*>(codes), static_cast<float*>(scales), count, dim, seed,
-            rsqrt_dim(dim), aligned16(in) ? 1 : 0, book);
+            rsqrt_dim(dim), aligned16(in) ? 1 : 0, grid, book);
+        return PITCH_OK;
+    }
+    turbo_encode_kernel<BITS, T, false><<<vec_grid(count, dim), VEC_THREADS, 0, s>>>(
+        static_cast<const T*>(in), static_cast<uint32_t*>(codes), static_cast<float*>(scales), count, dim, seed,
+        rsqrt_dim(dim), aligned16(in) ? 1 : 0, book);
     return PITCH_OK;
 }
 

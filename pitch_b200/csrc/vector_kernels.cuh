@@ -150,6 +150,108 @@ turbo_encode_kernel(const T* __restrict__ in, uint32_t* __restrict__ codes, floa
 }
 
 // ------------------------------------------------------------------------------------------
+// TurboQuant encode, dim >= 32, table-driven quantiser.
+//
+// Same arithmetic as turbo_encode_kernel up to the rotated coordinate u; only the search differs.
+// The code of u is the number of decision boundaries strictly below u.  A uniform grid of M
+// cells over [-1.125, 1.125] is laid over the boundaries, fine enough that no cell holds two of
+// them (the host checks this and picks M).  cell(u) is read from the mantissa of
+// fma(u, 8M/2.25, 1.5*2^23 + 4M), a monotone function of u, so every boundary in an earlier
+// cell is below u and every boundary in a later cell is above: code = base[cell] + (u > edge[cell])
+// with base[cell] = boundaries in earlier cells and edge[cell] = the cell's own boundary or +inf.
+// One 8-byte shared load and one compare replace the BITS-step binary search; the result is
+// identical for every u, ties included.  CTAs loop over warp tiles so the table is built once.
+// ------------------------------------------------------------------------------------------
+struct QuantGrid {
+    int cells;        // M, a power of two
+    float scale8;     // 8 * M / 2.25
+    float magic8;     // 1.5 * 2^23 + 4 * M
+};
+
+__host__ __device__ __forceinline__ uint32_t quant_cell8(float u, float scale8, float magic8, uint32_t mask8) {
+#ifdef __CUDA_ARCH__
+    return __float_as_uint(__fmaf_rn(u, scale8, magic8)) & mask8;      // byte offset of the cell's entry
+#else
+    float t = fmaf(u, scale8, magic8);
+    uint32_t b;
+    memcpy(&b, &t, 4);
+    return b & mask8;
+#endif
+}
+
+template <int BITS, typename T>
+__global__ void __launch_bounds__(VEC_THREADS)
+turbo_encode_grid_kernel(const T* __restrict__ in, uint32_t* __restrict__ codes, float* __restrict__ norms,
+                         int64_t count, int dim, uint32_t seed, float rs, int vec_ok, const QuantGrid grid,
+                         const Codebook<BITS> book) {
+    extern __shared__ __align__(16) unsigned char dyn[];            // [cells] x {float edge, uint base}
+    __shared__ float s_edges[1 << BITS];
+    __shared__ int s_cell_of_edge[1 << BITS];
+    __shared__ uint32_t s_neg[32];
+    __shared__ __align__(16) unsigned char s_stage[VEC_WARPS][WarpStage<T, 32>::BYTES];
+    constexpr int NEDGES = (1 << BITS) - 1;
+    const uint32_t mask8 = (uint32_t)(grid.cells - 1) << 3;
+    for (int k = threadIdx.x; k < NEDGES; k += VEC_THREADS) {
+        const float e = 0.5f * (book.c[k] + book.c[k + 1]);
+        s_edges[k] = e;
+        s_cell_of_edge[k] = (int)(quant_cell8(e, grid.scale8, grid.magic8, mask8) >> 3);
+    }
+    init_negate_masks(s_neg, seed, dim, threadIdx.x, VEC_THREADS);
+    __syncthreads();
+    for (int j = threadIdx.x; j < grid.cells; j += VEC_THREADS) {
+        int lo = 0, hi = NEDGES;                                    // first boundary whose cell is >= j
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (s_cell_of_edge[mid] < j) lo = mid + 1; else hi = mid;
+        }
+        const bool own = lo < NEDGES && s_cell_of_edge[lo] == j;
+        *reinterpret_cast<float2*>(dyn + j * 8) =
+            make_float2(own ? s_edges[lo] : __int_as_float(0x7F800000), __uint_as_float((uint32_t)lo));
+    }
+    __syncthreads();
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const TileGeom<false> g(dim, BITS);
+    const int sub = lane & (g.tpv - 1);
+    const uint32_t neg = s_neg[sub];
+    const float2 rs2 = make_float2(rs, rs), sc2 = make_float2(grid.scale8, grid.scale8), mg2 = make_float2(grid.magic8, grid.magic8);
+    const int64_t tiles = (count + g.vpw - 1) / g.vpw;
+    for (int64_t tile = (int64_t)blockIdx.x * VEC_WARPS + warp; tile < tiles; tile += (int64_t)gridDim.x * VEC_WARPS) {
+        const int64_t v0 = tile * g.vpw;
+        const int64_t v = v0 + lane / g.tpv;
+        const bool valid = v < count;
+        float x[32];
+        load_lane_coords<T, false>(in, v0, count, dim, g, vec_ok != 0, s_stage[warp], lane, valid, v, x);
+
+        // norm: squares, then the balanced adjacent-pair tree (same order as tree_sum_regs + lanes_sum)
+        float t[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) t[i] = x[i] * x[i];
+        const float norm = sqrtf(lanes_sum(tree_sum_regs(t), g.tpv));
+        const float inv = norm > 0.0f ? 1.0f / norm : 0.0f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) x[i] = flip_if(x[i], neg, i) * inv;
+        wht_regs(x, 32);
+        wht_lanes(x, g.tpv, lane);
+
+        uint32_t w[BITS];
+#pragma unroll
+        for (int k = 0; k < BITS; ++k) w[k] = 0;
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+            const float2 u = __fmul2_rn(make_float2(x[i], x[i + 1]), rs2);
+            const float2 tt = __ffma2_rn(u, sc2, mg2);
+            const float2 e0 = *reinterpret_cast<const float2*>(dyn + (__float_as_uint(tt.x) & mask8));
+            const float2 e1 = *reinterpret_cast<const float2*>(dyn + (__float_as_uint(tt.y) & mask8));
+            insert_code<BITS>(w, i, __float_as_uint(e0.y) + (u.x > e0.x ? 1u : 0u));
+            insert_code<BITS>(w, i + 1, __float_as_uint(e1.y) + (u.y > e1.x ? 1u : 0u));
+        }
+        store_lane_words<BITS, false>(codes, v, sub, dim, g, valid, w);
+        if (valid && sub == 0) norms[v] = norm;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
 // TurboQuant decode: centroid lookup, WHT, sign, 1/sqrt(d), norm.
 // reference/pitch_reference.py:104-107, PITCHKernels.metal:154-174.
 // ------------------------------------------------------------------------------------------
