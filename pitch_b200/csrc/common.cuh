@@ -142,27 +142,47 @@ __device__ __forceinline__ void wht_regs(float (&x)[N], int limit) {
 #pragma unroll
     for (int h = 1; h < N; h <<= 1) {
         if (h < limit) {
+            if (h == 1) {
 #pragma unroll
-            for (int i = 0; i < N; ++i) {
-                if (!(i & h)) {
-                    const float a = x[i], b = x[i | h];
+                for (int i = 0; i < N; i += 2) {
+                    const float a = x[i], b = x[i + 1];
                     x[i] = a + b;
-                    x[i | h] = a - b;
+                    x[i + 1] = a - b;
+                }
+            } else {
+                // adjacent pairs (x[2j], x[2j+1]) go through the same butterfly: packed fp32x2 add, and
+                // a - b as fma(b, -1, a), each component one IEEE rounding like the scalar form
+#pragma unroll
+                for (int i = 0; i < N; i += 2) {
+                    if (!(i & h)) {
+                        const float2 a = make_float2(x[i], x[i + 1]), b = make_float2(x[i | h], x[(i | h) + 1]);
+                        const float2 sum = __fadd2_rn(a, b);
+                        const float2 dif = __ffma2_rn(b, make_float2(-1.0f, -1.0f), a);
+                        x[i] = sum.x; x[i + 1] = sum.y;
+                        x[i | h] = dif.x; x[(i | h) + 1] = dif.y;
+                    }
                 }
             }
         }
     }
 }
 
-// Stages across lanes: lane bit m corresponds to element bit m * N.
+// Stages across lanes: lane bit m corresponds to element bit m * N.  The lane whose bit m is set
+// holds the upper half: it needs (partner - own), the other (own + partner); both are
+// fma(own, +-1, partner), one rounding.
 template <int N>
 __device__ __forceinline__ void wht_lanes(float (&x)[N], int lanes_per_vector, int lane) {
     for (int m = 1; m < lanes_per_vector; m <<= 1) {
-        const bool upper = (lane & m) != 0;
+        const float sg = (lane & m) ? -1.0f : 1.0f;
+        const float2 s2 = make_float2(sg, sg);
 #pragma unroll
-        for (int i = 0; i < N; ++i) {
-            const float o = __shfl_xor_sync(FULL, x[i], m);
-            x[i] = upper ? (o - x[i]) : (x[i] + o);
+        for (int i = 0; i < N; i += 2) {
+            float2 o;
+            o.x = __shfl_xor_sync(FULL, x[i], m);
+            o.y = __shfl_xor_sync(FULL, x[i + 1], m);
+            const float2 r = __ffma2_rn(make_float2(x[i], x[i + 1]), s2, o);
+            x[i] = r.x;
+            x[i + 1] = r.y;
         }
     }
 }
