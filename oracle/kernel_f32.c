@@ -11,7 +11,7 @@
  * bit for bit on codes, and so that the count of codes on which float32 and
  * float64 disagree ("boundary ties") can be predicted on the CPU.
  *
- * Two deliberate, documented differences from the Metal text:
+ * Deliberate, documented differences from the Metal text:
  *  - the sum of squares is a balanced pairwise tree over ADJACENT elements
  *    (level 1 adds s[2j]+s[2j+1], ...) where PITCHKernels.metal:58-69 pairs
  *    element i with i+dim/2.  Both are balanced binary trees with identical
@@ -19,6 +19,10 @@
  *    over GPU lanes.
  *  - 1/sqrt(dim) is the correctly rounded float32 of the exact value (Metal's
  *    rsqrt is approximate).
+ *  - PolarQuant encode scales the radius by levels/rmax (one division per
+ *    vector) and the angle by bins/(2*pi) (one multiplication, a negative bin
+ *    index wrapping around) where PITCHKernels.metal:207-214 divides per pair;
+ *    the same real-number formula, two float roundings placed differently.
  *
  * Parity status: PINNED against the reference's golden fixtures within the
  * reference's own float32-vs-float64 tolerances (tests/test_oracle_golden.py):
@@ -35,6 +39,7 @@
 
 #define PITCH_MAX_DIM 1024
 static const float TWO_PI_F = 6.28318530717958647692f;
+static const float INV_TWO_PI_F = 0.15915494309189533577f;
 
 /* PITCHKernels.metal:26-31 */
 static inline uint32_t pcg_hash(uint32_t v) {
@@ -159,14 +164,17 @@ void pitch_oracle_polar_encode(const float* in, int64_t count, int dim, int bits
             rmax = fmaxf(rmax, r[p]);
         }
         const float safe = (rmax > 0.0f) ? rmax : 1.0f;
+        const float radius_scale = (float)radius_levels / safe;              /* one division per vector */
+        const float angle_scale = (float)angle_bins * INV_TWO_PI_F;          /* bins per radian */
         for (int p = 0; p < dim / 2; ++p) {
             const float a = s[2 * p] * rs, b = s[2 * p + 1] * rs;
-            float q = floorf(r[p] / safe * (float)radius_levels + 0.5f);
+            const float scaled = r[p] * radius_scale;
+            float q = floorf(scaled + 0.5f);
             q = fminf(fmaxf(q, 0.0f), (float)radius_levels);
             c[2 * p] = (uint32_t)q;
-            float theta = atan2f(b, a);
-            if (theta < 0.0f) theta += TWO_PI_F;
-            c[2 * p + 1] = (uint32_t)floorf(theta / TWO_PI_F * (float)angle_bins + 0.5f) & (angle_bins - 1u);
+            /* theta in (-pi, pi]: a negative bin index wraps to the bin of theta + 2*pi */
+            const float turns = atan2f(b, a) * angle_scale;
+            c[2 * p + 1] = (uint32_t)(int32_t)floorf(turns + 0.5f) & (angle_bins - 1u);
         }
         pack_vector(c, codes + v * words, dim, bits);
         scales[v] = rmax;

@@ -108,16 +108,16 @@ __device__ __forceinline__ void append_vector_cta(const T* __restrict__ x_in, ui
         float rmax = 0.0f;
         for (int k = 0; k < (int)((blockDim.x + 31) >> 5); ++k) rmax = fmaxf(rmax, s_red[k]);
         const float safe = rmax > 0.0f ? rmax : 1.0f;
-        const float RL = (float)((1u << bits) - 1u), NB = (float)(1u << bits);
+        const float RL = (float)((1u << bits) - 1u);
+        const float radius_scale = RL / safe, angle_scale = (float)(1u << bits) * INV_TWO_PI_F;
         if (active) {
             if ((tid & 1) == 0) {
-                float q = floorf(r / safe * RL + 0.5f);
+                float q = floorf(r * radius_scale + 0.5f);
                 q = fminf(fmaxf(q, 0.0f), RL);
                 code = (uint32_t)q;
             } else {
-                float theta = atan2f(c, a);
-                if (theta < 0.0f) theta += TWO_PI_F;
-                code = (uint32_t)floorf(theta / TWO_PI_F * NB + 0.5f) & ((1u << bits) - 1u);
+                const float theta = atan2f(c, a);
+                code = (uint32_t)(int)floorf(theta * angle_scale + 0.5f) & ((1u << bits) - 1u);
             }
         }
         scale = rmax;

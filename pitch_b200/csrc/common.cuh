@@ -12,6 +12,7 @@ namespace pitch {
 
 constexpr unsigned FULL = 0xFFFFFFFFu;
 constexpr float TWO_PI_F = 6.28318530717958647692f;
+constexpr float INV_TWO_PI_F = 0.15915494309189533577f;
 
 // ------------------------------------------------------------------------------------------
 // Element types of the full-precision side

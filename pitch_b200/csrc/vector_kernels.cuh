@@ -332,7 +332,8 @@ polar_encode_kernel(const T* __restrict__ in, uint32_t* __restrict__ codes, floa
     rmax = lanes_max(rmax, g.tpv);
     const float safe = rmax > 0.0f ? rmax : 1.0f;
     constexpr float RL = (float)((1 << BITS) - 1);
-    constexpr float NB = (float)(1 << BITS);
+    constexpr float ANGLE_SCALE = (float)(1 << BITS) * INV_TWO_PI_F;      // bins per radian (power of two x rounded 1/2pi)
+    const float radius_scale = RL / safe;                                 // one division per vector
 
     uint32_t w[BITS];
 #pragma unroll
@@ -340,12 +341,12 @@ polar_encode_kernel(const T* __restrict__ in, uint32_t* __restrict__ codes, floa
 #pragma unroll
     for (int p = 0; p < 16; ++p) {
         if (2 * p < g.e()) {
-            float q = floorf(r[p] / safe * RL + 0.5f);
+            float q = floorf(r[p] * radius_scale + 0.5f);
             q = fminf(fmaxf(q, 0.0f), RL);
             insert_code<BITS>(w, 2 * p, (uint32_t)q);
-            float theta = atan2f(x[2 * p + 1], x[2 * p]);
-            if (theta < 0.0f) theta += TWO_PI_F;
-            const uint32_t tq = (uint32_t)floorf(theta / TWO_PI_F * NB + 0.5f) & ((1u << BITS) - 1u);
+            // angle in (-pi, pi]: a negative bin index wraps to the same bin as theta + 2*pi
+            const float theta = atan2f(x[2 * p + 1], x[2 * p]);
+            const uint32_t tq = (uint32_t)(int)floorf(theta * ANGLE_SCALE + 0.5f) & ((1u << BITS) - 1u);
             insert_code<BITS>(w, 2 * p + 1, tq);
         }
     }
@@ -361,13 +362,14 @@ template <int BITS, typename T, bool SMALL>
 __global__ void __launch_bounds__(VEC_THREADS)
 polar_decode_kernel(const uint32_t* __restrict__ codes, const float* __restrict__ scales, T* __restrict__ out,
                     int64_t count, int dim, uint32_t seed, float rs, int vec_ok) {
-    __shared__ float s_cos[1 << BITS], s_sin[1 << BITS];
+    __shared__ float s_cos[1 << BITS], s_sin[1 << BITS], s_ratio[1 << BITS];
     __shared__ uint32_t s_neg[32];
     __shared__ __align__(16) unsigned char s_stage[VEC_WARPS][WarpStage<T, 32>::BYTES];
     for (int k = threadIdx.x; k < (1 << BITS); k += VEC_THREADS) {
         const float theta = (float)k / (float)(1 << BITS) * TWO_PI_F;
         s_cos[k] = cosf(theta);
         s_sin[k] = sinf(theta);
+        s_ratio[k] = (float)k / (float)((1 << BITS) - 1);                 // radius code / levels, the IEEE quotient
     }
     init_negate_masks(s_neg, seed, dim, threadIdx.x, VEC_THREADS);
     __syncthreads();
@@ -383,13 +385,12 @@ polar_decode_kernel(const uint32_t* __restrict__ codes, const float* __restrict_
     uint32_t w[BITS];
     load_lane_words<BITS, SMALL>(codes, v, sub, dim, g, valid, w);
     const float scale = valid ? __ldg(scales + v) : 0.0f;
-    constexpr float RL = (float)((1 << BITS) - 1);
 
     float x[32];
 #pragma unroll
     for (int p = 0; p < 16; ++p) {
         if (2 * p < g.e()) {
-            const float r = (float)extract_code<BITS>(w, 2 * p) / RL * scale;
+            const float r = s_ratio[extract_code<BITS>(w, 2 * p)] * scale;
             const uint32_t tq = extract_code<BITS>(w, 2 * p + 1);
             x[2 * p] = r * s_cos[tq];
             x[2 * p + 1] = r * s_sin[tq];
