@@ -71,6 +71,7 @@ class KVCache:
         self.capacity = (int(capacity) + 127) // 128 * 128      # keeps every segment stride 16-byte aligned
         self.out_dtype = torch_dtype(out_dtype)
         self.tokens = 0
+        self._desc_cache = None
         self.planes = [self._make_plane("keys", key_config), self._make_plane("values", value_config)]
         codebooks.register_all()
 
@@ -90,24 +91,37 @@ class KVCache:
 
     # ------------------------------------------------------------------ descriptors
     def _desc(self, tokens: int) -> _native.CacheDesc:
-        d = _native.CacheDesc()
-        d.dim = self.dim
-        d.out_dtype = native_dtype(self.out_dtype)
-        d.segments = self.segments
+        """The C descriptor of this cache.  Buffers never move, so it is filled once and only the
+        token count changes from call to call (this runs on the per-token path)."""
+        d = self._desc_cache
+        if d is None:
+            d = _native.CacheDesc()
+            d.dim = self.dim
+            d.out_dtype = native_dtype(self.out_dtype)
+            d.segments = self.segments
+            d.n_planes = len(self.planes)
+            for i, pl in enumerate(self.planes):
+                q = d.planes[i]
+                q.kind = pl.kind
+                q.bits = pl.config.bits
+                q.group_size = pl.config.group_size if pl.is_channel else 0
+                q.seed = 0 if pl.is_channel else pl.config.seed
+                q.codes = pl.codes.data_ptr()
+                q.codes_seg_stride = pl.codes.stride(0) * pl.codes.element_size()
+                q.side = pl.side.data_ptr()
+                q.side_seg_stride = pl.side.stride(0) * pl.side.element_size()
+                q.out = pl.out.data_ptr()
+                q.out_seg_stride = pl.out.stride(0) * pl.out.element_size()
+            self._desc_cache = d
+            self._desc_ref = ctypes.byref(d)
+            src = (_native.AppendSrc * 4)()
+            for i, pl in enumerate(self.planes):
+                if pl.residual is not None:
+                    src[i].residual = pl.residual.data_ptr()
+                    src[i].residual_seg_stride = pl.residual.stride(0) * 4
+            self._src_cache = src
+            self._lib = _native.lib()
         d.tokens = tokens
-        d.n_planes = len(self.planes)
-        for i, pl in enumerate(self.planes):
-            q = d.planes[i]
-            q.kind = pl.kind
-            q.bits = pl.config.bits
-            q.group_size = pl.config.group_size if pl.is_channel else 0
-            q.seed = 0 if pl.is_channel else pl.config.seed
-            q.codes = pl.codes.data_ptr()
-            q.codes_seg_stride = pl.codes.stride(0) * pl.codes.element_size()
-            q.side = pl.side.data_ptr()
-            q.side_seg_stride = pl.side.stride(0) * pl.side.element_size()
-            q.out = pl.out.data_ptr()
-            q.out_seg_stride = pl.out.stride(0) * pl.out.element_size()
         return d
 
     # ------------------------------------------------------------------ writing
@@ -142,18 +156,18 @@ class KVCache:
             done += step
 
     def _append_piece(self, keys, values, first: int, n: int, stream) -> None:
-        desc = self._desc(self.tokens)
-        src = (_native.AppendSrc * 4)()
-        for i, (pl, x) in enumerate(zip(self.planes, (keys, values))):
-            esz = x.element_size()
-            src[i].input = x.data_ptr() + first * self.dim * esz
-            src[i].input_seg_stride = x.stride(0) * esz
-            if pl.residual is not None:
-                src[i].residual = pl.residual.data_ptr()
-                src[i].residual_seg_stride = pl.residual.stride(0) * 4
-        st = _native.lib().pitch_enqueue_cache_append(ctypes.byref(desc), src, native_dtype(keys.dtype), n,
-                                                      stream_handle(stream, self.device))
-        _native.check(st)
+        self._desc(self.tokens)
+        src = self._src_cache
+        esz = keys.element_size()
+        off = first * self.dim * esz
+        src[0].input = keys.data_ptr() + off
+        src[0].input_seg_stride = keys.stride(0) * esz
+        src[1].input = values.data_ptr() + off
+        src[1].input_seg_stride = values.stride(0) * esz
+        st = self._lib.pitch_enqueue_cache_append(self._desc_ref, src, native_dtype(keys.dtype), n,
+                                                  stream_handle(stream, self.device))
+        if st:
+            _native.check(st)
 
     def prefill(self, keys, values, stream=None) -> None:
         """Bulk-encodes ``[segments, T, dim]`` tensors into an empty cache with the stand-alone
@@ -205,9 +219,10 @@ class KVCache:
         once the stream reaches this point)."""
         if self.tokens < 1:
             raise InvalidInput("the cache is empty")
-        desc = self._desc(self.tokens)
-        st = _native.lib().pitch_enqueue_cache_decode(ctypes.byref(desc), stream_handle(stream, self.device))
-        _native.check(st)
+        self._desc(self.tokens)
+        st = self._lib.pitch_enqueue_cache_decode(self._desc_ref, stream_handle(stream, self.device))
+        if st:
+            _native.check(st)
         return tuple(pl.out[:, :self.tokens] for pl in self.planes)
 
     # ------------------------------------------------------------------ accounting

@@ -11,6 +11,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 #include <string>
 
@@ -167,28 +168,29 @@ unsigned vec_grid(int64_t count, int dim) {
 
 // Persistent whole-cache decode: one CTA per SM, opt-in dynamic shared memory.
 int sm_count() {
-    static int cached[64] = {0};
+    static std::atomic<int> cached[64];
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) dev = 0;
-    if (cached[dev] == 0) {
-        int n = 0;
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) n = 148;
-        cached[dev] = n;
+        cached[dev].store(n, std::memory_order_relaxed);     // idempotent: racing threads store the same value
     }
-    return cached[dev];
+    return n;
 }
 
 template <typename T, int D, int BITS>
 int launch_cache64_impl(const Cache64Params& p, cudaStream_t s) {
-    static bool configured[64] = {false};
+    static std::atomic<bool> configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
     constexpr int smem = cache64_smem_bytes<T>();
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (dev >= 0 && dev < 64 && !configured[dev].load(std::memory_order_acquire)) {
+        // idempotent: two threads racing here both set the same attribute
         if (cudaFuncSetAttribute(cache_decode_kernel<T, D, BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
             return launch_status(false, "cache_decode (shared memory opt-in)");
-        configured[dev] = true;
+        configured[dev].store(true, std::memory_order_release);
     }
     const int64_t work = (int64_t)p.segments * (p.full_items > 0 ? p.full_items : 1);
     int64_t ctas = ceil_div(work, CD_WARPS);
@@ -281,12 +283,12 @@ int launch_turbo_encode(int dim, uint32_t seed, const void* in, void* codes, voi
         if (ctas > cap) ctas = cap;
         const int smem = grid.cells * 8;
         if (smem > 16 * 1024) {
-            static bool configured[64] = {false};
+            static std::atomic<bool> configured[64];
             int dev = 0;
             cudaGetDevice(&dev);
-            if (dev >= 0 && dev < 64 && !configured[dev]) {
+            if (dev >= 0 && dev < 64 && !configured[dev].load(std::memory_order_acquire)) {
                 cudaFuncSetAttribute(turbo_encode_grid_kernel<BITS, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-                configured[dev] = true;
+                configured[dev].store(true, std::memory_order_release);
             }
         }
         turbo_encode_grid_kernel<BITS, T><<<(unsigned)ctas, VEC_THREADS, smem, s>>>(

@@ -210,3 +210,16 @@ def test_gather_fails_cleanly_when_a_rank_is_missing():
     outs = [p.communicate(timeout=120) for p in procs]
     assert procs[1].returncode == 3
     assert procs[0].returncode not in (0, None), outs     # the survivor gets an error, it does not hang
+
+
+# ---------------------------------------------------------------- benchmark bookkeeping
+def test_bench_byte_accounting_matches_the_published_workload():
+    """Algorithmic bytes of one whole-cache decode of configuration 4."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bench", ROOT / "bench.py")
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    rd, wr = bench.step_bytes(48, 32768)
+    assert (rd, wr) == (113_246_208, 402_653_184) and rd + wr == 515_899_392
+    rd1, wr1 = bench.step_bytes(1, 65)                       # a partial second group still costs a full range block
+    assert rd1 == 65 * 32 + 2 * 256 + 65 * 32 + 65 * 4 and wr1 == 2 * 65 * 64 * 2
