@@ -72,7 +72,9 @@ class KVCache:
         self.out_dtype = torch_dtype(out_dtype)
         self.tokens = 0
         self._desc_cache = None
+        self._float_dtypes = (torch.float32, torch.float16, torch.bfloat16)
         self.planes = [self._make_plane("keys", key_config), self._make_plane("values", value_config)]
+        self._piece_limit = min([pl.config.group_size for pl in self.planes if pl.is_channel] + [65535])
         codebooks.register_all()
 
     def _make_plane(self, name: str, cfg) -> _Plane:
@@ -131,7 +133,8 @@ class KVCache:
             raise InvalidInput(f"{name} must be a contiguous CUDA tensor")
         if x.dim() != 3 or x.shape[0] != self.segments or x.shape[2] != self.dim:
             raise InvalidInput(f"{name} must have shape [segments={self.segments}, n_new, dim={self.dim}]")
-        torch_dtype(x.dtype)
+        if x.dtype not in self._float_dtypes:
+            torch_dtype(x.dtype)          # raises with the list of accepted types
         return x
 
     def append(self, keys, values, stream=None) -> None:
@@ -146,7 +149,7 @@ class KVCache:
             raise InvalidInput("n_new must be at least 1")
         if self.tokens + n_new > self.capacity:
             raise InvalidInput(f"cache holds {self.tokens} of {self.capacity} tokens; cannot append {n_new}")
-        limit = min([pl.config.group_size for pl in self.planes if pl.is_channel] + [65535])
+        limit = self._piece_limit           # new tokens of one launch must fall into one per-channel group
         done = 0
         while done < n_new:
             room = limit - (self.tokens % limit) if limit != 65535 else limit

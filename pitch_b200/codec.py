@@ -32,11 +32,23 @@ def _torch():
     return torch
 
 
+_NATIVE_BY_TORCH: dict = {}
+
+
 def native_dtype(dtype) -> int:
     """``pitch_dtype`` of a torch dtype / its name; float32 for anything that is not a float type
     (raw byte buffers)."""
+    try:
+        return _NATIVE_BY_TORCH[dtype]
+    except (KeyError, TypeError):
+        pass
     name = str(dtype).replace("torch.", "")
-    return _DTYPE_NAMES.get(name, _native.F32)
+    code = _DTYPE_NAMES.get(name, _native.F32)
+    try:
+        _NATIVE_BY_TORCH[dtype] = code
+    except TypeError:
+        pass
+    return code
 
 
 def torch_dtype(dtype):
