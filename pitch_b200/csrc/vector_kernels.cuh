@@ -252,6 +252,43 @@ turbo_encode_grid_kernel(const T* __restrict__ in, uint32_t* __restrict__ codes,
 }
 
 // ------------------------------------------------------------------------------------------
+// Decode tail for dim >= 256 (8, 16 or 32 lanes per vector): the Walsh-Hadamard stages above
+// coordinate bit 4 go through shared memory instead of lane shuffles.  Each lane writes its 32
+// contiguous coordinates as a row of a padded warp tile and reads the tile back transposed, so
+// that it then holds coordinates j*32 + lane (j = 0...31): stages 32, 64, ... become register
+// butterflies over j, in the same order as before.  In that layout every j is 32 consecutive
+// coordinates across the warp, so the result is stored straight to global memory (128 contiguous
+// bytes per instruction for float32) and the output staging of the general path is not needed.
+// The float operations, and their order, are those of the general path.
+// ------------------------------------------------------------------------------------------
+template <typename T, bool WITH_NORM>
+__device__ __forceinline__ void finish_decode_transposed(float (&x)[32], unsigned char* sm, int lane, int tpv,
+                                                         uint32_t my_neg, float my_norm, float rs,
+                                                         T* __restrict__ tile_out, int valid_elems) {
+    typedef WarpStage<float, 32> Stage;
+#pragma unroll
+    for (int q = 0; q < 8; ++q)
+        *reinterpret_cast<float4*>(sm + lane * Stage::PITCHB + q * 16) =
+            make_float4(x[4 * q], x[4 * q + 1], x[4 * q + 2], x[4 * q + 3]);
+    // the row's pad carries what the transposed side needs to know about the row: the norm of the
+    // vector it belongs to and the sign word of its 32 coordinates
+    *reinterpret_cast<uint2*>(sm + lane * Stage::PITCHB + Stage::ROWB) = make_uint2(__float_as_uint(my_norm), my_neg);
+    __syncwarp();
+    float y[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) y[j] = *reinterpret_cast<const float*>(sm + j * Stage::PITCHB + lane * 4);
+    wht_regs(y, tpv);                       // row index bit k is coordinate bit 5 + k
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        const uint2 row = *reinterpret_cast<const uint2*>(sm + j * Stage::PITCHB + Stage::ROWB);   // broadcast
+        float v = flip_if(y[j], row.y, lane) * rs;
+        if (WITH_NORM) v = v * __uint_as_float(row.x);
+        if (j * 32 + lane < valid_elems) tile_out[j * 32 + lane] = Elem<T>::from_f32(v);
+    }
+    __syncwarp();
+}
+
+// ------------------------------------------------------------------------------------------
 // TurboQuant decode: centroid lookup, WHT, sign, 1/sqrt(d), norm.
 // reference/pitch_reference.py:104-107, PITCHKernels.metal:154-174.
 // ------------------------------------------------------------------------------------------
@@ -261,7 +298,7 @@ turbo_decode_kernel(const uint32_t* __restrict__ codes, const float* __restrict_
                     int64_t count, int dim, uint32_t seed, float rs, int vec_ok, const Codebook<BITS> book) {
     __shared__ float s_book[1 << BITS];
     __shared__ uint32_t s_neg[32];
-    __shared__ __align__(16) unsigned char s_stage[VEC_WARPS][WarpStage<T, 32>::BYTES];
+    __shared__ __align__(16) unsigned char s_stage[VEC_WARPS][WarpStage<float, 32>::BYTES];   // float rows: also used by the transposed tail
     for (int k = threadIdx.x; k < (1 << BITS); k += VEC_THREADS) s_book[k] = book.c[k];
     init_negate_masks(s_neg, seed, dim, threadIdx.x, VEC_THREADS);
     __syncthreads();
@@ -282,6 +319,12 @@ turbo_decode_kernel(const uint32_t* __restrict__ codes, const float* __restrict_
 #pragma unroll
     for (int i = 0; i < 32; ++i) x[i] = (i < g.e()) ? s_book[extract_code<BITS>(w, i)] : 0.0f;
     wht_regs(x, g.e());
+    if (!SMALL && g.tpv >= 8) {
+        const int64_t left = count - v0;
+        const int valid_elems = (int)(left < g.vpw ? left : g.vpw) * dim;
+        finish_decode_transposed<T, true>(x, s_stage[warp], lane, g.tpv, s_neg[sub], norm, rs, out + v0 * dim, valid_elems);
+        return;
+    }
     wht_lanes(x, g.tpv, lane);
     const uint32_t neg = s_neg[sub];
 #pragma unroll
@@ -364,7 +407,7 @@ polar_decode_kernel(const uint32_t* __restrict__ codes, const float* __restrict_
                     int64_t count, int dim, uint32_t seed, float rs, int vec_ok) {
     __shared__ float s_cos[1 << BITS], s_sin[1 << BITS], s_ratio[1 << BITS];
     __shared__ uint32_t s_neg[32];
-    __shared__ __align__(16) unsigned char s_stage[VEC_WARPS][WarpStage<T, 32>::BYTES];
+    __shared__ __align__(16) unsigned char s_stage[VEC_WARPS][WarpStage<float, 32>::BYTES];   // float rows: also used by the transposed tail
     for (int k = threadIdx.x; k < (1 << BITS); k += VEC_THREADS) {
         const float theta = (float)k / (float)(1 << BITS) * TWO_PI_F;
         s_cos[k] = cosf(theta);
@@ -400,6 +443,12 @@ polar_decode_kernel(const uint32_t* __restrict__ codes, const float* __restrict_
         }
     }
     wht_regs(x, g.e());
+    if (!SMALL && g.tpv >= 8) {
+        const int64_t left = count - v0;
+        const int valid_elems = (int)(left < g.vpw ? left : g.vpw) * dim;
+        finish_decode_transposed<T, false>(x, s_stage[warp], lane, g.tpv, s_neg[sub], 0.0f, rs, out + v0 * dim, valid_elems);
+        return;
+    }
     wht_lanes(x, g.tpv, lane);
     const uint32_t neg = s_neg[sub];
 #pragma unroll
