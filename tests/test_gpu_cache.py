@@ -79,16 +79,19 @@ def test_fused_equals_standalone_decoders(q):
 
 
 @pytest.mark.parametrize("kcfg_name,vcfg_name,d", [("turbo3", "turbo3", 128), ("turbo4", "turbo4", 128),
+                                                     ("chan4", "turbo3", 128), ("chan4g32", "turbo3", 64),
                                                      ("chan4g32", "polar4", 64), ("chan3", "turbo5", 32)])
-def test_general_shapes_take_the_per_segment_path(q, kcfg_name, vcfg_name, d):
-    """Config 5's shape (K and V both TurboQuant, d=128, b in {3,4}) and other combinations."""
+def test_other_cache_shapes(q, kcfg_name, vcfg_name, d):
+    """Config 5's shape (K and V both TurboQuant, d=128, b in {3,4}), per-channel keys at d=128 and
+    3-bit values (all on the one-launch path), and combinations that take one launch per segment."""
     import torch
     from pitch_b200 import ChannelQuantConfig, KVCache, QuantConfig
 
     def cfg(name):
         return {"turbo3": QuantConfig("turboQuant", d, 3), "turbo4": QuantConfig("turboQuant", d, 4),
                 "turbo5": QuantConfig("turboQuant", d, 5), "polar4": QuantConfig("polarQuant", d, 4),
-                "chan4g32": ChannelQuantConfig(d, 4, 32), "chan3": ChannelQuantConfig(d, 3, 64)}[name]
+                "chan4": ChannelQuantConfig(d, 4, 64), "chan4g32": ChannelQuantConfig(d, 4, 32),
+                "chan3": ChannelQuantConfig(d, 3, 64)}[name]
     rng = np.random.default_rng(6)
     S, T = 3, 200
     K, V = make_inputs(rng, S, T, d)

@@ -192,3 +192,29 @@ def test_unaligned_offsets_take_the_scalar_path(q):
     q.enqueue_per_channel_decode(codes, ranges, out, n, ccfg, codes_offset=4, ranges_offset=4, output_offset=4)
     o = out.cpu().numpy()
     assert np.array_equal(o[1: 1 + n * 64], ref_out) and o[0] == -7.0 and np.all(o[1 + n * 64:] == -7.0)
+
+
+def test_more_than_2_to_32_coordinates_in_one_call(q):
+    """The reference rejects count * dim > 2^32 - 1 (Codec.swift:30-32); here indices are 64-bit.
+    4,194,368 vectors of dim 1024 (4.29e9 coordinates) are decoded in one call and both ends of the
+    batch are compared with the float32 oracle."""
+    import torch
+    from pitch_b200 import QuantConfig
+    d, b = 1024, 2
+    n = (1 << 22) + 64
+    assert n * d > 2 ** 32
+    cfg = QuantConfig("turboQuant", d, b)
+    dev = q.device
+    g = torch.Generator(device=dev)
+    g.manual_seed(77)
+    codes = torch.randint(0, 256, (n * cfg.code_stride,), generator=g, device=dev, dtype=torch.uint8)
+    norms = torch.rand((n,), generator=g, device=dev) + 0.5
+    out = torch.empty((n, d), dtype=torch.bfloat16, device=dev)
+    q.enqueue_decode(codes, norms, out, n, cfg)
+    torch.cuda.synchronize()
+    for lo, hi in ((0, 48), (n - 48, n)):
+        c = codes[lo * cfg.code_stride: hi * cfg.code_stride].cpu().numpy()
+        ref = kernel_f32.decode("turboQuant", c, norms[lo:hi].cpu().numpy(), d, b)
+        assert torch.equal(out[lo:hi].cpu(), torch.from_numpy(ref).bfloat16()), (lo, hi)
+    del out, codes
+    torch.cuda.empty_cache()
