@@ -215,6 +215,34 @@ int pitch_enqueue_cache_append(const pitch_cache_desc* desc, const pitch_append_
 int pitch_enqueue_cache_append_noalloc(const pitch_cache_desc* desc, const pitch_append_src* src, int in_dtype,
                                        int64_t n_new, void* stream);
 
+/* Single-token attention computed straight from the compressed cache, without writing the
+ * decoded cache to memory: for every segment s and query r < n_queries
+ *     out[s][r] = softmax_t(scale * <queries[s][r], K_s,t>) . V_s,t      (t < desc->tokens)
+ * where K and V are what pitch_enqueue_cache_decode would reconstruct for plane 0 and plane 1
+ * (before its final rounding to out_dtype).  n_queries (1...8) is the number of query heads that
+ * share one KV head (grouped-query attention).  No counterpart in the reference: its README.md:96
+ * names this fusion ("decoding needs to move inside the attention kernel") as the work that has
+ * to follow the whole-cache decode.
+ *   Supported cache shape: dim 64; plane 0 per-channel, 4 bits, group size a multiple of 32;
+ *   plane 1 TurboQuant, 4 bits.  Anything else returns PITCH_ERR_INVALID_INPUT.  The planes'
+ *   `out` pointers are not used and may be null.
+ *   queries, out: float32 [segments][n_queries][64], 16-byte aligned, device memory.
+ *   workspace: device scratch of at least pitch_cache_attention_workspace(desc, n_queries)
+ *   bytes, 16-byte aligned; its content on entry does not matter, and it may be reused by the
+ *   next stream-ordered call.
+ * Results agree with attention over the decoded float32 cache to about 1e-5 relative L2 (float32
+ * accumulation in a different order, base-2 exponentials). */
+typedef struct pitch_attention_args {
+    const void* queries;
+    void* out;
+    void* workspace;
+    int64_t workspace_bytes;
+    int32_t n_queries;
+    float scale;               /* softmax scale, usually 1/sqrt(dim) */
+} pitch_attention_args;
+int64_t pitch_cache_attention_workspace(const pitch_cache_desc* desc, int n_queries);
+int pitch_enqueue_cache_attention(const pitch_cache_desc* desc, const pitch_attention_args* args, void* stream);
+
 /* 64-bit checksum of `bytes` bytes (multiple of 4) at buf: sum over 32-bit words w_i of
  * (w_i + 1) * (2*i + 1) mod 2^64, ADDED onto *result (a device uint64 the caller zeroes).
  * Used to compare shards across GPUs without moving them; no counterpart in the reference. */

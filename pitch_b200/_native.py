@@ -44,6 +44,12 @@ class CacheDesc(Structure):
                 ("n_planes", c_int32), ("reserved", c_int32), ("planes", Plane * 4)]
 
 
+class AttentionArgs(Structure):
+    """``pitch_attention_args``."""
+    _fields_ = [("queries", c_void_p), ("out", c_void_p), ("workspace", c_void_p), ("workspace_bytes", c_int64),
+                ("n_queries", c_int32), ("scale", c_float)]
+
+
 # name -> (restype, argtypes); every symbol include/pitch_b200.h declares
 PROTOTYPES = {
     "pitch_abi_version": (c_int, []),
@@ -62,6 +68,8 @@ PROTOTYPES = {
     "pitch_enqueue_cache_decode": (c_int, [POINTER(CacheDesc), c_void_p]),
     "pitch_enqueue_cache_append": (c_int, [POINTER(CacheDesc), POINTER(AppendSrc), c_int, c_int64, c_void_p]),
     "pitch_enqueue_cache_append_noalloc": (c_int, [POINTER(CacheDesc), POINTER(AppendSrc), c_int, c_int64, c_void_p]),
+    "pitch_cache_attention_workspace": (c_int64, [POINTER(CacheDesc), c_int]),
+    "pitch_enqueue_cache_attention": (c_int, [POINTER(CacheDesc), POINTER(AttentionArgs), c_void_p]),
     "pitch_enqueue_checksum": (c_int, [Buffer, c_int64, c_void_p, c_void_p]),
 }
 

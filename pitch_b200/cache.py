@@ -228,6 +228,43 @@ class KVCache:
             _native.check(st)
         return tuple(pl.out[:, :self.tokens] for pl in self.planes)
 
+    def attend(self, queries, scale: float | None = None, out=None, stream=None):
+        """Single-token attention over the compressed cache without decoding it to memory:
+        ``queries`` is float32 ``[segments, n_queries, dim]`` (``n_queries`` <= 8: the query
+        heads that share a KV head); returns float32 ``[segments, n_queries, dim]`` with
+        ``softmax_t(scale * q . K_t) . V_t`` over the ``tokens`` tokens held.  ``scale`` defaults
+        to ``1/sqrt(dim)``.  Supported: dim 64, per-channel 4-bit keys (group size a multiple of
+        32), TurboQuant 4-bit values.  Stream-ordered; the scratch buffer is kept by the cache and
+        reused, so calls on one cache must be stream-ordered with respect to each other."""
+        torch = _torch()
+        if self.tokens < 1:
+            raise InvalidInput("the cache is empty")
+        if not (isinstance(queries, torch.Tensor) and queries.is_cuda and queries.is_contiguous()
+                and queries.dtype == torch.float32):
+            raise InvalidInput("queries must be a contiguous float32 CUDA tensor")
+        if queries.dim() != 3 or queries.shape[0] != self.segments or queries.shape[2] != self.dim:
+            raise InvalidInput(f"queries must have shape [segments={self.segments}, n_queries, dim={self.dim}]")
+        n_q = int(queries.shape[1])
+        if out is None:
+            out = torch.empty_like(queries)
+        elif not (isinstance(out, torch.Tensor) and out.is_cuda and out.is_contiguous() and out.dtype == torch.float32
+                  and out.shape == queries.shape):
+            raise InvalidInput("out must be a contiguous float32 CUDA tensor shaped like queries")
+        self._desc(self.tokens)
+        need = self._lib.pitch_cache_attention_workspace(self._desc_ref, n_q)
+        if need < 0:
+            _native.check(1)               # invalid input; the library holds the reason
+        ws = getattr(self, "_attention_ws", None)
+        if ws is None or ws.numel() < need:
+            ws = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=self.device)
+            self._attention_ws = ws
+        args = _native.AttentionArgs(queries.data_ptr(), out.data_ptr(), ws.data_ptr(), ws.numel(), n_q,
+                                     float(scale) if scale is not None else self.dim ** -0.5)
+        st = self._lib.pitch_enqueue_cache_attention(self._desc_ref, ctypes.byref(args), stream_handle(stream, self.device))
+        if st:
+            _native.check(st)
+        return out
+
     # ------------------------------------------------------------------ accounting
     def stored_bytes(self, tokens: int | None = None) -> int:
         """Bytes of packed codes plus side information for ``tokens`` tokens per segment."""

@@ -16,6 +16,7 @@
 #include <string>
 
 #include "append_kernels.cuh"
+#include "attention_kernels.cuh"
 #include "cache_kernels.cuh"
 #include "channel_kernels.cuh"
 #include "common.cuh"
@@ -217,6 +218,20 @@ template <typename T>
 int launch_cache64(const Cache64Params& p, int dim, int bits, cudaStream_t s) {
     if (dim == 64) return bits == 4 ? launch_cache64_impl<T, 64, 4>(p, s) : launch_cache64_impl<T, 64, 3>(p, s);
     return bits == 4 ? launch_cache64_impl<T, 128, 4>(p, s) : launch_cache64_impl<T, 128, 3>(p, s);
+}
+
+template <int R>
+int launch_attention_partial(const AttentionParams& p, cudaStream_t s) {
+    static std::atomic<bool> configured[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev].load(std::memory_order_acquire)) {
+        if (cudaFuncSetAttribute(attention_partial_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES) != cudaSuccess)
+            return launch_status(false, "cache_attention (shared memory opt-in)");
+        configured[dev].store(true, std::memory_order_release);
+    }
+    attention_partial_kernel<R><<<dim3((unsigned)p.splits, (unsigned)p.segments), AT_THREADS, AT_SMEM_BYTES, s>>>(p);
+    return PITCH_OK;
 }
 
 // Fills the geometry of a fast-path launch: `tokens` tokens per segment at head dimension `dim`.
@@ -936,6 +951,111 @@ int pitch_enqueue_cache_append_noalloc(const pitch_cache_desc* d, const pitch_ap
         g_noalloc[dev].tokens = d->tokens + n_new;
     }
     return st;
+}
+
+// -------------------------------------------------------------------------------- attention
+// How a segment's tokens are cut into slices (one CTA each).  Depends on the shape only, so that
+// the workspace size can be computed ahead of the call: slices of 1024 tokens, shorter (down to
+// 256) while the launch would have fewer than about four CTAs per SM, at most 64 slices.
+static void attention_slices(int64_t segments, int64_t tokens, int* splits, int* tokens_per_split) {
+    int64_t tps = 1024;
+    while (tps > 256 && segments * ceil_div(tokens, tps) < 592) tps /= 2;
+    if (ceil_div(tokens, tps) > 64) tps = ceil_div(ceil_div(tokens, 64), 256) * 256;
+    *tokens_per_split = (int)tps;
+    *splits = (int)ceil_div(tokens, tps);
+}
+
+static int check_attention_shape(const pitch_cache_desc* d, int n_queries) {
+    if (d == nullptr) return fail(PITCH_ERR_INVALID_INPUT, "descriptor is null");
+    if (n_queries < 1 || n_queries > AT_MAX_QUERIES)
+        return fail(PITCH_ERR_INVALID_INPUT, "n_queries %d must be in 1...%d", n_queries, AT_MAX_QUERIES);
+    if (d->segments < 1 || d->segments > 65535 || d->tokens < 1 || d->tokens > 0x7FFFFFFF - 1024)
+        return fail(PITCH_ERR_INVALID_INPUT, "segments must be in 1...65535 and tokens in 1...2^31-1025");
+    if (d->dim != 64 || d->n_planes != 2)
+        return fail(PITCH_ERR_INVALID_INPUT, "cache attention needs dim 64 and two planes (keys, values)");
+    const pitch_plane& k = d->planes[0];
+    const pitch_plane& v = d->planes[1];
+    if (k.kind != PITCH_PLANE_CHANNEL || k.bits != 4 || k.group_size < 32 || k.group_size % 32 != 0 || k.group_size > PITCH_MAX_GROUP)
+        return fail(PITCH_ERR_INVALID_INPUT, "cache attention needs per-channel 4-bit keys with a group size that is a multiple of 32");
+    if (v.kind != PITCH_PLANE_TURBO || v.bits != 4)
+        return fail(PITCH_ERR_INVALID_INPUT, "cache attention needs TurboQuant 4-bit values");
+    return PITCH_OK;
+}
+
+int64_t pitch_cache_attention_workspace(const pitch_cache_desc* d, int n_queries) {
+    if (check_attention_shape(d, n_queries)) return -1;
+    int splits, tps;
+    attention_slices(d->segments, d->tokens, &splits, &tps);
+    return d->segments * splits * n_queries * AT_PART_FLOATS * (int64_t)sizeof(float);
+}
+
+int pitch_enqueue_cache_attention(const pitch_cache_desc* d, const pitch_attention_args* a, void* stream) {
+    if (a == nullptr) return fail(PITCH_ERR_INVALID_INPUT, "arguments are null");
+    int st;
+    if ((st = check_attention_shape(d, a->n_queries))) return st;
+    if (!(a->scale > 0.0f) || !std::isfinite(a->scale)) return fail(PITCH_ERR_INVALID_INPUT, "scale must be positive and finite");
+    if (!a->queries || !a->out || !a->workspace) return fail(PITCH_ERR_INVALID_INPUT, "queries, out or workspace is null");
+    if (!aligned16(a->queries) || !aligned16(a->out) || !aligned16(a->workspace))
+        return fail(PITCH_ERR_INVALID_INPUT, "queries, out and workspace must be 16-byte aligned");
+    const int64_t need = pitch_cache_attention_workspace(d, a->n_queries);
+    if (a->workspace_bytes < need)
+        return fail(PITCH_ERR_INVALID_INPUT, "workspace has %lld bytes; needs %lld", (long long)a->workspace_bytes, (long long)need);
+    for (int i = 0; i < 2; ++i) {
+        const pitch_plane& pl = d->planes[i];
+        if (!pl.codes || !pl.side) return fail(PITCH_ERR_INVALID_INPUT, "plane %d: null pointer", i);
+        if (!aligned16(pl.codes) || !aligned16(pl.side) || (pl.codes_seg_stride & 15) || (pl.side_seg_stride & 15))
+            return fail(PITCH_ERR_INVALID_INPUT, "plane %d: pointers and segment strides must be multiples of 16", i);
+        if (d->segments > 1 && (pl.codes_seg_stride < d->tokens * 32 || pl.side_seg_stride < plane_side_bytes(pl, 64, d->tokens)))
+            return fail(PITCH_ERR_INVALID_INPUT, "plane %d: a segment stride is smaller than one segment", i);
+    }
+    const pitch_buffer bufs[5] = {{const_cast<void*>(a->queries), 0, 0}, {a->out, 0, 0}, {a->workspace, 0, 0},
+                                  {d->planes[0].codes, 0, 0}, {d->planes[1].codes, 0, 0}};
+    const char* const names[5] = {"queries", "out", "workspace", "key codes", "value codes"};
+    int dev;
+    if ((st = check_same_device(bufs, names, 5, &dev))) return st;
+    DeviceGuard guard(dev);
+
+    AttentionParams p;
+    memset(&p, 0, sizeof p);
+    p.segments = (int)d->segments;
+    p.tokens = (int)d->tokens;
+    attention_slices(d->segments, d->tokens, &p.splits, &p.tokens_per_split);
+    p.n_queries = a->n_queries;
+    p.group_size = d->planes[0].group_size;
+    p.scale_log2 = (float)((double)a->scale * 1.4426950408889634);
+    p.neg_lo = negate_mask32(d->planes[1].seed, 0);
+    p.neg_hi = negate_mask32(d->planes[1].seed, 32);
+    p.k_codes = static_cast<const unsigned char*>(d->planes[0].codes);
+    p.k_codes_seg = d->planes[0].codes_seg_stride;
+    p.k_ranges = static_cast<const unsigned char*>(d->planes[0].side);
+    p.k_ranges_seg = d->planes[0].side_seg_stride;
+    p.v_codes = static_cast<const unsigned char*>(d->planes[1].codes);
+    p.v_codes_seg = d->planes[1].codes_seg_stride;
+    p.v_norms = static_cast<const unsigned char*>(d->planes[1].side);
+    p.v_norms_seg = d->planes[1].side_seg_stride;
+    p.q = static_cast<const float*>(a->queries);
+    p.work = static_cast<float*>(a->workspace);
+    p.out = static_cast<float*>(a->out);
+    {
+        std::lock_guard<std::mutex> guardb(g_books.lock);
+        if (!g_books.present[6][4]) return fail(PITCH_ERR_INVALID_INPUT, "no TurboQuant codebook for dim 64, bits 4");
+        memcpy(p.book.c, g_books.values[6][4], sizeof(float) * 16);
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (a->n_queries) {
+        case 1: st = launch_attention_partial<1>(p, s); break;
+        case 2: st = launch_attention_partial<2>(p, s); break;
+        case 3: st = launch_attention_partial<3>(p, s); break;
+        case 4: st = launch_attention_partial<4>(p, s); break;
+        case 5: st = launch_attention_partial<5>(p, s); break;
+        case 6: st = launch_attention_partial<6>(p, s); break;
+        case 7: st = launch_attention_partial<7>(p, s); break;
+        default: st = launch_attention_partial<8>(p, s); break;
+    }
+    if (st) return st;
+    if ((st = launch_status(false, "cache_attention"))) return st;
+    attention_combine_kernel<<<(unsigned)p.segments, 32 * p.n_queries, 0, s>>>(p);
+    return launch_status(false, "cache_attention (combine)");
 }
 
 // --------------------------------------------------------------------------------- checksum

@@ -24,7 +24,7 @@ def lib():
 def test_library_exports_every_declared_symbol(lib):
     from pitch_b200 import _native
     header = (ROOT / "include" / "pitch_b200.h").read_text()
-    declared = set(re.findall(r"^\s*(?:int|const char\*)\s+(pitch_\w+)\s*\(", header, flags=re.M))
+    declared = set(re.findall(r"^\s*(?:int|int64_t|const char\*)\s+(pitch_\w+)\s*\(", header, flags=re.M))
     assert declared, "no declarations found in the header"
     assert declared == set(_native.PROTOTYPES), declared ^ set(_native.PROTOTYPES)
     for name in declared:
