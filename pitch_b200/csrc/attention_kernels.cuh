@@ -3,27 +3,42 @@
 // the reference names as what has to come next for long contexts (README.md:96, "decoding needs
 // to move inside the attention kernel").
 //
-// For one segment (layer x KV head) with R query vectors q_r (grouped-query attention: the query
-// heads that share this KV head) and T cached tokens:
+// For one segment (layer x KV head) with up to eight query vectors q_r (grouped-query attention:
+// the query heads that share this KV head) and T cached tokens:
 //
 //   scores   s_r,t = scale * sum_c q_r,c * K_t,c        with K_t,c = code_t,c * step_g,c + lo_g,c
 //                  = sum_c (scale * q_r,c * step_g,c) * code_t,c  +  scale * sum_c q_r,c * lo_g,c
-//            -> per group g of tokens the query is folded into the quantisation grid once
-//               (qk_r,c and a bias qb_r); a score is then a dot product with the 4-bit codes.
+//            -> per group g of tokens the query is folded into the quantisation grid once; a
+//               score is then a dot product with the 4-bit codes plus a bias.
 //   output   o_r = sum_t p_r,t V_t / sum_t p_r,t        with V_t = norm_t/8 * D H cb[codes_t]
 //                = D H ( sum_t p_r,t norm_t cb[codes_t] ) / (8 sum_t p_r,t)
-//            -> centroids are accumulated in the rotated domain and the Walsh-Hadamard transform
-//               and the sign diagonal are applied once per query at the very end, instead of once
-//               per cached token.
+//            -> centroids are accumulated in the rotated domain; the Walsh-Hadamard transform and
+//               the sign diagonal are applied once per query at the very end, not once per token.
 //
-// Kernel 1 (attention_partial_kernel): grid (splits, segments); a CTA of 8 warps walks one slice of
-// the tokens of one segment in tiles of 32 tokens.  For the scores a lane owns a token (its 32 code
-// bytes arrive as two 128-bit loads, the folded query is read from shared memory as broadcasts);
-// softmax is online (running maximum and sum per query, base-2 exponentials); for the value
-// accumulation a lane owns two of the 64 output coordinates: it reads its code byte of every token
-// of the tile from a shared tile and maps it to two centroids through a lane-replicated, conflict
-// free table.  Each CTA writes (max, sum, 64 accumulators) per query to a workspace.
-// Kernel 2 (attention_combine_kernel): merges the slices of a segment, normalises, un-rotates.
+// Both contractions are small matrix products per tile of 32 tokens, and the eight queries of a
+// KV head fill the N = 8 side of the m16n8k16 tensor-core shape exactly:
+//   scores^T [tokens x queries] = codes [tokens x channels] . folded query^T [channels x queries]
+//   out^T    [dims x queries]   = centroids^T [dims x tokens] . weights^T [tokens x queries]
+// Operands are bf16 with float32 accumulation.  float32 quantities are split into bf16 parts
+// (x = hi + mid + lo to 2^-25 for the folded query; hi + lo to 2^-17 for weights and centroids,
+// accumulated as hi*hi + hi*lo + lo*hi), so the result keeps float32-like accuracy.
+//  * key codes become bf16 without a conversion instruction: nibble n placed in the top mantissa
+//    bits of 16.0 reads as 16 + n exactly (one shift and one logic operation per pair of codes);
+//    the constant 16 * sum(folded query) goes into the bias, i.e. the accumulator's initial value;
+//  * value codes of two adjacent tokens are interleaved into one byte per coordinate, and a
+//    lane-replicated (bank-conflict free) table maps that byte to the hi and lo pairs of the two
+//    centroids, already in A-fragment form;
+//  * the score fragment (token rows, two queries per thread) becomes the weight operand of the
+//    second product (token pairs per thread, one query) through movmatrix transposes.
+// Free permutations make this cheap: the order of channels inside the first contraction and of
+// output coordinates in the second is chosen to match how codes sit in their words.
+// Thread (g, t) = (lane / 4, lane % 4).  Rows >= n_queries carry a zero query and are discarded.
+//
+// Kernel 1 (attention_partial_kernel): every warp is on its own.  The tokens of a segment are cut
+// into runs of whole tiles, about one run per resident warp of the GPU; a warp walks its run with
+// online softmax (running maximum and sum per query, base-2 exponentials) and writes (max, sum,
+// 64 accumulators) per query to a workspace.  Apart from the table build there is no barrier.
+// Kernel 2 (attention_combine_kernel): merges the runs of a segment, normalises, un-rotates.
 #pragma once
 
 #include "cache_kernels.cuh"
@@ -34,12 +49,13 @@ namespace pitch {
 constexpr int AT_THREADS = 256;
 constexpr int AT_WARPS = AT_THREADS / 32;
 constexpr int AT_MAX_QUERIES = 8;
-constexpr int AT_PART_FLOATS = 66;                     // per (segment, split, query): max, sum, 64 accumulators
-constexpr int AT_WARP_SMEM = 1024 + 1024 + AT_MAX_QUERIES * 64 * 4 + 32;   // value codes, weights, folded query, bias
+constexpr int AT_PART_FLOATS = 66;                     // per (segment, slice, query): max, sum, 64 accumulators
+constexpr int AT_WARP_SMEM = 8 * 64 * 4 + 512;         // per warp: scaled queries; per-group steps and offsets of the keys
 constexpr int AT_SMEM_BYTES = CD_TABLE_BYTES + AT_WARPS * AT_WARP_SMEM;
+constexpr int AT_COMBINE_WARPS = 8;
 
 struct AttentionParams {
-    int segments, tokens, splits, tokens_per_split;    // tokens_per_split is a multiple of 256
+    int segments, tokens, splits, tokens_per_split;    // a run: tokens_per_split tokens, a multiple of 32
     int n_queries, group_size;
     float scale_log2;                                  // softmax scale * log2(e)
     uint32_t neg_lo, neg_hi;                           // sign diagonal of the values' rotation
@@ -53,201 +69,352 @@ struct AttentionParams {
     Book16 book;                                       // TurboQuant centroids (64, 4)
 };
 
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-    for (int m = 16; m > 0; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, m));
-    return v;
-}
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-    for (int m = 16; m > 0; m >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, m);
-    return v;
-}
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t transpose8x8(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+__device__ __forceinline__ uint32_t bf16_pair(float x0, float x1) {     // lower half = x0
+    const __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+// (x0, x1) -> bf16 pair of heads and bf16 pair of remainders
+__device__ __forceinline__ void split_pair(float x0, float x1, uint32_t& hi, uint32_t& lo) {
+    hi = bf16_pair(x0, x1);
+    lo = bf16_pair(x0 - __uint_as_float(hi << 16), x1 - __uint_as_float(hi & 0xFFFF0000u));
+}
+__device__ __forceinline__ void split_pair3(float x0, float x1, uint32_t& hi, uint32_t& mid, uint32_t& lo) {
+    hi = bf16_pair(x0, x1);
+    const float r0 = x0 - __uint_as_float(hi << 16), r1 = x1 - __uint_as_float(hi & 0xFFFF0000u);
+    mid = bf16_pair(r0, r1);
+    lo = bf16_pair(r0 - __uint_as_float(mid << 16), r1 - __uint_as_float(mid & 0xFFFF0000u));
+}
+// nibbles KB and KB + 4 of a word as the bf16 pair (16 + n_KB, 16 + n_KB+4)
+template <int KB>
+__device__ __forceinline__ uint32_t key_pair(uint32_t w) {
+    const uint32_t s = KB == 0 ? (w << 3) : (w >> (4 * KB - 3));
+    return (s & 0x00780078u) | 0x41804180u;
+}
 
-template <int R>
-__global__ void __launch_bounds__(AT_THREADS, 2)
-attention_partial_kernel(const __grid_constant__ AttentionParams p) {
-    extern __shared__ __align__(1024) unsigned char smem[];
-    unsigned char* table = smem;                                       // entry e, slot l: (c[e & 15], c[e >> 4])
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    unsigned char* mine = smem + CD_TABLE_BYTES + warp * AT_WARP_SMEM;
-    unsigned char* vtile = mine;                                       // [32 tokens][32 code bytes]
-    float* wtile = reinterpret_cast<float*>(mine + 1024);              // [32 tokens][8 weights]
-    float* qk = reinterpret_cast<float*>(mine + 2048);                 // [R][64] folded query
-    float* qb = reinterpret_cast<float*>(mine + 2048 + AT_MAX_QUERIES * 256);   // [R] bias
+struct AttnTile {                 // what thread (g, t) loads for a tile of 32 tokens (two blocks of 16)
+    uint2 k[2][2];                // words 2t, 2t+1 of tokens 16m + g and 16m + g + 8
+    uint32_t v[2][4];             // word g of tokens 16m + {2t, 2t+1, 2t+8, 2t+9}
+    float n[2][2];                // norms of tokens 16m + g and 16m + g + 8
+};
 
-    for (int idx = threadIdx.x; idx < 256 * 32; idx += AT_THREADS) {
-        const int e = idx >> 5;
-        *reinterpret_cast<float2*>(table + idx * 8) = make_float2(p.book.c[e & 15], p.book.c[e >> 4]);
-    }
-    const int64_t seg = blockIdx.y;
-    const int split = blockIdx.x;
-    const int t_begin = split * p.tokens_per_split;
-    int t_end = t_begin + p.tokens_per_split;
-    if (t_end > p.tokens) t_end = p.tokens;
-
-    // this lane's two channels of every query, pre-multiplied by the softmax scale (base 2)
-    float q0[R], q1[R];
+// kp, vp, np point at this thread's first key word pair, value word and norm of the tile.
+template <bool WHOLE>
+__device__ __forceinline__ void load_attn_tile(AttnTile& f, const unsigned char* __restrict__ kp,
+                                               const unsigned char* __restrict__ vp, const float* __restrict__ np,
+                                               int nvalid, int g, int t) {
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-        const float2 v = *reinterpret_cast<const float2*>(p.q + (seg * R + r) * 64 + 2 * lane);
-        q0[r] = v.x * p.scale_log2;
-        q1[r] = v.y * p.scale_log2;
-    }
-    __syncthreads();
-
-    const unsigned char* k_codes = p.k_codes + seg * p.k_codes_seg;
-    const __half* k_ranges = reinterpret_cast<const __half*>(p.k_ranges + seg * p.k_ranges_seg);
-    const unsigned char* v_codes = p.v_codes + seg * p.v_codes_seg;
-    const float* v_norms = reinterpret_cast<const float*>(p.v_norms + seg * p.v_norms_seg);
-    const uint32_t slot = (uint32_t)lane * 8u;
-
-    float m[R], l[R];
-    float2 acc[R];
+    for (int m = 0; m < 2; ++m) {
 #pragma unroll
-    for (int r = 0; r < R; ++r) { m[r] = -INFINITY; l[r] = 0.0f; acc[r] = make_float2(0.0f, 0.0f); }
-    int cur_group = -1;
-
-    for (int t0 = t_begin + warp * 32; t0 < t_end; t0 += AT_WARPS * 32) {
-        const int nvalid = t_end - t0 < 32 ? t_end - t0 : 32;
-        const bool valid = lane < nvalid;
-        // ---- loads of this tile: key codes and value codes of token t0 + lane, its norm
-        uint4 ka = make_uint4(0, 0, 0, 0), kb = ka, va = ka, vb = ka;
-        float norm = 0.0f;
-        if (valid) {
-            const uint4* kp = reinterpret_cast<const uint4*>(k_codes + (int64_t)(t0 + lane) * 32);
-            const uint4* vp = reinterpret_cast<const uint4*>(v_codes + (int64_t)(t0 + lane) * 32);
-            ka = ldg_stream(kp); kb = ldg_stream(kp + 1);
-            va = ldg_stream(vp); vb = ldg_stream(vp + 1);
-            norm = __ldg(v_norms + t0 + lane);
-        }
-        // ---- a new group of tokens: fold the queries into its quantisation grid
-        const int group = t0 / p.group_size;
-        if (group != cur_group) {
-            cur_group = group;
-            const __half2 lo2 = *reinterpret_cast<const __half2*>(k_ranges + (int64_t)group * 128 + 2 * lane);
-            const __half2 hi2 = *reinterpret_cast<const __half2*>(k_ranges + (int64_t)group * 128 + 64 + 2 * lane);
-            const float2 lo = __half22float2(lo2), hi = __half22float2(hi2);
-            const float s0 = step15(lo.x, hi.x), s1 = step15(lo.y, hi.y);
-            __syncwarp();                               // the previous tile's reads of qk are done
-#pragma unroll
-            for (int r = 0; r < R; ++r) {
-                *reinterpret_cast<float2*>(qk + r * 64 + 2 * lane) = make_float2(q0[r] * s0, q1[r] * s1);
-                const float b = warp_sum(q0[r] * lo.x + q1[r] * lo.y);
-                if (lane == 0) qb[r] = b;
+        for (int h = 0; h < 2; ++h) {
+            const int row = 16 * m + 8 * h;
+            f.k[m][h] = make_uint2(0u, 0u);
+            f.n[m][h] = 0.0f;
+            if (WHOLE || row + g < nvalid) {
+                f.k[m][h] = ldg_stream64(reinterpret_cast<const uint2*>(kp + row * 32));
+                f.n[m][h] = __ldg(np + row);
             }
         }
-        *reinterpret_cast<uint4*>(vtile + lane * 32) = va;
-        *reinterpret_cast<uint4*>(vtile + lane * 32 + 16) = vb;
-        __syncwarp();
-
-        // ---- scores of token t0 + lane against every query
-        const uint32_t kw[8] = {ka.x, ka.y, ka.z, ka.w, kb.x, kb.y, kb.z, kb.w};
-        float2 s2[R];
 #pragma unroll
-        for (int r = 0; r < R; ++r) s2[r] = make_float2(0.0f, 0.0f);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            float2 f[4];
-            codes8_to_pairs(kw[j], f);
-#pragma unroll
-            for (int r = 0; r < R; ++r) {
-                const float4 a = *reinterpret_cast<const float4*>(qk + r * 64 + 8 * j);        // broadcast
-                const float4 b = *reinterpret_cast<const float4*>(qk + r * 64 + 8 * j + 4);
-                s2[r] = __ffma2_rn(f[0], make_float2(a.x, a.y), s2[r]);
-                s2[r] = __ffma2_rn(f[1], make_float2(a.z, a.w), s2[r]);
-                s2[r] = __ffma2_rn(f[2], make_float2(b.x, b.y), s2[r]);
-                s2[r] = __ffma2_rn(f[3], make_float2(b.z, b.w), s2[r]);
-            }
+        for (int j = 0; j < 4; ++j) {
+            const int row = 16 * m + (j & 1) + 8 * (j >> 1);
+            f.v[m][j] = 0u;
+            if (WHOLE || row + 2 * t < nvalid) f.v[m][j] = ldg_stream32(reinterpret_cast<const uint32_t*>(vp + row * 32));
         }
-        // ---- online softmax (base 2) and the weights of this tile
-        float w[AT_MAX_QUERIES];
-#pragma unroll
-        for (int r = 0; r < AT_MAX_QUERIES; ++r) w[r] = 0.0f;
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const float s = valid ? (s2[r].x + s2[r].y + qb[r]) : -INFINITY;
-            const float mn = fmaxf(m[r], warp_max(s));          // finite: every tile has a valid token
-            const float corr = fast_exp2(m[r] - mn);            // 0 on the first tile (m = -inf)
-            const float pr = fast_exp2(s - mn);                 // 0 for tokens that do not exist
-            l[r] = l[r] * corr + warp_sum(pr);
-            acc[r].x *= corr;
-            acc[r].y *= corr;
-            m[r] = mn;
-            w[r] = pr * norm;
-        }
-        *reinterpret_cast<float4*>(wtile + lane * 8) = make_float4(w[0], w[1], w[2], w[3]);
-        *reinterpret_cast<float4*>(wtile + lane * 8 + 4) = make_float4(w[4], w[5], w[6], w[7]);
-        __syncwarp();
-
-        // ---- values: this lane accumulates output coordinates 2*lane and 2*lane + 1 over the tile
-#pragma unroll 8
-        for (int t = 0; t < 32; ++t) {
-            const uint32_t byte = vtile[t * 32 + lane];
-            const float2 c = *reinterpret_cast<const float2*>(table + __byte_perm(byte, slot, 0x5504));
-            const float4 wa = *reinterpret_cast<const float4*>(wtile + t * 8);                 // broadcast
-            const float4 wb = *reinterpret_cast<const float4*>(wtile + t * 8 + 4);
-            const float ws[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
-#pragma unroll
-            for (int r = 0; r < R; ++r) {
-                acc[r].x = fmaf(c.x, ws[r], acc[r].x);
-                acc[r].y = fmaf(c.y, ws[r], acc[r].y);
-            }
-        }
-        __syncwarp();
-    }
-
-    // ---- merge the eight warps of the CTA (the table is no longer needed: reuse its space)
-    __syncthreads();
-    float* merge = reinterpret_cast<float*>(smem);                    // [warp][R][66]
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-        float* dst = merge + (warp * R + r) * AT_PART_FLOATS;
-        if (lane == 0) { dst[0] = m[r]; dst[1] = l[r]; }
-        *reinterpret_cast<float2*>(dst + 2 + 2 * lane) = acc[r];
-    }
-    __syncthreads();
-    float* out = p.work + ((seg * p.splits + split) * R) * AT_PART_FLOATS;
-    for (int idx = threadIdx.x; idx < R * 64; idx += AT_THREADS) {
-        const int r = idx >> 6, c = idx & 63;
-        float mm = -INFINITY;
-        for (int wv = 0; wv < AT_WARPS; ++wv) mm = fmaxf(mm, merge[(wv * R + r) * AT_PART_FLOATS]);
-        float a = 0.0f, ll = 0.0f;
-        for (int wv = 0; wv < AT_WARPS; ++wv) {
-            const float* src = merge + (wv * R + r) * AT_PART_FLOATS;
-            const float f = src[0] == -INFINITY ? 0.0f : fast_exp2(src[0] - mm);   // a warp that saw no tile
-            a += src[2 + c] * f;
-            ll += src[1] * f;
-        }
-        out[r * AT_PART_FLOATS + 2 + c] = a;
-        if (c == 0) { out[r * AT_PART_FLOATS] = mm; out[r * AT_PART_FLOATS + 1] = ll; }
     }
 }
 
-// grid = segments, blockDim = 32 * n_queries: one warp per (segment, query).
-__global__ void __launch_bounds__(32 * AT_MAX_QUERIES)
+struct AttnState {
+    float m0, m1, l0, l1;         // running maximum and (per-thread partial) sum of queries 2t and 2t + 1
+    float acc[4][4];              // out^T fragments: [block of 16 coordinates][fragment register]
+};
+
+// One tile: scores, online softmax, value accumulation.  qf: folded query (B fragments, three
+// bf16 parts per 16 channels); bias0/1: score offsets of queries 2t and 2t + 1.
+__device__ __forceinline__ void attn_tile(const AttnTile& f, AttnState& st, const uint32_t (&qf)[3][4][2],
+                                          float bias0, float bias1, int nvalid, const unsigned char* table,
+                                          uint32_t slot, int g) {
+    // ---- scores^T: two blocks of 16 tokens x 8 queries
+    float sc[2][4];
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+        sc[m][0] = bias0; sc[m][1] = bias1; sc[m][2] = bias0; sc[m][3] = bias1;
+        const uint2 ra = f.k[m][0], rb = f.k[m][1];              // token rows g and g + 8
+#define PITCH_QK(KB)                                                                                 \
+        {                                                                                            \
+            const uint32_t a0 = key_pair<KB>(ra.x), a1 = key_pair<KB>(rb.x);                         \
+            const uint32_t a2 = key_pair<KB>(ra.y), a3 = key_pair<KB>(rb.y);                         \
+            mma_bf16(sc[m], a0, a1, a2, a3, qf[0][KB][0], qf[0][KB][1]);                             \
+            mma_bf16(sc[m], a0, a1, a2, a3, qf[1][KB][0], qf[1][KB][1]);                             \
+            mma_bf16(sc[m], a0, a1, a2, a3, qf[2][KB][0], qf[2][KB][1]);                             \
+        }
+        PITCH_QK(0) PITCH_QK(1) PITCH_QK(2) PITCH_QK(3)
+#undef PITCH_QK
+    }
+    if (nvalid < 32) {
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+            if (16 * m + g >= nvalid) { sc[m][0] = -INFINITY; sc[m][1] = -INFINITY; }
+            if (16 * m + 8 + g >= nvalid) { sc[m][2] = -INFINITY; sc[m][3] = -INFINITY; }
+        }
+    }
+    // ---- online softmax (base 2); sums over tokens stay per thread until the end of the run
+    float x0 = fmaxf(fmaxf(sc[0][0], sc[0][2]), fmaxf(sc[1][0], sc[1][2]));
+    float x1 = fmaxf(fmaxf(sc[0][1], sc[0][3]), fmaxf(sc[1][1], sc[1][3]));
+#pragma unroll
+    for (int s = 4; s < 32; s <<= 1) {
+        x0 = fmaxf(x0, __shfl_xor_sync(0xFFFFFFFFu, x0, s));
+        x1 = fmaxf(x1, __shfl_xor_sync(0xFFFFFFFFu, x1, s));
+    }
+    if (__any_sync(0xFFFFFFFFu, x0 > st.m0 || x1 > st.m1)) {
+        const float n0 = fmaxf(st.m0, x0), n1 = fmaxf(st.m1, x1);
+        const float c0 = fast_exp2(st.m0 - n0), c1 = fast_exp2(st.m1 - n1);     // 0 on the first tile
+        st.l0 *= c0; st.l1 *= c1;
+#pragma unroll
+        for (int mb = 0; mb < 4; ++mb) { st.acc[mb][0] *= c0; st.acc[mb][1] *= c1; st.acc[mb][2] *= c0; st.acc[mb][3] *= c1; }
+        st.m0 = n0; st.m1 = n1;
+    }
+    uint32_t wh[2][2], wl[2][2];                                  // weights^T, B fragments per 16 tokens
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const float p0 = fast_exp2(sc[m][2 * h] - st.m0), p1 = fast_exp2(sc[m][2 * h + 1] - st.m1);
+            st.l0 += p0; st.l1 += p1;
+            uint32_t hi, lo;
+            split_pair(p0 * f.n[m][h], p1 * f.n[m][h], hi, lo);
+            wh[m][h] = transpose8x8(hi);
+            wl[m][h] = transpose8x8(lo);
+        }
+    }
+    // ---- out^T += centroids^T . weights^T
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+        // coordinate-wise interleave of the token pairs (2t, 2t+1) and (2t+8, 2t+9)
+        const uint32_t ea = (f.v[m][0] & 0x0F0F0F0Fu) | ((f.v[m][1] << 4) & 0xF0F0F0F0u);   // even coordinates
+        const uint32_t oa = ((f.v[m][0] >> 4) & 0x0F0F0F0Fu) | (f.v[m][1] & 0xF0F0F0F0u);   // odd coordinates
+        const uint32_t eb = (f.v[m][2] & 0x0F0F0F0Fu) | ((f.v[m][3] << 4) & 0xF0F0F0F0u);
+        const uint32_t ob = ((f.v[m][2] >> 4) & 0x0F0F0F0Fu) | (f.v[m][3] & 0xF0F0F0F0u);
+#define PITCH_PV(MB)                                                                                          \
+        {                                                                                                     \
+            const unsigned char* e0 = table + __byte_perm(ea, slot, 0x5504 | (MB << 4));                      \
+            const unsigned char* e1 = table + __byte_perm(oa, slot, 0x5504 | (MB << 4));                      \
+            const unsigned char* e2 = table + __byte_perm(eb, slot, 0x5504 | (MB << 4));                      \
+            const unsigned char* e3 = table + __byte_perm(ob, slot, 0x5504 | (MB << 4));                      \
+            const uint32_t h0 = *reinterpret_cast<const uint32_t*>(e0), h1 = *reinterpret_cast<const uint32_t*>(e1); \
+            const uint32_t h2 = *reinterpret_cast<const uint32_t*>(e2), h3 = *reinterpret_cast<const uint32_t*>(e3); \
+            const uint32_t l0 = *reinterpret_cast<const uint32_t*>(e0 + 128), l1 = *reinterpret_cast<const uint32_t*>(e1 + 128); \
+            const uint32_t l2 = *reinterpret_cast<const uint32_t*>(e2 + 128), l3 = *reinterpret_cast<const uint32_t*>(e3 + 128); \
+            mma_bf16(st.acc[MB], h0, h1, h2, h3, wh[m][0], wh[m][1]);                                         \
+            mma_bf16(st.acc[MB], h0, h1, h2, h3, wl[m][0], wl[m][1]);                                         \
+            mma_bf16(st.acc[MB], l0, l1, l2, l3, wh[m][0], wh[m][1]);                                         \
+        }
+        PITCH_PV(0) PITCH_PV(1) PITCH_PV(2) PITCH_PV(3)
+#undef PITCH_PV
+    }
+}
+
+// Folds the queries of the run into the quantisation grid of one group of tokens: B fragments
+// (three bf16 parts) and the score bias of queries 2t and 2t + 1.  lo2 / hi2: this lane's two
+// channels of the group's fp16 minima and maxima.
+__device__ __forceinline__ void fold_group(__half2 lo2, __half2 hi2, const float* qs, float* gstep, float* goff,
+                                           uint32_t (&qf)[3][4][2], float& bias0, float& bias1, int lane, int g, int t) {
+    const float2 lo = __half22float2(lo2), hi = __half22float2(hi2);
+    const float s0 = step15(lo.x, hi.x), s1 = step15(lo.y, hi.y);
+    __syncwarp();
+    *reinterpret_cast<float2*>(gstep + 2 * lane) = make_float2(s0, s1);
+    *reinterpret_cast<float2*>(goff + 2 * lane) = make_float2(fmaf(-16.0f, s0, lo.x), fmaf(-16.0f, s1, lo.y));
+    __syncwarp();
+    float x[16];
+    float b = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float4 qv = *reinterpret_cast<const float4*>(qs + g * 64 + 16 * t + 4 * i);
+        const float4 sv = *reinterpret_cast<const float4*>(gstep + 16 * t + 4 * i);
+        const float4 ov = *reinterpret_cast<const float4*>(goff + 16 * t + 4 * i);
+        x[4 * i] = qv.x * sv.x; x[4 * i + 1] = qv.y * sv.y; x[4 * i + 2] = qv.z * sv.z; x[4 * i + 3] = qv.w * sv.w;
+        b = fmaf(qv.x, ov.x, b); b = fmaf(qv.y, ov.y, b); b = fmaf(qv.z, ov.z, b); b = fmaf(qv.w, ov.w, b);
+    }
+#pragma unroll
+    for (int kb = 0; kb < 4; ++kb) {
+        split_pair3(x[kb], x[kb + 4], qf[0][kb][0], qf[1][kb][0], qf[2][kb][0]);
+        split_pair3(x[8 + kb], x[12 + kb], qf[0][kb][1], qf[1][kb][1], qf[2][kb][1]);
+    }
+    b += __shfl_xor_sync(0xFFFFFFFFu, b, 1);
+    b += __shfl_xor_sync(0xFFFFFFFFu, b, 2);              // bias of query g
+    bias0 = __shfl_sync(0xFFFFFFFFu, b, 8 * t);           // of query 2t
+    bias1 = __shfl_sync(0xFFFFFFFFu, b, 8 * t + 4);       // of query 2t + 1
+}
+
+__global__ void __launch_bounds__(AT_THREADS, 2)
+attention_partial_kernel(const __grid_constant__ AttentionParams p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    // byte (na | nb << 4) of two tokens' codes, lane slot l: the bf16 pair (c[na], c[nb]) as hi parts at
+    // byte * 256 + l * 4 and lo parts 128 bytes further (every lane reads its own bank)
+    unsigned char* table = smem;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    float* qs = reinterpret_cast<float*>(smem + CD_TABLE_BYTES + warp * AT_WARP_SMEM);     // [8][64] query * scale (base 2)
+    float* gstep = qs + 8 * 64;                                                             // [64]
+    float* goff = gstep + 64;                                                               // [64] lo - 16 * step
+    const int R = p.n_queries;
+    const uint32_t slot = (uint32_t)lane * 4u;
+
+    for (int idx = threadIdx.x; idx < 256 * 32; idx += AT_THREADS) {
+        const int e = idx >> 5, l = idx & 31;
+        uint32_t hi, lo;
+        split_pair(p.book.c[e & 15], p.book.c[e >> 4], hi, lo);
+        *reinterpret_cast<uint32_t*>(table + e * 256 + l * 4) = hi;
+        *reinterpret_cast<uint32_t*>(table + e * 256 + 128 + l * 4) = lo;
+    }
+    __syncthreads();
+
+    const int n_runs = p.segments * p.splits;
+    for (int run = blockIdx.x * AT_WARPS + warp; run < n_runs; run += gridDim.x * AT_WARPS) {
+        const int64_t seg = run / p.splits;
+        const int split = run - (int)seg * p.splits;
+        const int w_begin = split * p.tokens_per_split;
+        int w_end = w_begin + p.tokens_per_split;
+        if (w_end > p.tokens) w_end = p.tokens;
+
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int idx = i * 32 + lane;
+            qs[idx] = (idx >> 6) < R ? p.q[seg * R * 64 + idx] * p.scale_log2 : 0.0f;
+        }
+        const __half* k_ranges = reinterpret_cast<const __half*>(p.k_ranges + seg * p.k_ranges_seg) + 2 * lane;
+        const unsigned char* kp = p.k_codes + seg * p.k_codes_seg + (int64_t)(w_begin + g) * 32 + t * 8;
+        const unsigned char* vp = p.v_codes + seg * p.v_codes_seg + (int64_t)(w_begin + 2 * t) * 32 + g * 4;
+        const float* np = reinterpret_cast<const float*>(p.v_norms + seg * p.v_norms_seg) + w_begin + g;
+
+        AttnState st;
+        st.m0 = st.m1 = -INFINITY;
+        st.l0 = st.l1 = 0.0f;
+#pragma unroll
+        for (int mb = 0; mb < 4; ++mb)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) st.acc[mb][i] = 0.0f;
+        uint32_t qf[3][4][2];
+        float bias0 = 0.0f, bias1 = 0.0f;
+
+        // the ranges of the first group; those of the following group are fetched a group ahead
+        int group = w_begin / p.group_size;
+        const int last_group = (w_end - 1) / p.group_size;
+        int group_end = (group + 1) * p.group_size;                   // first token of the next group
+        __half2 lo2 = *reinterpret_cast<const __half2*>(k_ranges + (int64_t)group * 128);
+        __half2 hi2 = *reinterpret_cast<const __half2*>(k_ranges + (int64_t)group * 128 + 64);
+        bool fold = true;
+
+        AttnTile bufA, bufB;
+        if (w_end - w_begin >= 32) load_attn_tile<true>(bufA, kp, vp, np, 32, g, t);
+        else load_attn_tile<false>(bufA, kp, vp, np, w_end - w_begin, g, t);
+
+        // two tiles per trip so that the prefetch alternates between two register sets
+#define PITCH_TILE(CUR, NXT)                                                                            \
+        {                                                                                               \
+            const int nvalid = w_end - t0;                                                              \
+            kp += 1024; vp += 1024; np += 32;                                                           \
+            if (nvalid >= 64) load_attn_tile<true>(NXT, kp, vp, np, 32, g, t);                          \
+            else if (nvalid > 32) load_attn_tile<false>(NXT, kp, vp, np, nvalid - 32, g, t);            \
+            if (t0 >= group_end) { ++group; group_end += p.group_size; fold = true; }                  \
+            if (fold) {                                                                                 \
+                fold = false;                                                                           \
+                fold_group(lo2, hi2, qs, gstep, goff, qf, bias0, bias1, lane, g, t);                    \
+                if (group < last_group) {                                                               \
+                    lo2 = *reinterpret_cast<const __half2*>(k_ranges + (int64_t)(group + 1) * 128);     \
+                    hi2 = *reinterpret_cast<const __half2*>(k_ranges + (int64_t)(group + 1) * 128 + 64); \
+                }                                                                                       \
+            }                                                                                           \
+            attn_tile(CUR, st, qf, bias0, bias1, nvalid, table, slot, g);                               \
+        }
+        for (int t0 = w_begin; t0 < w_end; t0 += 32) {
+            PITCH_TILE(bufA, bufB)
+            t0 += 32;
+            if (t0 >= w_end) break;
+            PITCH_TILE(bufB, bufA)
+        }
+#undef PITCH_TILE
+
+        // ---- finish the sums over tokens; this run's partial result
+#pragma unroll
+        for (int s = 4; s < 32; s <<= 1) {
+            st.l0 += __shfl_xor_sync(0xFFFFFFFFu, st.l0, s);
+            st.l1 += __shfl_xor_sync(0xFFFFFFFFu, st.l1, s);
+        }
+        float* d0 = p.work + ((seg * p.splits + split) * R + 2 * t) * AT_PART_FLOATS;   // query 2t
+        float* d1 = d0 + AT_PART_FLOATS;                                                // query 2t + 1
+        if (2 * t < R) {
+            if (g == 0) { d0[0] = st.m0; d0[1] = st.l0; }
+#pragma unroll
+            for (int mb = 0; mb < 4; ++mb)                            // coordinates 8g + 2mb and 8g + 2mb + 1
+                *reinterpret_cast<float2*>(d0 + 2 + 8 * g + 2 * mb) = make_float2(st.acc[mb][0], st.acc[mb][2]);
+        }
+        if (2 * t + 1 < R) {
+            if (g == 0) { d1[0] = st.m1; d1[1] = st.l1; }
+#pragma unroll
+            for (int mb = 0; mb < 4; ++mb)
+                *reinterpret_cast<float2*>(d1 + 2 + 8 * g + 2 * mb) = make_float2(st.acc[mb][1], st.acc[mb][3]);
+        }
+    }
+}
+
+// grid = (n_queries, segments), 8 warps: warp w merges runs w, w + 8, ... of its (segment, query),
+// lane l owning coordinates 2l and 2l + 1; warp 0 merges the eight, normalises and un-rotates.
+__global__ void __launch_bounds__(32 * AT_COMBINE_WARPS)
 attention_combine_kernel(const __grid_constant__ AttentionParams p) {
-    const int lane = threadIdx.x & 31, r = threadIdx.x >> 5;
-    const int64_t seg = blockIdx.x;
+    __shared__ float part[AT_COMBINE_WARPS][AT_PART_FLOATS];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int r = blockIdx.x;
+    const int64_t seg = blockIdx.y;
     const int R = p.n_queries;
     const float* base = p.work + (seg * p.splits * R + r) * AT_PART_FLOATS;
     const int64_t stride = (int64_t)R * AT_PART_FLOATS;
     float mm = -INFINITY;
-    for (int s = 0; s < p.splits; ++s) mm = fmaxf(mm, base[s * stride]);
     float2 a = make_float2(0.0f, 0.0f);
     float ll = 0.0f;
-    for (int s = 0; s < p.splits; ++s) {
+    for (int s = warp; s < p.splits; s += AT_COMBINE_WARPS) {
         const float* src = base + s * stride;
-        const float f = src[0] == -INFINITY ? 0.0f : fast_exp2(src[0] - mm);        // an empty slice
+        const float ms = src[0], ls = src[1];
         const float2 v = *reinterpret_cast<const float2*>(src + 2 + 2 * lane);
-        a.x += v.x * f;
-        a.y += v.y * f;
-        ll += src[1] * f;
+        const float mn = fmaxf(mm, ms);
+        const float fo = fast_exp2(mm - mn), fn = fast_exp2(ms - mn);     // every run holds at least one token
+        a.x = fmaf(v.x, fn, a.x * fo);
+        a.y = fmaf(v.y, fn, a.y * fo);
+        ll = fmaf(ls, fn, ll * fo);
+        mm = mn;
+    }
+    if (lane == 0) { part[warp][0] = mm; part[warp][1] = ll; }
+    *reinterpret_cast<float2*>(&part[warp][2 + 2 * lane]) = a;
+    __syncthreads();
+    if (warp != 0) return;
+    mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < AT_COMBINE_WARPS; ++w) mm = fmaxf(mm, part[w][0]);
+    a = make_float2(0.0f, 0.0f);
+    ll = 0.0f;
+#pragma unroll
+    for (int w = 0; w < AT_COMBINE_WARPS; ++w) {
+        const float f = part[w][0] == -INFINITY ? 0.0f : fast_exp2(part[w][0] - mm);   // a warp without a run
+        const float2 v = *reinterpret_cast<const float2*>(&part[w][2 + 2 * lane]);
+        a.x = fmaf(v.x, f, a.x);
+        a.y = fmaf(v.y, f, a.y);
+        ll = fmaf(part[w][1], f, ll);
     }
     // normalise, then rotate back once: H over 64 coordinates (two per lane), 1/8, sign diagonal
     const float inv = 0.125f / ll;

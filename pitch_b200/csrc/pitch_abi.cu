@@ -220,20 +220,6 @@ int launch_cache64(const Cache64Params& p, int dim, int bits, cudaStream_t s) {
     return bits == 4 ? launch_cache64_impl<T, 128, 4>(p, s) : launch_cache64_impl<T, 128, 3>(p, s);
 }
 
-template <int R>
-int launch_attention_partial(const AttentionParams& p, cudaStream_t s) {
-    static std::atomic<bool> configured[64];
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev].load(std::memory_order_acquire)) {
-        if (cudaFuncSetAttribute(attention_partial_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES) != cudaSuccess)
-            return launch_status(false, "cache_attention (shared memory opt-in)");
-        configured[dev].store(true, std::memory_order_release);
-    }
-    attention_partial_kernel<R><<<dim3((unsigned)p.splits, (unsigned)p.segments), AT_THREADS, AT_SMEM_BYTES, s>>>(p);
-    return PITCH_OK;
-}
-
 // Fills the geometry of a fast-path launch: `tokens` tokens per segment at head dimension `dim`.
 void cache64_geometry(Cache64Params& p, int dim, int64_t segments, int64_t tokens) {
     const int per_item = 2048 / dim;
@@ -954,15 +940,16 @@ int pitch_enqueue_cache_append_noalloc(const pitch_cache_desc* d, const pitch_ap
 }
 
 // -------------------------------------------------------------------------------- attention
-// How a segment's tokens are cut into slices (one CTA each).  Depends on the shape only, so that
-// the workspace size can be computed ahead of the call: slices of 1024 tokens, shorter (down to
-// 256) while the launch would have fewer than about four CTAs per SM, at most 64 slices.
+// How a segment's tokens are cut into runs (one warp each).  Depends on the shape only, so that
+// the workspace size can be computed ahead of the call: runs of whole 32-token tiles, about one
+// run per warp that a 148-SM GPU keeps resident (16 per SM), at least 4 tiles long.
 static void attention_slices(int64_t segments, int64_t tokens, int* splits, int* tokens_per_split) {
-    int64_t tps = 1024;
-    while (tps > 256 && segments * ceil_div(tokens, tps) < 592) tps /= 2;
-    if (ceil_div(tokens, tps) > 64) tps = ceil_div(ceil_div(tokens, 64), 256) * 256;
-    *tokens_per_split = (int)tps;
-    *splits = (int)ceil_div(tokens, tps);
+    const int64_t tiles = ceil_div(tokens, 32);
+    int64_t run = ceil_div(segments * tiles, 148 * 16);
+    if (run < 4) run = 4;
+    if (run > tiles) run = tiles;
+    *tokens_per_split = (int)(run * 32);
+    *splits = (int)ceil_div(tiles, run);
 }
 
 static int check_attention_shape(const pitch_cache_desc* d, int n_queries) {
@@ -1042,19 +1029,20 @@ int pitch_enqueue_cache_attention(const pitch_cache_desc* d, const pitch_attenti
         memcpy(p.book.c, g_books.values[6][4], sizeof(float) * 16);
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    switch (a->n_queries) {
-        case 1: st = launch_attention_partial<1>(p, s); break;
-        case 2: st = launch_attention_partial<2>(p, s); break;
-        case 3: st = launch_attention_partial<3>(p, s); break;
-        case 4: st = launch_attention_partial<4>(p, s); break;
-        case 5: st = launch_attention_partial<5>(p, s); break;
-        case 6: st = launch_attention_partial<6>(p, s); break;
-        case 7: st = launch_attention_partial<7>(p, s); break;
-        default: st = launch_attention_partial<8>(p, s); break;
+    {
+        static std::atomic<bool> configured[64];
+        if (dev >= 0 && dev < 64 && !configured[dev].load(std::memory_order_acquire)) {
+            if (cudaFuncSetAttribute(attention_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES) != cudaSuccess)
+                return launch_status(false, "cache_attention (shared memory opt-in)");
+            configured[dev].store(true, std::memory_order_release);
+        }
+        // two CTAs of eight warps per SM; a warp takes runs warp, warp + all warps, ...
+        int64_t ctas = ceil_div((int64_t)p.segments * p.splits, AT_WARPS);
+        if (ctas > 2 * sm_count()) ctas = 2 * sm_count();
+        attention_partial_kernel<<<(unsigned)ctas, AT_THREADS, AT_SMEM_BYTES, s>>>(p);
     }
-    if (st) return st;
     if ((st = launch_status(false, "cache_attention"))) return st;
-    attention_combine_kernel<<<(unsigned)p.segments, 32 * p.n_queries, 0, s>>>(p);
+    attention_combine_kernel<<<dim3((unsigned)p.n_queries, (unsigned)p.segments), 32 * AT_COMBINE_WARPS, 0, s>>>(p);
     return launch_status(false, "cache_attention (combine)");
 }
 
