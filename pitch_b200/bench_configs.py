@@ -1,6 +1,6 @@
 """Throughput of the stand-alone codec kernels at the benchmark configurations' shapes.
 
-    python -m pitch_b200.bench_configs [--only cfg1,cfg2,cfg3,sweep,cfg5] [--reps 50]
+    python -m pitch_b200.bench_configs [--only cfg1,cfg2,cfg3,sweep,cfg5,attn] [--reps 50]
 
 Prints one JSON line per measurement: encode vectors/s, decode output GB/s and the fraction of
 the HBM roofline, counting algorithmic bytes (full-precision tensor + packed codes + side
@@ -124,6 +124,52 @@ def bench_cfg5(q, bits, reps, segments=80, tokens=131072):
             "decode_output_GB_per_s": round(cache.decoded_bytes() / t / 1e9, 1)})
 
 
+def bench_attention(q, reps, segments=48, tokens=32768, n_queries=7):
+    """Single-token attention straight from the compressed cache at configuration 4's shape
+    (Qwen2.5-0.5B: 24 layers x 2 KV heads, 7 query heads per KV head), next to what it replaces:
+    whole-cache decode followed by attention over the decoded bf16 cache (torch SDPA)."""
+    d = 64
+    cache = KVCache(segments, d, tokens, ChannelQuantConfig(d, 4, 64), QuantConfig("turboQuant", d, 4),
+                    out_dtype="bfloat16", pitch=q)
+    g = torch.Generator(device=q.device)
+    g.manual_seed(7)
+    k = torch.randn((segments, tokens, d), generator=g, device=q.device) + 2.0 * torch.randn((segments, 1, d), generator=g, device=q.device)
+    v = lognormal_vectors(segments * tokens, d, 8, q.device).reshape(segments, tokens, d)
+    cache.prefill(k, v)
+    del k, v
+    qs = [torch.randn((segments, n_queries, d), generator=g, device=q.device) for _ in range(4)]
+    out = torch.empty_like(qs[0])
+    flush = torch.empty(L2_BYTES * 2, dtype=torch.uint8, device=q.device)       # the compressed cache (113 MB) fits L2
+
+    def timed(fn):
+        for i in range(3):
+            fn(i)
+        ts = []
+        for i in range(reps):
+            flush.fill_(i & 0xFF)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn(i)
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e-3)
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    t = timed(lambda i: cache.attend(qs[i % 4], out=out))
+    stored = cache.stored_bytes()
+    extra = {"dim": d, "segments": segments, "tokens": tokens, "n_queries": n_queries, "l2": "flushed before every launch",
+             "tokens_per_s": round(segments * tokens / t, 1)}
+    report("cfg4 attention", "attention from the compressed cache", t, segments * tokens, "kv_tokens", stored, extra)
+
+    def two_step(i):
+        ko, vo = cache.decode()
+        torch.nn.functional.scaled_dot_product_attention(qs[i % 4].to(torch.bfloat16).unsqueeze(0), ko.unsqueeze(0), vo.unsqueeze(0))
+    t2 = timed(two_step)
+    report("cfg4 attention", "decode, then torch SDPA over the decoded cache", t2, segments * tokens, "kv_tokens",
+           stored + 2 * cache.decoded_bytes(), {**extra, "speedup_of_fused": round(t2 / t, 2)})
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--only", default="cfg1,cfg2,cfg3,sweep")
@@ -145,6 +191,8 @@ def main():
         for method in ("turboQuant", "polarQuant"):
             for d in (64, 128, 256, 512, 1024):
                 bench_vector(q, "cfg3 sweep", method, (1 << 27) // d, d, 4, max(5, args.reps // 5))
+    if "attn" in which:
+        bench_attention(q, max(5, args.reps // 5))
     if "cfg5" in which:
         for bits in (4, 3):
             bench_cfg5(q, bits, max(3, args.reps // 10))

@@ -50,7 +50,7 @@ constexpr int AT_THREADS = 256;
 constexpr int AT_WARPS = AT_THREADS / 32;
 constexpr int AT_MAX_QUERIES = 8;
 constexpr int AT_PART_FLOATS = 66;                     // per (segment, slice, query): max, sum, 64 accumulators
-constexpr int AT_WARP_SMEM = 8 * 64 * 4 + 512;         // per warp: scaled queries; per-group steps and offsets of the keys
+constexpr int AT_WARP_SMEM = 8 * 64 * 4 + 512 + 12 * 32 * 8;   // per warp: scaled queries; per-group steps and offsets of the keys; folded query
 constexpr int AT_SMEM_BYTES = CD_TABLE_BYTES + AT_WARPS * AT_WARP_SMEM;
 constexpr int AT_COMBINE_WARPS = 8;
 
@@ -127,7 +127,7 @@ __device__ __forceinline__ void load_attn_tile(AttnTile& f, const unsigned char*
             f.n[m][h] = 0.0f;
             if (WHOLE || row + g < nvalid) {
                 f.k[m][h] = ldg_stream64(reinterpret_cast<const uint2*>(kp + row * 32));
-                f.n[m][h] = __ldg(np + row);
+                f.n[m][h] = __uint_as_float(ldg_stream32(reinterpret_cast<const uint32_t*>(np + row)));
             }
         }
 #pragma unroll
@@ -144,28 +144,38 @@ struct AttnState {
     float acc[4][4];              // out^T fragments: [block of 16 coordinates][fragment register]
 };
 
-// One tile: scores, online softmax, value accumulation.  qf: folded query (B fragments, three
-// bf16 parts per 16 channels); bias0/1: score offsets of queries 2t and 2t + 1.
-__device__ __forceinline__ void attn_tile(const AttnTile& f, AttnState& st, const uint32_t (&qf)[3][4][2],
+// One tile: scores, online softmax, value accumulation.  qf: this lane's folded-query fragments
+// in shared memory (stride 32 entries); bias0/1: score offsets of queries 2t and 2t + 1.
+__device__ __forceinline__ void attn_tile(const AttnTile& f, AttnState& st, const uint2* qf,
                                           float bias0, float bias1, int nvalid, const unsigned char* table,
                                           uint32_t slot, int g) {
-    // ---- scores^T: two blocks of 16 tokens x 8 queries
-    float sc[2][4];
+    // ---- scores^T: two blocks of 16 tokens x 8 queries; one accumulator per part of the query, so
+    //      that six short chains of products are in flight instead of two long ones
+    float sc[2][4], sm[2][4], sl[2][4];
 #pragma unroll
     for (int m = 0; m < 2; ++m) {
         sc[m][0] = bias0; sc[m][1] = bias1; sc[m][2] = bias0; sc[m][3] = bias1;
-        const uint2 ra = f.k[m][0], rb = f.k[m][1];              // token rows g and g + 8
-#define PITCH_QK(KB)                                                                                 \
-        {                                                                                            \
-            const uint32_t a0 = key_pair<KB>(ra.x), a1 = key_pair<KB>(rb.x);                         \
-            const uint32_t a2 = key_pair<KB>(ra.y), a3 = key_pair<KB>(rb.y);                         \
-            mma_bf16(sc[m], a0, a1, a2, a3, qf[0][KB][0], qf[0][KB][1]);                             \
-            mma_bf16(sc[m], a0, a1, a2, a3, qf[1][KB][0], qf[1][KB][1]);                             \
-            mma_bf16(sc[m], a0, a1, a2, a3, qf[2][KB][0], qf[2][KB][1]);                             \
-        }
-        PITCH_QK(0) PITCH_QK(1) PITCH_QK(2) PITCH_QK(3)
-#undef PITCH_QK
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { sm[m][i] = 0.0f; sl[m][i] = 0.0f; }
     }
+#define PITCH_QK(KB)                                                                                 \
+    {                                                                                                \
+        const uint2 qh = qf[(0 * 4 + KB) * 32], qm = qf[(1 * 4 + KB) * 32], ql = qf[(2 * 4 + KB) * 32]; \
+        _Pragma("unroll")                                                                            \
+        for (int m = 0; m < 2; ++m) {                                                                \
+            const uint32_t a0 = key_pair<KB>(f.k[m][0].x), a1 = key_pair<KB>(f.k[m][1].x);           \
+            const uint32_t a2 = key_pair<KB>(f.k[m][0].y), a3 = key_pair<KB>(f.k[m][1].y);           \
+            mma_bf16(sc[m], a0, a1, a2, a3, qh.x, qh.y);                                             \
+            mma_bf16(sm[m], a0, a1, a2, a3, qm.x, qm.y);                                             \
+            mma_bf16(sl[m], a0, a1, a2, a3, ql.x, ql.y);                                             \
+        }                                                                                            \
+    }
+    PITCH_QK(0) PITCH_QK(1) PITCH_QK(2) PITCH_QK(3)
+#undef PITCH_QK
+#pragma unroll
+    for (int m = 0; m < 2; ++m)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sc[m][i] += sm[m][i] + sl[m][i];
     if (nvalid < 32) {
 #pragma unroll
         for (int m = 0; m < 2; ++m) {
@@ -210,51 +220,64 @@ __device__ __forceinline__ void attn_tile(const AttnTile& f, AttnState& st, cons
         const uint32_t oa = ((f.v[m][0] >> 4) & 0x0F0F0F0Fu) | (f.v[m][1] & 0xF0F0F0F0u);   // odd coordinates
         const uint32_t eb = (f.v[m][2] & 0x0F0F0F0Fu) | ((f.v[m][3] << 4) & 0xF0F0F0F0u);
         const uint32_t ob = ((f.v[m][2] >> 4) & 0x0F0F0F0Fu) | (f.v[m][3] & 0xF0F0F0F0u);
-#define PITCH_PV(MB)                                                                                          \
-        {                                                                                                     \
-            const unsigned char* e0 = table + __byte_perm(ea, slot, 0x5504 | (MB << 4));                      \
-            const unsigned char* e1 = table + __byte_perm(oa, slot, 0x5504 | (MB << 4));                      \
-            const unsigned char* e2 = table + __byte_perm(eb, slot, 0x5504 | (MB << 4));                      \
-            const unsigned char* e3 = table + __byte_perm(ob, slot, 0x5504 | (MB << 4));                      \
-            const uint32_t h0 = *reinterpret_cast<const uint32_t*>(e0), h1 = *reinterpret_cast<const uint32_t*>(e1); \
-            const uint32_t h2 = *reinterpret_cast<const uint32_t*>(e2), h3 = *reinterpret_cast<const uint32_t*>(e3); \
-            const uint32_t l0 = *reinterpret_cast<const uint32_t*>(e0 + 128), l1 = *reinterpret_cast<const uint32_t*>(e1 + 128); \
-            const uint32_t l2 = *reinterpret_cast<const uint32_t*>(e2 + 128), l3 = *reinterpret_cast<const uint32_t*>(e3 + 128); \
-            mma_bf16(st.acc[MB], h0, h1, h2, h3, wh[m][0], wh[m][1]);                                         \
-            mma_bf16(st.acc[MB], h0, h1, h2, h3, wl[m][0], wl[m][1]);                                         \
-            mma_bf16(st.acc[MB], l0, l1, l2, l3, wh[m][0], wh[m][1]);                                         \
+        uint32_t ch[4][4], cl[4][4];                               // [coordinate block][fragment register]
+#pragma unroll
+        for (int mb = 0; mb < 4; ++mb) {
+            const unsigned char* e0 = table + __byte_perm(ea, slot, 0x5504 | (mb << 4));
+            const unsigned char* e1 = table + __byte_perm(oa, slot, 0x5504 | (mb << 4));
+            const unsigned char* e2 = table + __byte_perm(eb, slot, 0x5504 | (mb << 4));
+            const unsigned char* e3 = table + __byte_perm(ob, slot, 0x5504 | (mb << 4));
+            ch[mb][0] = *reinterpret_cast<const uint32_t*>(e0); cl[mb][0] = *reinterpret_cast<const uint32_t*>(e0 + 128);
+            ch[mb][1] = *reinterpret_cast<const uint32_t*>(e1); cl[mb][1] = *reinterpret_cast<const uint32_t*>(e1 + 128);
+            ch[mb][2] = *reinterpret_cast<const uint32_t*>(e2); cl[mb][2] = *reinterpret_cast<const uint32_t*>(e2 + 128);
+            ch[mb][3] = *reinterpret_cast<const uint32_t*>(e3); cl[mb][3] = *reinterpret_cast<const uint32_t*>(e3 + 128);
         }
-        PITCH_PV(0) PITCH_PV(1) PITCH_PV(2) PITCH_PV(3)
-#undef PITCH_PV
+#pragma unroll
+        for (int mb = 0; mb < 4; ++mb) mma_bf16(st.acc[mb], ch[mb][0], ch[mb][1], ch[mb][2], ch[mb][3], wh[m][0], wh[m][1]);
+#pragma unroll
+        for (int mb = 0; mb < 4; ++mb) mma_bf16(st.acc[mb], ch[mb][0], ch[mb][1], ch[mb][2], ch[mb][3], wl[m][0], wl[m][1]);
+#pragma unroll
+        for (int mb = 0; mb < 4; ++mb) mma_bf16(st.acc[mb], cl[mb][0], cl[mb][1], cl[mb][2], cl[mb][3], wh[m][0], wh[m][1]);
     }
 }
 
 // Folds the queries of the run into the quantisation grid of one group of tokens: B fragments
-// (three bf16 parts) and the score bias of queries 2t and 2t + 1.  lo2 / hi2: this lane's two
+// (three bf16 parts, left in shared memory: qf[(part * 4 + block of 16 channels) * 32 + lane])
+// and the score bias of queries 2t and 2t + 1.  lo2 / hi2: this lane's two
 // channels of the group's fp16 minima and maxima.
-__device__ __forceinline__ void fold_group(__half2 lo2, __half2 hi2, const float* qs, float* gstep, float* goff,
-                                           uint32_t (&qf)[3][4][2], float& bias0, float& bias1, int lane, int g, int t) {
-    const float2 lo = __half22float2(lo2), hi = __half22float2(hi2);
+__device__ __forceinline__ void fold_group(uint32_t lo2, uint32_t hi2, const float* qs, float* gstep, float* goff,
+                                           uint2* qf, float& bias0, float& bias1, int lane, int g, int t) {
+    const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&lo2));
+    const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&hi2));
     const float s0 = step15(lo.x, hi.x), s1 = step15(lo.y, hi.y);
+    // Shared-memory layout of the per-channel rows (steps, offsets, each query): the 16-byte chunk
+    // of channels 16t + 4i ... + 3 sits at chunk index 4i + t (for queries: xor 4 on odd rows), so
+    // that the eight lanes of a 128-bit load phase touch eight different bank groups.
+    const int chunk = 4 * ((lane >> 1) & 3) + (lane >> 3);            // of channels 2 * lane, 2 * lane + 1
     __syncwarp();
-    *reinterpret_cast<float2*>(gstep + 2 * lane) = make_float2(s0, s1);
-    *reinterpret_cast<float2*>(goff + 2 * lane) = make_float2(fmaf(-16.0f, s0, lo.x), fmaf(-16.0f, s1, lo.y));
+    *reinterpret_cast<float2*>(gstep + 4 * chunk + (2 * lane & 3)) = make_float2(s0, s1);
+    *reinterpret_cast<float2*>(goff + 4 * chunk + (2 * lane & 3)) = make_float2(fmaf(-16.0f, s0, lo.x), fmaf(-16.0f, s1, lo.y));
     __syncwarp();
     float x[16];
     float b = 0.0f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const float4 qv = *reinterpret_cast<const float4*>(qs + g * 64 + 16 * t + 4 * i);
-        const float4 sv = *reinterpret_cast<const float4*>(gstep + 16 * t + 4 * i);
-        const float4 ov = *reinterpret_cast<const float4*>(goff + 16 * t + 4 * i);
+        const float4 qv = *reinterpret_cast<const float4*>(qs + g * 64 + 4 * ((4 * i + t) ^ (4 * (g & 1))));
+        const float4 sv = *reinterpret_cast<const float4*>(gstep + 4 * (4 * i + t));
+        const float4 ov = *reinterpret_cast<const float4*>(goff + 4 * (4 * i + t));
         x[4 * i] = qv.x * sv.x; x[4 * i + 1] = qv.y * sv.y; x[4 * i + 2] = qv.z * sv.z; x[4 * i + 3] = qv.w * sv.w;
         b = fmaf(qv.x, ov.x, b); b = fmaf(qv.y, ov.y, b); b = fmaf(qv.z, ov.z, b); b = fmaf(qv.w, ov.w, b);
     }
 #pragma unroll
     for (int kb = 0; kb < 4; ++kb) {
-        split_pair3(x[kb], x[kb + 4], qf[0][kb][0], qf[1][kb][0], qf[2][kb][0]);
-        split_pair3(x[8 + kb], x[12 + kb], qf[0][kb][1], qf[1][kb][1], qf[2][kb][1]);
+        uint2 h, m, l;
+        split_pair3(x[kb], x[kb + 4], h.x, m.x, l.x);
+        split_pair3(x[8 + kb], x[12 + kb], h.y, m.y, l.y);
+        qf[(0 * 4 + kb) * 32 + lane] = h;
+        qf[(1 * 4 + kb) * 32 + lane] = m;
+        qf[(2 * 4 + kb) * 32 + lane] = l;
     }
+    __syncwarp();
     b += __shfl_xor_sync(0xFFFFFFFFu, b, 1);
     b += __shfl_xor_sync(0xFFFFFFFFu, b, 2);              // bias of query g
     bias0 = __shfl_sync(0xFFFFFFFFu, b, 8 * t);           // of query 2t
@@ -272,6 +295,7 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
     float* qs = reinterpret_cast<float*>(smem + CD_TABLE_BYTES + warp * AT_WARP_SMEM);     // [8][64] query * scale (base 2)
     float* gstep = qs + 8 * 64;                                                             // [64]
     float* goff = gstep + 64;                                                               // [64] lo - 16 * step
+    uint2* qf = reinterpret_cast<uint2*>(goff + 64);                                        // [3 parts][4 blocks][32 lanes]
     const int R = p.n_queries;
     const uint32_t slot = (uint32_t)lane * 4u;
 
@@ -294,9 +318,10 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
 
         __syncwarp();
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const int idx = i * 32 + lane;
-            qs[idx] = (idx >> 6) < R ? p.q[seg * R * 64 + idx] * p.scale_log2 : 0.0f;
+        for (int i = 0; i < 16; ++i) {                                // row r = i / 2, channel c; chunk layout as in fold_group
+            const int idx = i * 32 + lane, r = idx >> 6, c = idx & 63;
+            const int chunk = (4 * ((c >> 2) & 3) + (c >> 4)) ^ (4 * (r & 1));
+            qs[r * 64 + 4 * chunk + (c & 3)] = r < R ? p.q[seg * R * 64 + idx] * p.scale_log2 : 0.0f;
         }
         const __half* k_ranges = reinterpret_cast<const __half*>(p.k_ranges + seg * p.k_ranges_seg) + 2 * lane;
         const unsigned char* kp = p.k_codes + seg * p.k_codes_seg + (int64_t)(w_begin + g) * 32 + t * 8;
@@ -310,15 +335,14 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
         for (int mb = 0; mb < 4; ++mb)
 #pragma unroll
             for (int i = 0; i < 4; ++i) st.acc[mb][i] = 0.0f;
-        uint32_t qf[3][4][2];
         float bias0 = 0.0f, bias1 = 0.0f;
 
         // the ranges of the first group; those of the following group are fetched a group ahead
         int group = w_begin / p.group_size;
         const int last_group = (w_end - 1) / p.group_size;
         int group_end = (group + 1) * p.group_size;                   // first token of the next group
-        __half2 lo2 = *reinterpret_cast<const __half2*>(k_ranges + (int64_t)group * 128);
-        __half2 hi2 = *reinterpret_cast<const __half2*>(k_ranges + (int64_t)group * 128 + 64);
+        uint32_t lo2 = ldg_stream32(reinterpret_cast<const uint32_t*>(k_ranges + (int64_t)group * 128));
+        uint32_t hi2 = ldg_stream32(reinterpret_cast<const uint32_t*>(k_ranges + (int64_t)group * 128 + 64));
         bool fold = true;
 
         AttnTile bufA, bufB;
@@ -337,11 +361,11 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
                 fold = false;                                                                           \
                 fold_group(lo2, hi2, qs, gstep, goff, qf, bias0, bias1, lane, g, t);                    \
                 if (group < last_group) {                                                               \
-                    lo2 = *reinterpret_cast<const __half2*>(k_ranges + (int64_t)(group + 1) * 128);     \
-                    hi2 = *reinterpret_cast<const __half2*>(k_ranges + (int64_t)(group + 1) * 128 + 64); \
+                    lo2 = ldg_stream32(reinterpret_cast<const uint32_t*>(k_ranges + (int64_t)(group + 1) * 128));      \
+                    hi2 = ldg_stream32(reinterpret_cast<const uint32_t*>(k_ranges + (int64_t)(group + 1) * 128 + 64)); \
                 }                                                                                       \
             }                                                                                           \
-            attn_tile(CUR, st, qf, bias0, bias1, nvalid, table, slot, g);                               \
+            attn_tile(CUR, st, qf + lane, bias0, bias1, nvalid, table, slot, g);                               \
         }
         for (int t0 = w_begin; t0 < w_end; t0 += 32) {
             PITCH_TILE(bufA, bufB)
