@@ -243,6 +243,27 @@ typedef struct pitch_attention_args {
 int64_t pitch_cache_attention_workspace(const pitch_cache_desc* desc, int n_queries);
 int pitch_enqueue_cache_attention(const pitch_cache_desc* desc, const pitch_attention_args* args, void* stream);
 
+/* Exact key-bias removal (reference/mechanism_eval.py:4-7 and rotated_bias, :82-91; README.md:100
+ * lists it as not yet built into the reference's kernels).  A model whose key projection has a
+ * bias b caches k_t = R_t W x_t + R_t b, and R_t b is known exactly, so it can be subtracted before
+ * quantisation and added back after decoding at no storage cost.  In place, for every segment s,
+ * vector v < count and coordinate i < dim of data (dtype elements, [segments][..][dim]):
+ *     data[s][v][i] -/+= bias[s][i] * cos[p][i] + rotate_half(bias[s])[i] * sin[p][i],  p = first_position + v
+ * with rotate_half(b) = (-b[dim/2:], b[:dim/2]) and cos / sin the model's own full-width rotary
+ * tables (float32 [positions][dim]).  float32 arithmetic with one rounding per operation, one
+ * rounding to dtype.  subtract != 0 before encoding, 0 after decoding.
+ *   dim: even, a multiple of 8, at most PITCH_MAX_DIM; data 16-byte aligned, data_seg_stride a
+ *   multiple of 16; first_position + count <= positions; segments <= 65535. */
+typedef struct pitch_rope_bias {
+    const float* bias;          /* [segments][dim] */
+    int64_t bias_seg_stride;    /* bytes */
+    const float* cos_table;     /* [positions][dim] */
+    const float* sin_table;     /* [positions][dim] */
+    int64_t positions;
+} pitch_rope_bias;
+int pitch_enqueue_rope_bias(int dim, int dtype, int subtract, void* data, int64_t data_seg_stride, int64_t segments,
+                            int64_t first_position, int64_t count, const pitch_rope_bias* rope, void* stream);
+
 /* 64-bit checksum of `bytes` bytes (multiple of 4) at buf: sum over 32-bit words w_i of
  * (w_i + 1) * (2*i + 1) mod 2^64, ADDED onto *result (a device uint64 the caller zeroes).
  * Used to compare shards across GPUs without moving them; no counterpart in the reference. */

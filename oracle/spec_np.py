@@ -243,6 +243,18 @@ def channel_decode(codes, ranges, b: int, G: int = CHANNEL_DEFAULT_GROUP):
     return out
 
 
+def rotated_bias(bias, cos_table, sin_table):
+    """R_t b for every position t of the rotary tables: ``b * cos + rotate_half(b) * sin`` with
+    ``rotate_half(b) = (-b[d/2:], b[:d/2])`` (reference/mechanism_eval.py:82-91, ``rotated_bias``),
+    in float32 with one rounding per operation.  bias (d,), tables (T, d) -> (T, d) float32."""
+    b = np.asarray(bias, dtype=np.float32)
+    d = b.shape[0]
+    rh = np.concatenate([-b[d // 2:], b[:d // 2]]).astype(np.float32)
+    c = np.asarray(cos_table, dtype=np.float32)
+    s = np.asarray(sin_table, dtype=np.float32)
+    return (b[None, :] * c).astype(np.float32) + (rh[None, :] * s).astype(np.float32)
+
+
 def channel_bits_per_coordinate(d: int, b: int, G: int = CHANNEL_DEFAULT_GROUP) -> float:
     """(reference/pitch_reference.py:177-178)."""
     return code_stride_bytes(d, b) * 8 / d + 32 / G

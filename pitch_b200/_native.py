@@ -50,6 +50,12 @@ class AttentionArgs(Structure):
                 ("n_queries", c_int32), ("scale", c_float)]
 
 
+class RopeBias(Structure):
+    """``pitch_rope_bias``."""
+    _fields_ = [("bias", c_void_p), ("bias_seg_stride", c_int64), ("cos_table", c_void_p), ("sin_table", c_void_p),
+                ("positions", c_int64)]
+
+
 # name -> (restype, argtypes); every symbol include/pitch_b200.h declares
 PROTOTYPES = {
     "pitch_abi_version": (c_int, []),
@@ -70,6 +76,8 @@ PROTOTYPES = {
     "pitch_enqueue_cache_append_noalloc": (c_int, [POINTER(CacheDesc), POINTER(AppendSrc), c_int, c_int64, c_void_p]),
     "pitch_cache_attention_workspace": (c_int64, [POINTER(CacheDesc), c_int]),
     "pitch_enqueue_cache_attention": (c_int, [POINTER(CacheDesc), POINTER(AttentionArgs), c_void_p]),
+    "pitch_enqueue_rope_bias": (c_int, [c_int, c_int, c_int, c_void_p, c_int64, c_int64, c_int64, c_int64,
+                                        POINTER(RopeBias), c_void_p]),
     "pitch_enqueue_checksum": (c_int, [Buffer, c_int64, c_void_p, c_void_p]),
 }
 

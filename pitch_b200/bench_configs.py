@@ -1,6 +1,6 @@
 """Throughput of the stand-alone codec kernels at the benchmark configurations' shapes.
 
-    python -m pitch_b200.bench_configs [--only cfg1,cfg2,cfg3,sweep,cfg5,attn] [--reps 50]
+    python -m pitch_b200.bench_configs [--only cfg1,cfg2,cfg3,sweep,cfg5,attn,bias] [--reps 50]
 
 Prints one JSON line per measurement: encode vectors/s, decode output GB/s and the fraction of
 the HBM roofline, counting algorithmic bytes (full-precision tensor + packed codes + side
@@ -170,6 +170,32 @@ def bench_attention(q, reps, segments=48, tokens=32768, n_queries=7):
            stored + 2 * cache.decoded_bytes(), {**extra, "speedup_of_fused": round(t2 / t, 2)})
 
 
+def bench_key_bias(q, reps, segments=48, tokens=32768):
+    """Whole-cache decode with exact key-bias removal (TurboQuant keys and values, d=64, bf16 out):
+    the rotated bias is added back to the decoded keys by one extra element-wise launch."""
+    d = 64
+    cfg = QuantConfig("turboQuant", d, 4)
+    dev = q.device
+    inv = 10000.0 ** (-torch.arange(0, d, 2, dtype=torch.float64, device=dev) / d)
+    ang = torch.arange(tokens, dtype=torch.float64, device=dev)[:, None] * inv[None, :]
+    ang = torch.cat([ang, ang], dim=1)
+    kb = (torch.randn((segments, d), device=dev) * 4.0, torch.cos(ang).float().contiguous(), torch.sin(ang).float().contiguous())
+    for name, bias in (("without key bias", None), ("with key-bias removal", kb)):
+        cache = KVCache(segments, d, tokens, cfg, cfg, out_dtype="bfloat16", pitch=q, key_bias=bias)
+        for s0 in range(0, segments, 8):
+            x = lognormal_vectors(8 * tokens, d, 300 + s0, dev).reshape(8, tokens, d)
+            for pl in cache.planes:
+                for j in range(8):
+                    q.enqueue_encode(x[j], pl.codes[s0 + j], pl.side[s0 + j], tokens, cfg)
+            torch.cuda.synchronize()
+        cache.tokens = tokens
+        t = time_launches(lambda i: cache.decode(), 1, reps)
+        nbytes = cache.stored_bytes() + cache.decoded_bytes()
+        report("cfg4-shape TurboQuant keys", "whole-cache decode " + name, t, 2 * segments * tokens, "vectors", nbytes,
+               {"dim": d, "segments": segments, "tokens": tokens, "out_dtype": "bfloat16",
+                "extra_pass_bytes": 0 if bias is None else cache.decoded_bytes()})
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--only", default="cfg1,cfg2,cfg3,sweep")
@@ -193,6 +219,8 @@ def main():
                 bench_vector(q, "cfg3 sweep", method, (1 << 27) // d, d, 4, max(5, args.reps // 5))
     if "attn" in which:
         bench_attention(q, max(5, args.reps // 5))
+    if "bias" in which:
+        bench_key_bias(q, max(5, args.reps // 5))
     if "cfg5" in which:
         for bits in (4, 3):
             bench_cfg5(q, bits, max(3, args.reps // 10))

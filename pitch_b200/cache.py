@@ -58,7 +58,12 @@ class KVCache:
     ``capacity`` tokens of dimension ``dim``."""
 
     def __init__(self, segments: int, dim: int, capacity: int, key_config, value_config, *,
-                 out_dtype="bfloat16", device=None, pitch: PITCH | None = None):
+                 out_dtype="bfloat16", device=None, pitch: PITCH | None = None, key_bias=None):
+        """``key_bias=(bias, cos_table, sin_table)`` turns on exact key-bias removal
+        (reference/mechanism_eval.py:4-7): ``bias`` float32 ``[segments, dim]`` is the key
+        projection's bias per KV head, the tables float32 ``[positions, dim]`` are the model's
+        rotary tables.  The rotated bias of a token's position is subtracted from the keys before
+        they are encoded and added back to the decoded keys, at no storage cost."""
         torch = _torch()
         self.pitch = pitch if pitch is not None else PITCH(device)
         self.device = self.pitch.device
@@ -75,6 +80,12 @@ class KVCache:
         self._float_dtypes = (torch.float32, torch.float16, torch.bfloat16)
         self.planes = [self._make_plane("keys", key_config), self._make_plane("values", value_config)]
         self._piece_limit = min([pl.config.group_size for pl in self.planes if pl.is_channel] + [65535])
+        self.key_bias = None
+        if key_bias is not None:
+            bias, cos_table, sin_table = key_bias
+            if tuple(bias.shape) != (self.segments, self.dim) or cos_table.shape[0] < self.capacity:
+                raise InvalidInput(f"key_bias needs bias [{self.segments}, {self.dim}] and tables with at least {self.capacity} rows")
+            self.key_bias = (bias, cos_table, sin_table)
         codebooks.register_all()
 
     def _make_plane(self, name: str, cfg) -> _Plane:
@@ -149,6 +160,9 @@ class KVCache:
             raise InvalidInput("n_new must be at least 1")
         if self.tokens + n_new > self.capacity:
             raise InvalidInput(f"cache holds {self.tokens} of {self.capacity} tokens; cannot append {n_new}")
+        if self.key_bias is not None:
+            keys = keys.clone()
+            self.pitch.enqueue_rope_bias(keys, *self.key_bias, first_position=self.tokens, subtract=True, stream=stream)
         limit = self._piece_limit           # new tokens of one launch must fall into one per-channel group
         done = 0
         while done < n_new:
@@ -187,6 +201,10 @@ class KVCache:
         if len(set(groups)) > 1:
             raise InvalidInput("per-channel planes of one cache must share a group size")
         p = self.pitch
+        key_bias, self.key_bias = self.key_bias, None          # applied once here, not again by append() below
+        if key_bias is not None:
+            keys = keys.clone()
+            p.enqueue_rope_bias(keys, *key_bias, first_position=0, subtract=True, stream=stream)
         esz = keys.element_size()
         for pl, x in zip(self.planes, (keys, values)):
             if bulk == 0:
@@ -202,8 +220,11 @@ class KVCache:
                     p.enqueue_encode(x, pl.codes, pl.side, bulk, pl.config, input_offset=in_off,
                                      codes_offset=c_off, scales_offset=s_off, stream=stream)
         self.tokens = bulk
-        if bulk < T:
-            self.append(keys[:, bulk:].contiguous(), values[:, bulk:].contiguous(), stream)
+        try:
+            if bulk < T:
+                self.append(keys[:, bulk:].contiguous(), values[:, bulk:].contiguous(), stream)
+        finally:
+            self.key_bias = key_bias
 
     def truncate(self, tokens: int) -> None:
         """Forgets every token from ``tokens`` on (host-side bookkeeping only).  The new length
@@ -226,6 +247,9 @@ class KVCache:
         st = self._lib.pitch_enqueue_cache_decode(self._desc_ref, stream_handle(stream, self.device))
         if st:
             _native.check(st)
+        if self.key_bias is not None:
+            self.pitch.enqueue_rope_bias(self.planes[0].out[:, :self.tokens], *self.key_bias, first_position=0,
+                                         subtract=False, stream=stream)
         return tuple(pl.out[:, :self.tokens] for pl in self.planes)
 
     def attend(self, queries, scale: float | None = None, out=None, stream=None):
@@ -239,6 +263,8 @@ class KVCache:
         torch = _torch()
         if self.tokens < 1:
             raise InvalidInput("the cache is empty")
+        if self.key_bias is not None:
+            raise InvalidInput("attention from the compressed cache does not support key-bias removal")
         if not (isinstance(queries, torch.Tensor) and queries.is_cuda and queries.is_contiguous()
                 and queries.dtype == torch.float32):
             raise InvalidInput("queries must be a contiguous float32 CUDA tensor")

@@ -16,6 +16,8 @@ every byte of codec work is done by the kernels behind the C ABI.
 """
 from __future__ import annotations
 
+import ctypes
+
 import numpy as np
 
 from . import _native, codebooks
@@ -195,6 +197,32 @@ class PITCH:
                                                   stream_handle(stream, tensor.device))
         _native.check(st)
         return int(acc.item()) & 0xFFFFFFFFFFFFFFFF
+
+    def enqueue_rope_bias(self, data, bias, cos_table, sin_table, *, first_position: int = 0, subtract: bool,
+                          stream=None) -> None:
+        """Exact key-bias removal (reference/mechanism_eval.py:82-91, ``rotated_bias``): in place,
+        ``data[s, v] -= / += bias[s] * cos[p] + rotate_half(bias[s]) * sin[p]`` with
+        ``p = first_position + v``.  ``data`` is ``[segments, count, dim]`` (float32 / float16 /
+        bfloat16; the segment stride may exceed ``count * dim``), ``bias`` float32
+        ``[segments, dim]``, the tables float32 ``[positions, dim]`` (the model's own rotary
+        tables).  ``subtract=True`` before encoding, ``False`` after decoding."""
+        torch = _torch()
+        for t, name in ((data, "data"), (bias, "bias"), (cos_table, "cos_table"), (sin_table, "sin_table")):
+            if not (isinstance(t, torch.Tensor) and t.is_cuda):
+                raise InvalidInput(f"{name} must be a CUDA tensor")
+        if data.dim() != 3 or data.stride(2) != 1 or data.stride(1) != data.shape[2]:
+            raise InvalidInput("data must be [segments, count, dim] with contiguous vectors")
+        S, count, dim = (int(v) for v in data.shape)
+        for t, name in ((bias, "bias"), (cos_table, "cos_table"), (sin_table, "sin_table")):
+            if t.dtype != torch.float32 or not t.is_contiguous() or t.dim() != 2 or t.shape[1] != dim:
+                raise InvalidInput(f"{name} must be a contiguous float32 tensor with {dim} columns")
+        if bias.shape[0] != S or cos_table.shape != sin_table.shape:
+            raise InvalidInput("bias needs one row per segment; cos and sin tables must have the same shape")
+        rope = _native.RopeBias(bias.data_ptr(), dim * 4, cos_table.data_ptr(), sin_table.data_ptr(), int(cos_table.shape[0]))
+        st = _native.lib().pitch_enqueue_rope_bias(dim, native_dtype(data.dtype), 1 if subtract else 0, data.data_ptr(),
+                                                   data.stride(0) * data.element_size(), S, int(first_position), count,
+                                                   ctypes.byref(rope), stream_handle(stream, data.device))
+        _native.check(st)
 
     # ------------------------------------------------------------------ array API, per-vector
     @staticmethod

@@ -17,6 +17,7 @@
 
 #include "append_kernels.cuh"
 #include "attention_kernels.cuh"
+#include "bias_kernels.cuh"
 #include "cache_kernels.cuh"
 #include "channel_kernels.cuh"
 #include "common.cuh"
@@ -1044,6 +1045,44 @@ int pitch_enqueue_cache_attention(const pitch_cache_desc* d, const pitch_attenti
     if ((st = launch_status(false, "cache_attention"))) return st;
     attention_combine_kernel<<<dim3((unsigned)p.n_queries, (unsigned)p.segments), 32 * AT_COMBINE_WARPS, 0, s>>>(p);
     return launch_status(false, "cache_attention (combine)");
+}
+
+// ------------------------------------------------------------------------- key-bias removal
+int pitch_enqueue_rope_bias(int dim, int dtype, int subtract, void* data, int64_t data_seg_stride, int64_t segments,
+                            int64_t first_position, int64_t count, const pitch_rope_bias* rope, void* stream) {
+    if (dim < 8 || dim > PITCH_MAX_DIM || (dim & 7)) return fail(PITCH_ERR_INVALID_DIMENSION, "dimension %d must be a multiple of 8 in 8...%d", dim, PITCH_MAX_DIM);
+    if (dtype < PITCH_F32 || dtype > PITCH_BF16) return fail(PITCH_ERR_INVALID_INPUT, "unknown dtype %d", dtype);
+    if (rope == nullptr || data == nullptr) return fail(PITCH_ERR_INVALID_INPUT, "data or rope description is null");
+    if (!rope->bias || !rope->cos_table || !rope->sin_table) return fail(PITCH_ERR_INVALID_INPUT, "bias or rotary tables are null");
+    if (segments < 1 || segments > 65535) return fail(PITCH_ERR_INVALID_INPUT, "segments must be in 1...65535");
+    if (count < 0 || first_position < 0 || first_position + count > rope->positions)
+        return fail(PITCH_ERR_INVALID_INPUT, "positions %lld...%lld are outside the rotary tables (%lld rows)",
+                    (long long)first_position, (long long)(first_position + count), (long long)rope->positions);
+    if (!aligned16(data) || (data_seg_stride & 15) || !aligned16(rope->cos_table) || !aligned16(rope->sin_table) ||
+        (rope->bias_seg_stride & 3) || (reinterpret_cast<uintptr_t>(rope->bias) & 3))
+        return fail(PITCH_ERR_INVALID_INPUT, "data and tables must be 16-byte aligned, strides multiples of 16 (data) and 4 (bias)");
+    if (segments > 1 && data_seg_stride < count * dim * elem_size(dtype))
+        return fail(PITCH_ERR_INVALID_INPUT, "data segment stride is smaller than one segment");
+    const pitch_buffer bufs[4] = {{data, 0, 0}, {const_cast<float*>(rope->bias), 0, 0}, {const_cast<float*>(rope->cos_table), 0, 0},
+                                  {const_cast<float*>(rope->sin_table), 0, 0}};
+    const char* const names[4] = {"data", "bias", "cos table", "sin table"};
+    int dev, st;
+    if ((st = check_same_device(bufs, names, 4, &dev))) return st;
+    if (count == 0) return PITCH_OK;
+    DeviceGuard guard(dev);
+    const int seg_tile = rope_bias_seg_tile(dim, segments);
+    const int64_t tiles = ceil_div(segments, seg_tile);
+    const int64_t chunks = count * dim * elem_size(dtype) / 16;
+    int64_t blocks = ceil_div(chunks, RB_THREADS);
+    if (blocks > 0x7FFFFFFF) blocks = 0x7FFFFFFF;                             // the kernel strides over what is left
+    if (tiles > 65535) return fail(PITCH_ERR_INVALID_INPUT, "too many segments for dimension %d", dim);
+    const dim3 grid((unsigned)blocks, (unsigned)tiles);
+    const size_t smem = 2 * (size_t)dim * sizeof(float) * seg_tile;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    PITCH_DISPATCH_DTYPE(dtype, (rope_bias_kernel<T><<<grid, RB_THREADS, smem, s>>>(
+        static_cast<unsigned char*>(data), data_seg_stride, reinterpret_cast<const unsigned char*>(rope->bias),
+        rope->bias_seg_stride, rope->cos_table, rope->sin_table, dim, segments, seg_tile, first_position, count, subtract)));
+    return launch_status(subtract != 0, "rope_bias");
 }
 
 // --------------------------------------------------------------------------------- checksum
