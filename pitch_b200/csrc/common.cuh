@@ -231,6 +231,8 @@ __device__ __forceinline__ void stg_stream(uint4* p, const uint4& v) {
 // bytes of a warp-private shared buffer; the 16-byte pad keeps both the row-owner accesses
 // and the transposed accesses free of bank conflicts.
 // ------------------------------------------------------------------------------------------
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
+
 template <typename T, int E> struct WarpStage {
     static constexpr int ROWB = E * (int)sizeof(T);
     static constexpr int PITCHB = ROWB + 16;
@@ -259,6 +261,33 @@ template <typename T, int E> struct WarpStage {
             }
         }
         __syncwarp();
+        uint32_t w[WORDS];
+#pragma unroll
+        for (int j = 0; j < CPR; ++j) {
+            const uint4 q = *reinterpret_cast<const uint4*>(sm + lane * PITCHB + j * 16);
+            w[4 * j] = q.x; w[4 * j + 1] = q.y; w[4 * j + 2] = q.z; w[4 * j + 3] = q.w;
+        }
+        Packer<T, E>::unpack(w, x);
+        __syncwarp();
+    }
+
+    // The same tile, fetched by asynchronous 16-byte copies straight into the staging buffer (no
+    // registers, nothing waits): issue for the next tile, compute the current one, then
+    // cp_async_wait + __syncwarp + read_rows.  Needs a 16-byte aligned `g`; chunks beyond
+    // valid_elems are zero-filled without touching memory.
+    static __device__ __forceinline__ void issue_async(const T* __restrict__ g, int valid_elems, unsigned char* sm, int lane) {
+        const uint32_t base = (uint32_t)__cvta_generic_to_shared(sm);
+#pragma unroll
+        for (int k = 0; k < CPR; ++k) {
+            const int c = k * 32 + lane;
+            const bool live = c * EPC < valid_elems;
+            const void* src = live ? static_cast<const void*>(reinterpret_cast<const uint4*>(g) + c) : static_cast<const void*>(g);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                         :: "r"(base + (c / CPR) * PITCHB + (c % CPR) * 16), "l"(src), "r"(live ? 16 : 0) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    static __device__ __forceinline__ void read_rows(const unsigned char* sm, int lane, float (&x)[E]) {
         uint32_t w[WORDS];
 #pragma unroll
         for (int j = 0; j < CPR; ++j) {

@@ -284,7 +284,7 @@ int launch_turbo_encode(int dim, uint32_t seed, const void* in, void* codes, voi
         const int64_t cap = (int64_t)sm_count() * 8;
         if (ctas > cap) ctas = cap;
         const int smem = grid.cells * 8;
-        if (smem > 16 * 1024) {
+        if (smem > 4 * 1024) {                 // static staging buffers (about 40 KB) + table may pass the 48 KB default
             static std::atomic<bool> configured[64];
             int dev = 0;
             cudaGetDevice(&dev);

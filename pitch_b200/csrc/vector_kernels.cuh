@@ -188,7 +188,7 @@ turbo_encode_grid_kernel(const T* __restrict__ in, uint32_t* __restrict__ codes,
     __shared__ float s_edges[1 << BITS];
     __shared__ int s_cell_of_edge[1 << BITS];
     __shared__ uint32_t s_neg[32];
-    __shared__ __align__(16) unsigned char s_stage[VEC_WARPS][WarpStage<T, 32>::BYTES];
+    __shared__ __align__(16) unsigned char s_stage[VEC_WARPS][2][WarpStage<T, 32>::BYTES];     // two tiles: one in flight
     constexpr int NEDGES = (1 << BITS) - 1;
     const uint32_t mask8 = (uint32_t)(grid.cells - 1) << 3;
     for (int k = threadIdx.x; k < NEDGES; k += VEC_THREADS) {
@@ -216,12 +216,35 @@ turbo_encode_grid_kernel(const T* __restrict__ in, uint32_t* __restrict__ codes,
     const uint32_t neg = s_neg[sub];
     const float2 rs2 = make_float2(rs, rs), sc2 = make_float2(grid.scale8, grid.scale8), mg2 = make_float2(grid.magic8, grid.magic8);
     const int64_t tiles = (count + g.vpw - 1) / g.vpw;
-    for (int64_t tile = (int64_t)blockIdx.x * VEC_WARPS + warp; tile < tiles; tile += (int64_t)gridDim.x * VEC_WARPS) {
+    const int64_t stride = (int64_t)gridDim.x * VEC_WARPS;
+    // With an aligned input the next tile is copied into the other staging buffer asynchronously
+    // while this one is encoded.
+    auto tile_elems = [&](int64_t tile) {
+        const int64_t left = count - tile * g.vpw;
+        return (int)(left < g.vpw ? left : g.vpw) * dim;
+    };
+    int cur = 0;
+    const int64_t first = (int64_t)blockIdx.x * VEC_WARPS + warp;
+    if (vec_ok && first < tiles) WarpStage<T, 32>::issue_async(in + first * g.vpw * dim, tile_elems(first), s_stage[warp][0], lane);
+    for (int64_t tile = first; tile < tiles; tile += stride) {
         const int64_t v0 = tile * g.vpw;
         const int64_t v = v0 + lane / g.tpv;
         const bool valid = v < count;
         float x[32];
-        load_lane_coords<T, false>(in, v0, count, dim, g, vec_ok != 0, s_stage[warp], lane, valid, v, x);
+        if (vec_ok) {
+            const int64_t next = tile + stride;
+            if (next < tiles) {
+                WarpStage<T, 32>::issue_async(in + next * g.vpw * dim, tile_elems(next), s_stage[warp][cur ^ 1], lane);
+                cp_async_wait<1>();
+            } else {
+                cp_async_wait<0>();
+            }
+            __syncwarp();
+            WarpStage<T, 32>::read_rows(s_stage[warp][cur], lane, x);
+            cur ^= 1;
+        } else {
+            load_lane_coords<T, false>(in, v0, count, dim, g, false, s_stage[warp][0], lane, valid, v, x);
+        }
 
         // norm: squares, then the balanced adjacent-pair tree (same order as tree_sum_regs + lanes_sum)
         float t[32];
