@@ -109,15 +109,14 @@ __device__ __forceinline__ void append_vector_cta(const T* __restrict__ x_in, ui
         for (int k = 0; k < (int)((blockDim.x + 31) >> 5); ++k) rmax = fmaxf(rmax, s_red[k]);
         const float safe = rmax > 0.0f ? rmax : 1.0f;
         const float RL = (float)((1u << bits) - 1u);
-        const float radius_scale = RL / safe, angle_scale = (float)(1u << bits) * INV_TWO_PI_F;
+        const float radius_scale = RL / safe;
         if (active) {
             if ((tid & 1) == 0) {
                 float q = floorf(r * radius_scale + 0.5f);
                 q = fminf(fmaxf(q, 0.0f), RL);
                 code = (uint32_t)q;
             } else {
-                const float theta = atan2f(c, a);
-                code = (uint32_t)(int)floorf(theta * angle_scale + 0.5f) & ((1u << bits) - 1u);
+                code = angle_bin(a, c, bits);
             }
         }
         scale = rmax;

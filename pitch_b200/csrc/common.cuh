@@ -231,6 +231,33 @@ __device__ __forceinline__ void stg_stream(uint4* p, const uint4& v) {
 // bytes of a warp-private shared buffer; the 16-byte pad keeps both the row-owner accesses
 // and the transposed accesses free of bank conflicts.
 // ------------------------------------------------------------------------------------------
+// PolarQuant angle code of the pair (x, y): floor(atan2(y, x) * 2^bits / 2pi + 1/2) mod 2^bits
+// (reference/pitch_reference.py:116-119).  For 2, 3 and 4 bits no arctangent is needed: the
+// first-quadrant angle atan2(|y|, |x|) has reached bin j once |y| >= |x| * tan((j - 1/2) * 2pi/N), so j
+// is a count of at most four comparisons, and the quadrant is restored from the two sign bits
+// (atan2's own conventions for signed zeros included).  Decisions differ from the arctangent
+// route only for angles within rounding distance of a bin boundary.  Wider codes use atan2f.
+__device__ __forceinline__ uint32_t angle_bin(float x, float y, int bits) {
+    const uint32_t n = 1u << bits;
+    if (bits > 4) {
+        const float theta = atan2f(y, x);                      // (-pi, pi]: a negative bin index wraps to theta + 2*pi
+        return (uint32_t)(int)floorf(theta * ((float)n * INV_TWO_PI_F) + 0.5f) & (n - 1u);
+    }
+    const float a = fabsf(x), b = fabsf(y);
+    uint32_t j;
+    if (bits == 2) {
+        j = b >= a ? 1u : 0u;
+    } else if (bits == 3) {
+        j = (b >= a * 0.4142135679721832f ? 1u : 0u) + (b >= a * 2.4142136573791504f ? 1u : 0u);
+    } else {
+        j = (b >= a * 0.1989123672246933f ? 1u : 0u) + (b >= a * 0.6681786179542542f ? 1u : 0u) +
+            (b >= a * 1.4966057538986206f ? 1u : 0u) + (b >= a * 5.027339458465576f ? 1u : 0u);
+    }
+    if (b == 0.0f) j = 0u;                                     // also the pair (0, 0), where every comparison holds
+    const uint32_t k = (__float_as_uint(x) >> 31) ? n / 2u - j : j;             // x < 0 or -0: pi - angle
+    return (__float_as_uint(y) >> 31) ? (n - k) & (n - 1u) : k;                 // y < 0 or -0: negated angle
+}
+
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
 
 template <typename T, int E> struct WarpStage {

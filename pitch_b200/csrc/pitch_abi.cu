@@ -462,7 +462,9 @@ int pitch_enqueue_encode(int method, int dim, int bits, uint32_t seed, int dtype
                                                                       reinterpret_cast<float*>(at(scales)), count, dim, seed, rs,
                                                                       aligned16(at(input)) ? 1 : 0))));
         } else {
-            PITCH_DISPATCH_BITS(bits, PITCH_DISPATCH_DTYPE(dtype, (polar_encode_kernel<BITS, T, false><<<vec_grid(count, dim), VEC_THREADS, 0, s>>>(
+            unsigned ctas = vec_grid(count, dim);                       // CTAs loop over warp tiles
+            if (ctas > (unsigned)sm_count() * 8u) ctas = (unsigned)sm_count() * 8u;
+            PITCH_DISPATCH_BITS(bits, PITCH_DISPATCH_DTYPE(dtype, (polar_encode_kernel<BITS, T, false><<<ctas, VEC_THREADS, 0, s>>>(
                                                                       reinterpret_cast<const T*>(at(input)),
                                                                       reinterpret_cast<uint32_t*>(at(codes)),
                                                                       reinterpret_cast<float*>(at(scales)), count, dim, seed, rs,

@@ -365,21 +365,46 @@ __global__ void __launch_bounds__(VEC_THREADS)
 polar_encode_kernel(const T* __restrict__ in, uint32_t* __restrict__ codes, float* __restrict__ scales,
                     int64_t count, int dim, uint32_t seed, float rs, int vec_ok) {
     __shared__ uint32_t s_neg[32];
-    __shared__ __align__(16) unsigned char s_stage[VEC_WARPS][WarpStage<T, 32>::BYTES];
+    __shared__ __align__(16) unsigned char s_stage[VEC_WARPS][SMALL ? 1 : 2][WarpStage<T, 32>::BYTES];   // two tiles: one in flight
     init_negate_masks(s_neg, seed, dim, threadIdx.x, VEC_THREADS);
     __syncthreads();
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const TileGeom<SMALL> g(dim, BITS);
-    const int64_t v0 = ((int64_t)blockIdx.x * VEC_WARPS + warp) * g.vpw;
-    if (v0 >= count) return;
     const int sub = lane & (g.tpv - 1);
+    const uint32_t neg = s_neg[sub];
+    // CTAs loop over warp tiles; with an aligned input (dim >= 32) the next tile is copied into the
+    // other staging buffer asynchronously while this one is encoded.
+    const int64_t tiles = (count + g.vpw - 1) / g.vpw;
+    const int64_t stride = (int64_t)gridDim.x * VEC_WARPS;
+    const bool async = !SMALL && vec_ok != 0;
+    auto tile_elems = [&](int64_t tile) {
+        const int64_t left = count - tile * g.vpw;
+        return (int)(left < g.vpw ? left : g.vpw) * dim;
+    };
+    int cur = 0;
+    const int64_t first = (int64_t)blockIdx.x * VEC_WARPS + warp;
+    if (async && first < tiles) WarpStage<T, 32>::issue_async(in + first * g.vpw * dim, tile_elems(first), s_stage[warp][0], lane);
+    for (int64_t tile = first; tile < tiles; tile += stride) {
+    const int64_t v0 = tile * g.vpw;
     const int64_t v = v0 + lane / g.tpv;
     const bool valid = v < count;
 
     float x[32];
-    load_lane_coords<T, SMALL>(in, v0, count, dim, g, vec_ok != 0, s_stage[warp], lane, valid, v, x);
-    const uint32_t neg = s_neg[sub];
+    if (async) {
+        const int64_t next = tile + stride;
+        if (next < tiles) {
+            WarpStage<T, 32>::issue_async(in + next * g.vpw * dim, tile_elems(next), s_stage[warp][SMALL ? 0 : (cur ^ 1)], lane);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncwarp();
+        WarpStage<T, 32>::read_rows(s_stage[warp][SMALL ? 0 : cur], lane, x);
+        cur ^= 1;
+    } else {
+        load_lane_coords<T, SMALL>(in, v0, count, dim, g, false, s_stage[warp][0], lane, valid, v, x);
+    }
 #pragma unroll
     for (int i = 0; i < 32; ++i) x[i] = flip_if(x[i], neg, i);
     wht_regs(x, g.e());
@@ -398,7 +423,6 @@ polar_encode_kernel(const T* __restrict__ in, uint32_t* __restrict__ codes, floa
     rmax = lanes_max(rmax, g.tpv);
     const float safe = rmax > 0.0f ? rmax : 1.0f;
     constexpr float RL = (float)((1 << BITS) - 1);
-    constexpr float ANGLE_SCALE = (float)(1 << BITS) * INV_TWO_PI_F;      // bins per radian (power of two x rounded 1/2pi)
     const float radius_scale = RL / safe;                                 // one division per vector
 
     uint32_t w[BITS];
@@ -410,14 +434,12 @@ polar_encode_kernel(const T* __restrict__ in, uint32_t* __restrict__ codes, floa
             float q = floorf(r[p] * radius_scale + 0.5f);
             q = fminf(fmaxf(q, 0.0f), RL);
             insert_code<BITS>(w, 2 * p, (uint32_t)q);
-            // angle in (-pi, pi]: a negative bin index wraps to the same bin as theta + 2*pi
-            const float theta = atan2f(x[2 * p + 1], x[2 * p]);
-            const uint32_t tq = (uint32_t)(int)floorf(theta * ANGLE_SCALE + 0.5f) & ((1u << BITS) - 1u);
-            insert_code<BITS>(w, 2 * p + 1, tq);
+            insert_code<BITS>(w, 2 * p + 1, angle_bin(x[2 * p], x[2 * p + 1], BITS));
         }
     }
     store_lane_words<BITS, SMALL>(codes, v, sub, dim, g, valid, w);
     if (valid && sub == 0) scales[v] = rmax;
+    }
 }
 
 // ------------------------------------------------------------------------------------------
