@@ -115,17 +115,6 @@ struct Prefetch64 {
     uint4 c, d;   // TurboQuant: c.x = norm bits.  Per-channel: fp16 minima (c) and maxima (d) of the lane's 8 channels
 };
 
-__device__ __forceinline__ uint32_t ldg_stream32(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
-    return v;
-}
-__device__ __forceinline__ uint2 ldg_stream64(const uint2* p) {
-    uint2 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
-    return v;
-}
-
 // Geometry of a work item for head dimension D.
 template <int D> struct Item64 {
     static constexpr int LPV = D / 64;          // lanes per vector (TurboQuant)

@@ -163,6 +163,14 @@ int check_channel_config(int dim, int bits, int group_size, int dtype) {
         default: { typedef __nv_bfloat16 T; __VA_ARGS__; break; }         \
     }
 
+unsigned vec_grid(int64_t count, int dim);
+int sm_count();
+// Grid of a kernel whose CTAs loop over warp tiles: enough CTAs for every SM's registers, no more.
+unsigned vec_grid_looping(int64_t count, int dim) {
+    const unsigned all = vec_grid(count, dim), cap = (unsigned)sm_count() * 8u;
+    return all < cap ? all : cap;
+}
+
 unsigned vec_grid(int64_t count, int dim) {
     const int vpw = dim < 32 ? 32 : 1024 / dim;
     return (unsigned)ceil_div(ceil_div(count, vpw), VEC_WARPS);
@@ -331,7 +339,7 @@ int launch_turbo_decode(int dim, uint32_t seed, const void* codes, const void* s
             static_cast<const uint32_t*>(codes), static_cast<const float*>(scales), static_cast<T*>(out), count, dim, seed,
             rsqrt_dim(dim), aligned16(out) ? 1 : 0, book);
     else
-        turbo_decode_kernel<BITS, T, false><<<vec_grid(count, dim), VEC_THREADS, 0, s>>>(
+        turbo_decode_kernel<BITS, T, false><<<vec_grid_looping(count, dim), VEC_THREADS, 0, s>>>(
             static_cast<const uint32_t*>(codes), static_cast<const float*>(scales), static_cast<T*>(out), count, dim, seed,
             rsqrt_dim(dim), aligned16(out) ? 1 : 0, book);
     return PITCH_OK;
@@ -502,7 +510,7 @@ int pitch_enqueue_decode(int method, int dim, int bits, uint32_t seed, int dtype
                                                                       reinterpret_cast<T*>(at(output)), count, dim, seed, rs,
                                                                       aligned16(at(output)) ? 1 : 0))));
         } else {
-            PITCH_DISPATCH_BITS(bits, PITCH_DISPATCH_DTYPE(dtype, (polar_decode_kernel<BITS, T, false><<<vec_grid(count, dim), VEC_THREADS, 0, s>>>(
+            PITCH_DISPATCH_BITS(bits, PITCH_DISPATCH_DTYPE(dtype, (polar_decode_kernel<BITS, T, false><<<vec_grid_looping(count, dim), VEC_THREADS, 0, s>>>(
                                                                       reinterpret_cast<const uint32_t*>(at(codes)),
                                                                       reinterpret_cast<const float*>(at(scales)),
                                                                       reinterpret_cast<T*>(at(output)), count, dim, seed, rs,

@@ -74,7 +74,7 @@ __device__ __forceinline__ void load_lane_words(const uint32_t* __restrict__ cod
 #pragma unroll
     for (int k = 0; k < BITS; ++k) {
         w[k] = 0;
-        if (valid && (!SMALL || k < g.wpv)) w[k] = __ldg(codes + v * g.wpv + sub * BITS + k);
+        if (valid && (!SMALL || k < g.wpv)) w[k] = ldg_stream32(codes + v * g.wpv + sub * BITS + k);
     }
 }
 
@@ -328,31 +328,47 @@ turbo_decode_kernel(const uint32_t* __restrict__ codes, const float* __restrict_
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const TileGeom<SMALL> g(dim, BITS);
-    const int64_t v0 = ((int64_t)blockIdx.x * VEC_WARPS + warp) * g.vpw;
-    if (v0 >= count) return;
     const int sub = lane & (g.tpv - 1);
-    const int64_t v = v0 + lane / g.tpv;
-    const bool valid = v < count;
-
-    uint32_t w[BITS];
-    load_lane_words<BITS, SMALL>(codes, v, sub, dim, g, valid, w);
-    const float norm = valid ? __ldg(norms + v) : 0.0f;
-
-    float x[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) x[i] = (i < g.e()) ? s_book[extract_code<BITS>(w, i)] : 0.0f;
-    wht_regs(x, g.e());
-    if (!SMALL && g.tpv >= 8) {
-        const int64_t left = count - v0;
-        const int valid_elems = (int)(left < g.vpw ? left : g.vpw) * dim;
-        finish_decode_transposed<T, true>(x, s_stage[warp], lane, g.tpv, s_neg[sub], norm, rs, out + v0 * dim, valid_elems);
-        return;
-    }
-    wht_lanes(x, g.tpv, lane);
     const uint32_t neg = s_neg[sub];
+    // CTAs loop over warp tiles; the code words and the norm of the next tile are fetched while
+    // this one is decoded.
+    const int64_t tiles = (count + g.vpw - 1) / g.vpw;
+    const int64_t stride = (int64_t)gridDim.x * VEC_WARPS;
+    uint32_t wn[BITS];
+    float norm_n = 0.0f;
+    auto fetch = [&](int64_t tile) {
+        const int64_t vv = tile * g.vpw + lane / g.tpv;
+        const bool ok = vv < count;
+        load_lane_words<BITS, SMALL>(codes, vv, sub, dim, g, ok, wn);
+        norm_n = ok ? __uint_as_float(ldg_stream32(reinterpret_cast<const uint32_t*>(norms + vv))) : 0.0f;
+    };
+    const int64_t first = (int64_t)blockIdx.x * VEC_WARPS + warp;
+    if (first < tiles) fetch(first);
+    for (int64_t tile = first; tile < tiles; tile += stride) {
+        const int64_t v0 = tile * g.vpw;
+        const int64_t v = v0 + lane / g.tpv;
+        const bool valid = v < count;
+        uint32_t w[BITS];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) x[i] = flip_if(x[i], neg, i) * rs * norm;
-    store_lane_coords<T, SMALL>(out, v0, count, dim, g, vec_ok != 0, s_stage[warp], lane, valid, v, x);
+        for (int k = 0; k < BITS; ++k) w[k] = wn[k];
+        const float norm = norm_n;
+        if (tile + stride < tiles) fetch(tile + stride);
+
+        float x[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) x[i] = (i < g.e()) ? s_book[extract_code<BITS>(w, i)] : 0.0f;
+        wht_regs(x, g.e());
+        if (!SMALL && g.tpv >= 8) {
+            const int64_t left = count - v0;
+            const int valid_elems = (int)(left < g.vpw ? left : g.vpw) * dim;
+            finish_decode_transposed<T, true>(x, s_stage[warp], lane, g.tpv, neg, norm, rs, out + v0 * dim, valid_elems);
+            continue;
+        }
+        wht_lanes(x, g.tpv, lane);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) x[i] = flip_if(x[i], neg, i) * rs * norm;
+        store_lane_coords<T, SMALL>(out, v0, count, dim, g, vec_ok != 0, s_stage[warp], lane, valid, v, x);
+    }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -464,41 +480,57 @@ polar_decode_kernel(const uint32_t* __restrict__ codes, const float* __restrict_
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const TileGeom<SMALL> g(dim, BITS);
-    const int64_t v0 = ((int64_t)blockIdx.x * VEC_WARPS + warp) * g.vpw;
-    if (v0 >= count) return;
     const int sub = lane & (g.tpv - 1);
-    const int64_t v = v0 + lane / g.tpv;
-    const bool valid = v < count;
-
-    uint32_t w[BITS];
-    load_lane_words<BITS, SMALL>(codes, v, sub, dim, g, valid, w);
-    const float scale = valid ? __ldg(scales + v) : 0.0f;
-
-    float x[32];
-#pragma unroll
-    for (int p = 0; p < 16; ++p) {
-        if (2 * p < g.e()) {
-            const float r = s_ratio[extract_code<BITS>(w, 2 * p)] * scale;
-            const uint32_t tq = extract_code<BITS>(w, 2 * p + 1);
-            x[2 * p] = r * s_cos[tq];
-            x[2 * p + 1] = r * s_sin[tq];
-        } else {
-            x[2 * p] = 0.0f;
-            x[2 * p + 1] = 0.0f;
-        }
-    }
-    wht_regs(x, g.e());
-    if (!SMALL && g.tpv >= 8) {
-        const int64_t left = count - v0;
-        const int valid_elems = (int)(left < g.vpw ? left : g.vpw) * dim;
-        finish_decode_transposed<T, false>(x, s_stage[warp], lane, g.tpv, s_neg[sub], 0.0f, rs, out + v0 * dim, valid_elems);
-        return;
-    }
-    wht_lanes(x, g.tpv, lane);
     const uint32_t neg = s_neg[sub];
+    // CTAs loop over warp tiles (the angle tables are built once); the code words and the scale
+    // of the next tile are fetched while this one is decoded.
+    const int64_t tiles = (count + g.vpw - 1) / g.vpw;
+    const int64_t stride = (int64_t)gridDim.x * VEC_WARPS;
+    uint32_t wn[BITS];
+    float scale_n = 0.0f;
+    auto fetch = [&](int64_t tile) {
+        const int64_t vv = tile * g.vpw + lane / g.tpv;
+        const bool ok = vv < count;
+        load_lane_words<BITS, SMALL>(codes, vv, sub, dim, g, ok, wn);
+        scale_n = ok ? __uint_as_float(ldg_stream32(reinterpret_cast<const uint32_t*>(scales + vv))) : 0.0f;
+    };
+    const int64_t first = (int64_t)blockIdx.x * VEC_WARPS + warp;
+    if (first < tiles) fetch(first);
+    for (int64_t tile = first; tile < tiles; tile += stride) {
+        const int64_t v0 = tile * g.vpw;
+        const int64_t v = v0 + lane / g.tpv;
+        const bool valid = v < count;
+        uint32_t w[BITS];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) x[i] = flip_if(x[i], neg, i) * rs;
-    store_lane_coords<T, SMALL>(out, v0, count, dim, g, vec_ok != 0, s_stage[warp], lane, valid, v, x);
+        for (int k = 0; k < BITS; ++k) w[k] = wn[k];
+        const float scale = scale_n;
+        if (tile + stride < tiles) fetch(tile + stride);
+
+        float x[32];
+#pragma unroll
+        for (int p = 0; p < 16; ++p) {
+            if (2 * p < g.e()) {
+                const float r = s_ratio[extract_code<BITS>(w, 2 * p)] * scale;
+                const uint32_t tq = extract_code<BITS>(w, 2 * p + 1);
+                x[2 * p] = r * s_cos[tq];
+                x[2 * p + 1] = r * s_sin[tq];
+            } else {
+                x[2 * p] = 0.0f;
+                x[2 * p + 1] = 0.0f;
+            }
+        }
+        wht_regs(x, g.e());
+        if (!SMALL && g.tpv >= 8) {
+            const int64_t left = count - v0;
+            const int valid_elems = (int)(left < g.vpw ? left : g.vpw) * dim;
+            finish_decode_transposed<T, false>(x, s_stage[warp], lane, g.tpv, neg, 0.0f, rs, out + v0 * dim, valid_elems);
+            continue;
+        }
+        wht_lanes(x, g.tpv, lane);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) x[i] = flip_if(x[i], neg, i) * rs;
+        store_lane_coords<T, SMALL>(out, v0, count, dim, g, vec_ok != 0, s_stage[warp], lane, valid, v, x);
+    }
 }
 
 // ------------------------------------------------------------------------------------------
