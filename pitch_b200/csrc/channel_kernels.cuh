@@ -246,14 +246,21 @@ channel_encode_slab_kernel(const T* __restrict__ in, unsigned char* __restrict__
     load8<T>(in + first * dim + slab * 8, lo);
 #pragma unroll
     for (int i = 0; i < 8; ++i) hi[i] = lo[i];
-    for (int64_t t = first + tok_lane; t < last; t += tok_lanes) {
-        float x[8];
-        load8<T>(in + t * dim + slab * 8, x);
+    for (int64_t t = first + tok_lane; t < last; t += 4 * tok_lanes) {
+        // four tokens in flight per lane
+        float x[4][8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            lo[i] = fminf(lo[i], x[i]);
-            hi[i] = fmaxf(hi[i], x[i]);
+        for (int k = 0; k < 4; ++k) {
+            const int64_t tk = t + (int64_t)k * tok_lanes;
+            load8<T>(in + (tk < last ? tk : first) * dim + slab * 8, x[k]);      // a token of the group either way
         }
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                lo[i] = fminf(lo[i], x[k][i]);
+                hi[i] = fmaxf(hi[i], x[k][i]);
+            }
     }
     for (int m = 1 << log2_slabs; m < 32; m <<= 1) {
 #pragma unroll
@@ -281,9 +288,18 @@ channel_encode_slab_kernel(const T* __restrict__ in, unsigned char* __restrict__
         *reinterpret_cast<uint4*>(ranges + g * 2 * dim + dim + slab * 8) = make_uint4(hi_w[0], hi_w[1], hi_w[2], hi_w[3]);
     }
 
-    for (int64_t t = first + tok_lane; t < last; t += tok_lanes) {
-        float x[8];
-        load8<T>(in + t * dim + slab * 8, x);
+    for (int64_t t0 = first + tok_lane; t0 < last; t0 += 4 * tok_lanes) {
+      float xs[4][8];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+          const int64_t tk = t0 + (int64_t)k * tok_lanes;
+          if (tk < last) load8<T>(in + tk * dim + slab * 8, xs[k]);
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int64_t t = t0 + (int64_t)k * tok_lanes;
+        if (t >= last) break;
+        const float (&x)[8] = xs[k];
         uint32_t c[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) c[i] = quantise(x[i], lo[i], step[i], LEVELS);
@@ -307,6 +323,7 @@ channel_encode_slab_kernel(const T* __restrict__ in, unsigned char* __restrict__
             }
             *reinterpret_cast<uint2*>(dst) = w;
         }
+      }
     }
 }
 
