@@ -200,6 +200,7 @@ def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--only", default="cfg1,cfg2,cfg3,sweep")
     ap.add_argument("--reps", type=int, default=50)
+    ap.add_argument("--cfg5-segments", type=int, default=80, help="segments of the config 5 shard (80 = one GPU's share of 640)")
     args = ap.parse_args()
     which = set(args.only.split(","))
     q = PITCH()
@@ -223,7 +224,7 @@ def main():
         bench_key_bias(q, max(5, args.reps // 5))
     if "cfg5" in which:
         for bits in (4, 3):
-            bench_cfg5(q, bits, max(3, args.reps // 10))
+            bench_cfg5(q, bits, max(3, args.reps // 10), segments=args.cfg5_segments)
 
 
 if __name__ == "__main__":

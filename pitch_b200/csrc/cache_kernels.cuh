@@ -191,6 +191,31 @@ __device__ __forceinline__ void turbo64_decode_warp(const Prefetch64& f, T* __re
     const float norm = __uint_as_float(f.c.x);
     const uint32_t slot = (uint32_t)lane * 8u;
     float2 v[32];
+    if (D == 128 && BITS == 4) {
+        // The stage that pairs coordinate i with i + 64 (held by the other lane of the pair) is done
+        // first and inside the table: the lanes swap their 32 code bytes (8 shuffles instead of the
+        // 64 a float exchange takes), each interleaves its own nibbles with the partner's, and the
+        // table gives c[own] + c[partner] to even lanes (output coordinates 0...63) and
+        // c[partner] - c[own] to odd lanes (64...127) in one 4-byte lookup.
+        const uint32_t slot4 = (uint32_t)lane * 4u;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const uint32_t other = __shfl_xor_sync(0xFFFFFFFFu, w[k], 1);
+            const uint32_t even = (w[k] & 0x0F0F0F0Fu) | ((other << 4) & 0xF0F0F0F0u);     // coordinates 8k, 8k+2, 8k+4, 8k+6
+            const uint32_t odd = ((w[k] >> 4) & 0x0F0F0F0Fu) | (other & 0xF0F0F0F0u);      // coordinates 8k+1, ...
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float x = *reinterpret_cast<const float*>(table + __byte_perm(even, slot4, 0x5504 | (j << 4)));
+                const float y = *reinterpret_cast<const float*>(table + __byte_perm(odd, slot4, 0x5504 | (j << 4)));
+                v[4 * k + j] = make_float2(x + y, x - y);                                   // stage 1
+            }
+        }
+        wht64_pairs_from_stage2(v);
+        const float2 r2 = make_float2(rs, rs), n2 = make_float2(norm, norm);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = mul2(mul2(v[i], r2), n2);
+        PairStore<T>::row(v, sign, stage + lane * Stage::PITCHB);
+    } else {
 #pragma unroll
     for (int p = 0; p < 32; ++p) v[p] = *reinterpret_cast<const float2*>(table + pair_offset<BITS>(w, p, slot));
     wht64_pairs_from_stage2(v);
@@ -216,6 +241,7 @@ __device__ __forceinline__ void turbo64_decode_warp(const Prefetch64& f, T* __re
         for (int i = 0; i < 32; ++i) v[i] = mul2(v[i], scale);
     }
     PairStore<T>::row(v, sign, stage + lane * Stage::PITCHB);
+    }
     __syncwarp();
     // transposed read-out: chunk c = k*32 + lane of the item's contiguous output
     const unsigned char* src = stage + (lane / Stage::CPR) * Stage::PITCHB + (lane % Stage::CPR) * 16;
@@ -374,7 +400,10 @@ cache_decode_kernel(const __grid_constant__ Cache64Params p) {
         for (int idx = threadIdx.x; idx < ENTRIES * 32; idx += CD_THREADS) {
             const int e = idx >> 5;
             const float a = p.book.c[e & ((1 << BITS) - 1)], b = p.book.c[e >> BITS];
-            *reinterpret_cast<float2*>(table + idx * 8) = make_float2(a + b, a - b);
+            if (D == 128 && BITS == 4)      // 4-byte entries, own code in the low nibble: see turbo64_decode_warp
+                *reinterpret_cast<float*>(table + e * 256 + (idx & 31) * 4) = (idx & 1) ? b - a : a + b;
+            else
+                *reinterpret_cast<float2*>(table + idx * 8) = make_float2(a + b, a - b);
         }
         if (threadIdx.x < 4 * 64) {
             const int pl = threadIdx.x >> 6, i = threadIdx.x & 63;       // packed pair i = coordinates 2i, 2i+1
