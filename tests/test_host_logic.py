@@ -66,6 +66,51 @@ def test_validation_happens_before_any_device_work(lib):
     assert g(64, 1, 64, 0, ok, ok, ok, 1, None) == 2 and g(64, 4, 0, 0, ok, ok, ok, 1, None) == 1
 
 
+def _cache_desc(dim=64, segments=48, tokens=32768, k=(2, 4, 64), v=(0, 4, 0)):
+    from pitch_b200 import _native
+    d = _native.CacheDesc()
+    d.dim, d.out_dtype, d.segments, d.tokens, d.n_planes = dim, 2, segments, tokens, 2
+    for pl, (kind, bits, group) in zip(d.planes, (k, v)):
+        pl.kind, pl.bits, pl.group_size = kind, bits, group
+        pl.codes = pl.side = pl.out = 0x10000
+        pl.codes_seg_stride = pl.side_seg_stride = pl.out_seg_stride = 1 << 30
+    return d
+
+
+def test_attention_workspace_and_shape_rules(lib):
+    """Pure host logic of the cache attention entry point: run partitioning and refusals."""
+    import ctypes as C
+    from pitch_b200 import _native
+    ws = lib.pitch_cache_attention_workspace
+    d = _cache_desc()
+    # 48 x 1024 tiles over 2368 resident warps -> runs of 21 tiles, 49 runs per segment
+    assert ws(C.byref(d), 7) == 48 * 49 * 7 * 66 * 4
+    assert ws(C.byref(_cache_desc(segments=1, tokens=31)), 8) == 1 * 1 * 8 * 66 * 4
+    assert ws(C.byref(_cache_desc(segments=2, tokens=5000)), 1) == 2 * 40 * 1 * 66 * 4      # at least 4 tiles per run
+    for bad in (_cache_desc(dim=128), _cache_desc(k=(2, 4, 48)), _cache_desc(k=(2, 2, 64)), _cache_desc(k=(0, 4, 0)),
+                _cache_desc(v=(1, 4, 0)), _cache_desc(v=(0, 3, 0)), _cache_desc(tokens=0)):
+        assert ws(C.byref(bad), 4) == -1 and lib.pitch_last_error()
+    assert ws(C.byref(d), 0) == -1 and ws(C.byref(d), 9) == -1
+    args = _native.AttentionArgs(0x10000, 0x20000, 0x30000, 16, 7, 0.125)
+    assert lib.pitch_enqueue_cache_attention(C.byref(d), C.byref(args), None) == 1          # workspace too small
+    assert b"workspace" in lib.pitch_last_error()
+    args = _native.AttentionArgs(0x10000, 0x20000, 0x30000, 1 << 30, 7, 0.0)
+    assert lib.pitch_enqueue_cache_attention(C.byref(d), C.byref(args), None) == 1 and b"scale" in lib.pitch_last_error()
+
+
+def test_rope_bias_argument_rules(lib):
+    import ctypes as C
+    from pitch_b200 import _native
+    f = lib.pitch_enqueue_rope_bias
+    rope = _native.RopeBias(0x1000, 256, 0x2000, 0x3000, 100)
+    assert f(12, 0, 1, 0x4000, 1024, 1, 0, 4, C.byref(rope), None) == 3                      # dim not a multiple of 8
+    assert f(64, 5, 1, 0x4000, 1024, 1, 0, 4, C.byref(rope), None) == 1                      # unknown dtype
+    assert f(64, 0, 1, 0x4000, 1024, 1, 98, 4, C.byref(rope), None) == 1 and b"rotary tables" in lib.pitch_last_error()
+    assert f(64, 0, 1, 0x4004, 1024, 1, 0, 4, C.byref(rope), None) == 1 and b"aligned" in lib.pitch_last_error()
+    assert f(64, 0, 1, 0x4000, 1024, 1, 0, 4, None, None) == 1
+    assert f(64, 0, 1, 0x4000, 512, 2, 0, 4, C.byref(rope), None) == 1 and b"stride" in lib.pitch_last_error()
+
+
 def test_missing_library_fails_loudly(tmp_path, monkeypatch):
     from pitch_b200 import KernelUnavailable, _native
     monkeypatch.setattr(_native, "_lib", None)
