@@ -78,9 +78,20 @@ def as_buffer(t, offset: int, name: str) -> Buffer:
     return Buffer(t.data_ptr(), t.numel() * t.element_size(), int(offset))
 
 
+_raw_stream = None
+
+
 def stream_handle(stream, device) -> int:
-    torch = _torch()
+    """The ``cudaStream_t`` to launch on: ``stream`` (a torch stream or a raw handle), or the
+    device's current torch stream."""
+    global _raw_stream
     if stream is None:
+        torch = _torch()
+        if _raw_stream is None:
+            # the raw-handle query is several times cheaper than building a Stream object per call
+            _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", False)
+        if _raw_stream and device.index is not None:
+            return _raw_stream(device.index)
         return torch.cuda.current_stream(device).cuda_stream
     if isinstance(stream, int):
         return stream

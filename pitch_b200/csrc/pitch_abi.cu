@@ -1018,6 +1018,7 @@ int pitch_enqueue_cache_attention(const pitch_cache_desc* d, const pitch_attenti
     p.segments = (int)d->segments;
     p.tokens = (int)d->tokens;
     attention_slices(d->segments, d->tokens, &p.splits, &p.tokens_per_split);
+    if ((int64_t)p.segments * p.splits > 0x7FFFFFFF) return fail(PITCH_ERR_INVALID_INPUT, "segments x runs exceeds 2^31 - 1");
     p.n_queries = a->n_queries;
     p.group_size = d->planes[0].group_size;
     p.scale_log2 = (float)((double)a->scale * 1.4426950408889634);
