@@ -358,7 +358,11 @@ def run_ours(args) -> None:
 
     # ---- reduce over ranks: slowest rank sets the time
     stats = torch.tensor([step_ms, decode_ms, e2e_ms], dtype=torch.float64, device=dev)
+    rank_step_ms = [round(step_ms, 5)]
     if world > 1:
+        every = [torch.zeros_like(stats) for _ in range(world)]
+        dist.all_gather(every, stats)                       # per-rank step times, reported next to their maximum
+        rank_step_ms = [round(float(e[0]), 5) for e in every]
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
     step_ms, decode_ms, e2e_ms = (float(x) for x in stats.cpu())
     # verification checksums travel over NCCL (all_gather of four 64-bit words per rank); nothing else does
@@ -397,6 +401,7 @@ def run_ours(args) -> None:
                 "value": round(e2e_bytes / e2e_steps * n_gpus / (e2e_ms * 1e-3) / 1e9, 3), "unit": "GB/s",
                 "h2d_bytes_per_step": int(2 * segments * DIM * 4), "d2h_bytes_per_step": int(d2h),
                 "ms_per_step": round(e2e_ms, 4), "steps": e2e_steps},
+            "rank_ms_per_step": rank_step_ms,
             "gpu_launches": 2 * args.steps,   # per step: one append launch, one whole-cache decode launch
             "clocks": clocks,
             "parity_gate": gate,

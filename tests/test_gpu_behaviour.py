@@ -331,3 +331,57 @@ def test_per_channel_storage_and_json(q):
     assert block.stored_byte_count == 128 * 32 + 2 * 256 + 16
     b2 = q.encode_per_channel(offset_keys(70, 32, 4), dim=32, bits=3, group_size=32)
     assert ChannelCompressedBlock.from_json(b2.to_json()) == b2
+
+
+def test_concurrent_host_threads_on_their_own_streams(q):
+    """The C entry points are re-entrant: two host threads enqueue on two streams at once and each
+    gets exactly what a single thread gets."""
+    import threading
+    import torch
+    from pitch_b200 import ChannelQuantConfig, QuantConfig
+    dev = q.device
+    cfgs = [QuantConfig("turboQuant", 64, 4), QuantConfig("polarQuant", 128, 3), QuantConfig("turboQuant", 256, 5)]
+    ccfg = ChannelQuantConfig(64, 4, 64)
+    n = 4096
+
+    def work(seed, stream, result):
+        g = torch.Generator(device=dev)
+        g.manual_seed(seed)
+        outs = []
+        with torch.cuda.stream(stream) if stream is not None else torch.cuda.stream(torch.cuda.current_stream(dev)):
+            for rep in range(20):
+                for cfg in cfgs:
+                    x = torch.randn((n, cfg.dim), generator=g, device=dev)
+                    codes = torch.empty(n * cfg.code_stride, dtype=torch.uint8, device=dev)
+                    sc = torch.empty(n, device=dev)
+                    y = torch.empty_like(x)
+                    q.enqueue_encode(x, codes, sc, n, cfg, stream=stream)
+                    q.enqueue_decode(codes, sc, y, n, cfg, stream=stream)
+                    outs.append((codes, sc, y))
+                x = torch.randn((n, 64), generator=g, device=dev)
+                codes = torch.empty(n * ccfg.code_stride, dtype=torch.uint8, device=dev)
+                rng_ = torch.empty(ccfg.group_count(n) * 2 * 64, dtype=torch.float16, device=dev)
+                y = torch.empty_like(x)
+                q.enqueue_per_channel_encode(x, codes, rng_, n, ccfg, stream=stream)
+                q.enqueue_per_channel_decode(codes, rng_, y, n, ccfg, stream=stream)
+                outs.append((codes, rng_, y))
+            if stream is not None:
+                stream.synchronize()
+        result.extend(outs)
+
+    serial = [[], []]
+    for i in range(2):
+        work(100 + i, None, serial[i])
+    torch.cuda.synchronize()
+    parallel = [[], []]
+    streams = [torch.cuda.Stream(dev), torch.cuda.Stream(dev)]
+    threads = [threading.Thread(target=work, args=(100 + i, streams[i], parallel[i])) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    torch.cuda.synchronize()
+    for i in range(2):
+        assert len(serial[i]) == len(parallel[i]) == 80
+        for a, b in zip(serial[i], parallel[i]):
+            assert all(torch.equal(u, v) for u, v in zip(a, b))
