@@ -299,14 +299,25 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
     const int R = p.n_queries;
     const uint32_t slot = (uint32_t)lane * 4u;
 
-    for (int idx = threadIdx.x; idx < 256 * 32; idx += AT_THREADS) {
-        const int e = idx >> 5, l = idx & 31;
+    {
+        // one table entry per thread (256 threads, 256 code pairs), written to its 32 lane slots
+        const int e = threadIdx.x;
         uint32_t hi, lo;
         split_pair(p.book.c[e & 15], p.book.c[e >> 4], hi, lo);
-        *reinterpret_cast<uint32_t*>(table + e * 256 + l * 4) = hi;
-        *reinterpret_cast<uint32_t*>(table + e * 256 + 128 + l * 4) = lo;
+        uint4* row = reinterpret_cast<uint4*>(table + e * 256);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {                   // rows are 256 bytes apart: rotate the chunk order per lane
+            const int c = (i + threadIdx.x) & 15;        // so that a store phase spreads over the banks
+            const uint32_t v = c < 8 ? hi : lo;
+            row[c] = make_uint4(v, v, v, v);
+        }
     }
     __syncthreads();
+    // Everything above touched only kernel parameters and shared memory.  Under programmatic
+    // dependent launch this grid may have started before the previous kernel of the stream ended:
+    // wait for it before reading the cache, then let the combine kernel be scheduled early.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
 
     const int n_runs = p.segments * p.splits;
     for (int run = blockIdx.x * AT_WARPS + warp; run < n_runs; run += gridDim.x * AT_WARPS) {
@@ -316,13 +327,6 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
         int w_end = w_begin + p.tokens_per_split;
         if (w_end > p.tokens) w_end = p.tokens;
 
-        __syncwarp();
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {                                // row r = i / 2, channel c; chunk layout as in fold_group
-            const int idx = i * 32 + lane, r = idx >> 6, c = idx & 63;
-            const int chunk = (4 * ((c >> 2) & 3) + (c >> 4)) ^ (4 * (r & 1));
-            qs[r * 64 + 4 * chunk + (c & 3)] = r < R ? p.q[seg * R * 64 + idx] * p.scale_log2 : 0.0f;
-        }
         const __half* k_ranges = reinterpret_cast<const __half*>(p.k_ranges + seg * p.k_ranges_seg) + 2 * lane;
         const unsigned char* kp = p.k_codes + seg * p.k_codes_seg + (int64_t)(w_begin + g) * 32 + t * 8;
         const unsigned char* vp = p.v_codes + seg * p.v_codes_seg + (int64_t)(w_begin + 2 * t) * 32 + g * 4;
@@ -348,6 +352,22 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
         AttnTile bufA, bufB;
         if (w_end - w_begin >= 32) load_attn_tile<true>(bufA, kp, vp, np, 32, g, t);
         else load_attn_tile<false>(bufA, kp, vp, np, w_end - w_begin, g, t);
+
+        // the run's queries, scaled, into shared memory (issued after the first tile's loads so that
+        // the three round trips to memory at the start of a run overlap)
+        float qv[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int idx = i * 32 + lane;
+            qv[i] = (idx >> 6) < R ? __uint_as_float(ldg_stream32(reinterpret_cast<const uint32_t*>(p.q + seg * R * 64 + idx))) : 0.0f;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {                                // row r = i / 2, channel c; chunk layout as in fold_group
+            const int idx = i * 32 + lane, r = idx >> 6, c = idx & 63;
+            const int chunk = (4 * ((c >> 2) & 3) + (c >> 4)) ^ (4 * (r & 1));
+            qs[r * 64 + 4 * chunk + (c & 3)] = qv[i] * p.scale_log2;
+        }
 
         // two tiles per trip so that the prefetch alternates between two register sets
 #define PITCH_TILE(CUR, NXT)                                                                            \
@@ -407,21 +427,36 @@ attention_combine_kernel(const __grid_constant__ AttentionParams p) {
     const int r = blockIdx.x;
     const int64_t seg = blockIdx.y;
     const int R = p.n_queries;
+    asm volatile("griddepcontrol.wait;" ::: "memory");       // the partial results of the kernel before this one
     const float* base = p.work + (seg * p.splits * R + r) * AT_PART_FLOATS;
     const int64_t stride = (int64_t)R * AT_PART_FLOATS;
     float mm = -INFINITY;
     float2 a = make_float2(0.0f, 0.0f);
     float ll = 0.0f;
-    for (int s = warp; s < p.splits; s += AT_COMBINE_WARPS) {
-        const float* src = base + s * stride;
-        const float ms = src[0], ls = src[1];
-        const float2 v = *reinterpret_cast<const float2*>(src + 2 + 2 * lane);
-        const float mn = fmaxf(mm, ms);
-        const float fo = fast_exp2(mm - mn), fn = fast_exp2(ms - mn);     // every run holds at least one token
-        a.x = fmaf(v.x, fn, a.x * fo);
-        a.y = fmaf(v.y, fn, a.y * fo);
-        ll = fmaf(ls, fn, ll * fo);
-        mm = mn;
+    for (int s0 = warp; s0 < p.splits; s0 += 4 * AT_COMBINE_WARPS) {
+        // four runs in flight per warp
+        float ms[4], ls[4];
+        float2 v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int s = s0 + k * AT_COMBINE_WARPS;
+            ms[k] = -INFINITY; ls[k] = 0.0f; v[k] = make_float2(0.0f, 0.0f);
+            if (s < p.splits) {
+                const float* src = base + s * stride;
+                ms[k] = src[0]; ls[k] = src[1];
+                v[k] = *reinterpret_cast<const float2*>(src + 2 + 2 * lane);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (ms[k] == -INFINITY) continue;                             // beyond the last run
+            const float mn = fmaxf(mm, ms[k]);
+            const float fo = fast_exp2(mm - mn), fn = fast_exp2(ms[k] - mn);
+            a.x = fmaf(v[k].x, fn, a.x * fo);
+            a.y = fmaf(v[k].y, fn, a.y * fo);
+            ll = fmaf(ls[k], fn, ll * fo);
+            mm = mn;
+        }
     }
     if (lane == 0) { part[warp][0] = mm; part[warp][1] = ll; }
     *reinterpret_cast<float2*>(&part[warp][2 + 2 * lane]) = a;

@@ -955,9 +955,12 @@ int pitch_enqueue_cache_append_noalloc(const pitch_cache_desc* d, const pitch_ap
 // the workspace size can be computed ahead of the call: runs of whole 32-token tiles, about one
 // run per warp that a 148-SM GPU keeps resident (16 per SM), at least 4 tiles long.
 static void attention_slices(int64_t segments, int64_t tokens, int* splits, int* tokens_per_split) {
-    const int64_t tiles = ceil_div(tokens, 32);
-    int64_t run = ceil_div(segments * tiles, 148 * 16);
+    const int64_t tiles = ceil_div(tokens, 32), slots = 148 * 16;
+    int64_t run = ceil_div(segments * tiles, slots);
     if (run < 4) run = 4;
+    // rounding the runs per segment up must not push the total past the resident warps: a few
+    // left-over runs would cost a whole second round
+    while (run < tiles && segments * ceil_div(tiles, run) > slots && segments <= slots) ++run;
     if (run > tiles) run = tiles;
     *tokens_per_split = (int)(run * 32);
     *splits = (int)ceil_div(tiles, run);
@@ -1051,10 +1054,26 @@ int pitch_enqueue_cache_attention(const pitch_cache_desc* d, const pitch_attenti
         // two CTAs of eight warps per SM; a warp takes runs warp, warp + all warps, ...
         int64_t ctas = ceil_div((int64_t)p.segments * p.splits, AT_WARPS);
         if (ctas > 2 * sm_count()) ctas = 2 * sm_count();
-        attention_partial_kernel<<<(unsigned)ctas, AT_THREADS, AT_SMEM_BYTES, s>>>(p);
+        // Both launches are programmatic dependent launches: each grid may be scheduled while the
+        // kernel before it in the stream is still running, sets itself up, then waits for that
+        // kernel to complete before it reads what it wrote.
+        cudaLaunchAttribute pdl[1];
+        pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        pdl[0].val.programmaticStreamSerializationAllowed = 1;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)ctas);
+        cfg.blockDim = dim3(AT_THREADS);
+        cfg.dynamicSmemBytes = AT_SMEM_BYTES;
+        cfg.stream = s;
+        cfg.attrs = pdl;
+        cfg.numAttrs = 1;
+        cudaLaunchKernelEx(&cfg, attention_partial_kernel, p);
+        if ((st = launch_status(false, "cache_attention"))) return st;
+        cfg.gridDim = dim3((unsigned)p.n_queries, (unsigned)p.segments);
+        cfg.blockDim = dim3(32 * AT_COMBINE_WARPS);
+        cfg.dynamicSmemBytes = 0;
+        cudaLaunchKernelEx(&cfg, attention_combine_kernel, p);
     }
-    if ((st = launch_status(false, "cache_attention"))) return st;
-    attention_combine_kernel<<<dim3((unsigned)p.n_queries, (unsigned)p.segments), 32 * AT_COMBINE_WARPS, 0, s>>>(p);
     return launch_status(false, "cache_attention (combine)");
 }
 
