@@ -32,7 +32,7 @@
 //    second product (token pairs per thread, one query) through movmatrix transposes.
 // Free permutations make this cheap: the order of channels inside the first contraction and of
 // output coordinates in the second is chosen to match how codes sit in their words.
-// Thread (g, t) = (lane / 4, lane % 4).  Rows >= n_queries carry a zero query and are discarded.
+// Thread (g, t) = (lane / 4, lane % 4).  Rows >= n_queries repeat query 0 and are discarded.
 //
 // Kernel 1 (attention_partial_kernel): every warp is on its own.  The tokens of a segment are cut
 // into runs of whole tiles, about one run per resident warp of the GPU; a warp walks its run with
@@ -46,11 +46,15 @@
 
 namespace pitch {
 
-constexpr int AT_THREADS = 256;
+constexpr int AT_THREADS = 512;
 constexpr int AT_WARPS = AT_THREADS / 32;
 constexpr int AT_MAX_QUERIES = 8;
 constexpr int AT_PART_FLOATS = 66;                     // per (segment, slice, query): max, sum, 64 accumulators
-constexpr int AT_WARP_SMEM = 8 * 64 * 4 + 512 + 12 * 32 * 8;   // per warp: scaled queries; per-group steps and offsets of the keys; folded query
+constexpr int AT_STAGE_K = 32 * 32;                    // a tile's key codes, 32 bytes per token
+constexpr int AT_STAGE_V = 32 * 48;                    // a tile's value codes, rows padded to 48 bytes (bank spread)
+constexpr int AT_STAGE_BYTES = AT_STAGE_K + AT_STAGE_V + 128;       // + 32 norms
+// per warp: per-group steps and offsets of the keys; folded query; two tile buffers (one in flight)
+constexpr int AT_WARP_SMEM = 512 + 12 * 32 * 8 + 2 * AT_STAGE_BYTES;
 constexpr int AT_SMEM_BYTES = CD_TABLE_BYTES + AT_WARPS * AT_WARP_SMEM;
 constexpr int AT_COMBINE_WARPS = 8;
 
@@ -107,36 +111,32 @@ __device__ __forceinline__ uint32_t key_pair(uint32_t w) {
     return (s & 0x00780078u) | 0x41804180u;
 }
 
-struct AttnTile {                 // what thread (g, t) loads for a tile of 32 tokens (two blocks of 16)
-    uint2 k[2][2];                // words 2t, 2t+1 of tokens 16m + g and 16m + g + 8
-    uint32_t v[2][4];             // word g of tokens 16m + {2t, 2t+1, 2t+8, 2t+9}
-    float n[2][2];                // norms of tokens 16m + g and 16m + g + 8
-};
-
-// kp, vp, np point at this thread's first key word pair, value word and norm of the tile.
-template <bool WHOLE>
-__device__ __forceinline__ void load_attn_tile(AttnTile& f, const unsigned char* __restrict__ kp,
-                                               const unsigned char* __restrict__ vp, const float* __restrict__ np,
-                                               int nvalid, int g, int t) {
+// Starts the asynchronous copy of a tile (32 tokens from `tok`, `nvalid` of them existing) into a
+// warp's tile buffer: key codes, value codes, norms.  Bytes of tokens that do not exist are
+// zero-filled without touching memory.
+__device__ __forceinline__ void issue_attn_tile(unsigned char* stage, const unsigned char* __restrict__ k_codes,
+                                                const unsigned char* __restrict__ v_codes,
+                                                const float* __restrict__ v_norms, int tok, int nvalid, int lane) {
+    const uint32_t base = (uint32_t)__cvta_generic_to_shared(stage);
+    const unsigned char* ksrc = k_codes + (int64_t)tok * 32;
+    const unsigned char* vsrc = v_codes + (int64_t)tok * 32;
 #pragma unroll
-    for (int m = 0; m < 2; ++m) {
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const int row = 16 * m + 8 * h;
-            f.k[m][h] = make_uint2(0u, 0u);
-            f.n[m][h] = 0.0f;
-            if (WHOLE || row + g < nvalid) {
-                f.k[m][h] = ldg_stream64(reinterpret_cast<const uint2*>(kp + row * 32));
-                f.n[m][h] = __uint_as_float(ldg_stream32(reinterpret_cast<const uint32_t*>(np + row)));
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int row = 16 * m + (j & 1) + 8 * (j >> 1);
-            f.v[m][j] = 0u;
-            if (WHOLE || row + 2 * t < nvalid) f.v[m][j] = ldg_stream32(reinterpret_cast<const uint32_t*>(vp + row * 32));
-        }
+    for (int i = 0; i < 2; ++i) {
+        const int c = lane + 32 * i, token = c >> 1;                 // 16-byte chunk c of the tile's 1024 code bytes
+        const int live = token < nvalid ? 16 : 0;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                     :: "r"(base + c * 16), "l"(live ? ksrc + c * 16 : ksrc), "r"(live) : "memory");
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                     :: "r"(base + AT_STAGE_K + token * 48 + (c & 1) * 16), "l"(live ? vsrc + c * 16 : vsrc), "r"(live) : "memory");
     }
+    if (lane < 8) {
+        int live = nvalid * 4 - 16 * lane;
+        live = live < 0 ? 0 : (live > 16 ? 16 : live);
+        const float* nsrc = v_norms + tok;
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;"
+                     :: "r"(base + AT_STAGE_K + AT_STAGE_V + lane * 16), "l"(live ? nsrc + 4 * lane : nsrc), "r"(live) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
 struct AttnState {
@@ -144,13 +144,20 @@ struct AttnState {
     float acc[4][4];              // out^T fragments: [block of 16 coordinates][fragment register]
 };
 
-// One tile: scores, online softmax, value accumulation.  qf: this lane's folded-query fragments
+// One tile: scores, online softmax, value accumulation.  kb / vb / nb: this lane's places in the
+// tile buffer (key row g words 2t, 2t+1; value row 2t word g; norm g); qf: its folded-query fragments
 // in shared memory (stride 32 entries); bias0/1: score offsets of queries 2t and 2t + 1.
-__device__ __forceinline__ void attn_tile(const AttnTile& f, AttnState& st, const uint2* qf,
+__device__ __forceinline__ void attn_tile(const unsigned char* kb, const unsigned char* vb, const unsigned char* nb,
+                                          AttnState& st, const uint2* qf,
                                           float bias0, float bias1, int nvalid, const unsigned char* table,
                                           uint32_t slot, int g) {
     // ---- scores^T: two blocks of 16 tokens x 8 queries; one accumulator per part of the query, so
     //      that six short chains of products are in flight instead of two long ones
+    uint2 kc[2][2];                                               // words 2t, 2t+1 of tokens 16m + g and 16m + g + 8
+#pragma unroll
+    for (int m = 0; m < 2; ++m)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) kc[m][h] = *reinterpret_cast<const uint2*>(kb + (16 * m + 8 * h) * 32);
     float sc[2][4], sm[2][4], sl[2][4];
 #pragma unroll
     for (int m = 0; m < 2; ++m) {
@@ -163,8 +170,8 @@ __device__ __forceinline__ void attn_tile(const AttnTile& f, AttnState& st, cons
         const uint2 qh = qf[(0 * 4 + KB) * 32], qm = qf[(1 * 4 + KB) * 32], ql = qf[(2 * 4 + KB) * 32]; \
         _Pragma("unroll")                                                                            \
         for (int m = 0; m < 2; ++m) {                                                                \
-            const uint32_t a0 = key_pair<KB>(f.k[m][0].x), a1 = key_pair<KB>(f.k[m][1].x);           \
-            const uint32_t a2 = key_pair<KB>(f.k[m][0].y), a3 = key_pair<KB>(f.k[m][1].y);           \
+            const uint32_t a0 = key_pair<KB>(kc[m][0].x), a1 = key_pair<KB>(kc[m][1].x);             \
+            const uint32_t a2 = key_pair<KB>(kc[m][0].y), a3 = key_pair<KB>(kc[m][1].y);             \
             mma_bf16(sc[m], a0, a1, a2, a3, qh.x, qh.y);                                             \
             mma_bf16(sm[m], a0, a1, a2, a3, qm.x, qm.y);                                             \
             mma_bf16(sl[m], a0, a1, a2, a3, ql.x, ql.y);                                             \
@@ -207,7 +214,8 @@ __device__ __forceinline__ void attn_tile(const AttnTile& f, AttnState& st, cons
             const float p0 = fast_exp2(sc[m][2 * h] - st.m0), p1 = fast_exp2(sc[m][2 * h + 1] - st.m1);
             st.l0 += p0; st.l1 += p1;
             uint32_t hi, lo;
-            split_pair(p0 * f.n[m][h], p1 * f.n[m][h], hi, lo);
+            const float norm = *reinterpret_cast<const float*>(nb + (16 * m + 8 * h) * 4);
+            split_pair(p0 * norm, p1 * norm, hi, lo);
             wh[m][h] = transpose8x8(hi);
             wl[m][h] = transpose8x8(lo);
         }
@@ -216,10 +224,14 @@ __device__ __forceinline__ void attn_tile(const AttnTile& f, AttnState& st, cons
 #pragma unroll
     for (int m = 0; m < 2; ++m) {
         // coordinate-wise interleave of the token pairs (2t, 2t+1) and (2t+8, 2t+9)
-        const uint32_t ea = (f.v[m][0] & 0x0F0F0F0Fu) | ((f.v[m][1] << 4) & 0xF0F0F0F0u);   // even coordinates
-        const uint32_t oa = ((f.v[m][0] >> 4) & 0x0F0F0F0Fu) | (f.v[m][1] & 0xF0F0F0F0u);   // odd coordinates
-        const uint32_t eb = (f.v[m][2] & 0x0F0F0F0Fu) | ((f.v[m][3] << 4) & 0xF0F0F0F0u);
-        const uint32_t ob = ((f.v[m][2] >> 4) & 0x0F0F0F0Fu) | (f.v[m][3] & 0xF0F0F0F0u);
+        // word g of tokens 16m + {2t, 2t+1, 2t+8, 2t+9}
+        const unsigned char* vrow = vb + 16 * m * 48;
+        const uint32_t v0 = *reinterpret_cast<const uint32_t*>(vrow), v1 = *reinterpret_cast<const uint32_t*>(vrow + 48);
+        const uint32_t v2 = *reinterpret_cast<const uint32_t*>(vrow + 8 * 48), v3 = *reinterpret_cast<const uint32_t*>(vrow + 9 * 48);
+        const uint32_t ea = (v0 & 0x0F0F0F0Fu) | ((v1 << 4) & 0xF0F0F0F0u);   // even coordinates
+        const uint32_t oa = ((v0 >> 4) & 0x0F0F0F0Fu) | (v1 & 0xF0F0F0F0u);   // odd coordinates
+        const uint32_t eb = (v2 & 0x0F0F0F0Fu) | ((v3 << 4) & 0xF0F0F0F0u);
+        const uint32_t ob = ((v2 >> 4) & 0x0F0F0F0Fu) | (v3 & 0xF0F0F0F0u);
         uint32_t ch[4][4], cl[4][4];                               // [coordinate block][fragment register]
 #pragma unroll
         for (int mb = 0; mb < 4; ++mb) {
@@ -245,24 +257,26 @@ __device__ __forceinline__ void attn_tile(const AttnTile& f, AttnState& st, cons
 // (three bf16 parts, left in shared memory: qf[(part * 4 + block of 16 channels) * 32 + lane])
 // and the score bias of queries 2t and 2t + 1.  lo2 / hi2: this lane's two
 // channels of the group's fp16 minima and maxima.
-__device__ __forceinline__ void fold_group(uint32_t lo2, uint32_t hi2, const float* qs, float* gstep, float* goff,
+__device__ __forceinline__ void fold_group(uint32_t lo2, uint32_t hi2, const float* __restrict__ qrow, float qscale, float* gstep, float* goff,
                                            uint2* qf, float& bias0, float& bias1, int lane, int g, int t) {
     const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&lo2));
     const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&hi2));
     const float s0 = step15(lo.x, hi.x), s1 = step15(lo.y, hi.y);
-    // Shared-memory layout of the per-channel rows (steps, offsets, each query): the 16-byte chunk
-    // of channels 16t + 4i ... + 3 sits at chunk index 4i + t (for queries: xor 4 on odd rows), so
-    // that the eight lanes of a 128-bit load phase touch eight different bank groups.
+    // Shared-memory layout of the per-channel rows (steps, offsets): the 16-byte chunk of channels
+    // 16t + 4i ... + 3 sits at chunk index 4i + t, so that the lanes of a 128-bit load phase touch
+    // different bank groups.
     const int chunk = 4 * ((lane >> 1) & 3) + (lane >> 3);            // of channels 2 * lane, 2 * lane + 1
     __syncwarp();
-    *reinterpret_cast<float2*>(gstep + 4 * chunk + (2 * lane & 3)) = make_float2(s0, s1);
-    *reinterpret_cast<float2*>(goff + 4 * chunk + (2 * lane & 3)) = make_float2(fmaf(-16.0f, s0, lo.x), fmaf(-16.0f, s1, lo.y));
+    // both already carry the softmax scale (base 2), so the query is used as it is
+    *reinterpret_cast<float2*>(gstep + 4 * chunk + (2 * lane & 3)) = make_float2(s0 * qscale, s1 * qscale);
+    *reinterpret_cast<float2*>(goff + 4 * chunk + (2 * lane & 3)) =
+        make_float2(fmaf(-16.0f, s0, lo.x) * qscale, fmaf(-16.0f, s1, lo.y) * qscale);
     __syncwarp();
     float x[16];
     float b = 0.0f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const float4 qv = *reinterpret_cast<const float4*>(qs + g * 64 + 4 * ((4 * i + t) ^ (4 * (g & 1))));
+        const float4 qv = __ldg(reinterpret_cast<const float4*>(qrow + 16 * t + 4 * i));     // query g
         const float4 sv = *reinterpret_cast<const float4*>(gstep + 4 * (4 * i + t));
         const float4 ov = *reinterpret_cast<const float4*>(goff + 4 * (4 * i + t));
         x[4 * i] = qv.x * sv.x; x[4 * i + 1] = qv.y * sv.y; x[4 * i + 2] = qv.z * sv.z; x[4 * i + 3] = qv.w * sv.w;
@@ -284,7 +298,7 @@ __device__ __forceinline__ void fold_group(uint32_t lo2, uint32_t hi2, const flo
     bias1 = __shfl_sync(0xFFFFFFFFu, b, 8 * t + 4);       // of query 2t + 1
 }
 
-__global__ void __launch_bounds__(AT_THREADS, 2)
+__global__ void __launch_bounds__(AT_THREADS, 1)
 attention_partial_kernel(const __grid_constant__ AttentionParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];
     // byte (na | nb << 4) of two tokens' codes, lane slot l: the bf16 pair (c[na], c[nb]) as hi parts at
@@ -292,15 +306,15 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
     unsigned char* table = smem;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    float* qs = reinterpret_cast<float*>(smem + CD_TABLE_BYTES + warp * AT_WARP_SMEM);     // [8][64] query * scale (base 2)
-    float* gstep = qs + 8 * 64;                                                             // [64]
+    float* gstep = reinterpret_cast<float*>(smem + CD_TABLE_BYTES + warp * AT_WARP_SMEM);   // [64]
     float* goff = gstep + 64;                                                               // [64] lo - 16 * step
     uint2* qf = reinterpret_cast<uint2*>(goff + 64);                                        // [3 parts][4 blocks][32 lanes]
+    unsigned char* stage0 = reinterpret_cast<unsigned char*>(qf + 12 * 32);                 // two tile buffers
     const int R = p.n_queries;
     const uint32_t slot = (uint32_t)lane * 4u;
 
-    {
-        // one table entry per thread (256 threads, 256 code pairs), written to its 32 lane slots
+    if (threadIdx.x < 256) {
+        // one table entry per thread (256 code pairs), written to its 32 lane slots
         const int e = threadIdx.x;
         uint32_t hi, lo;
         split_pair(p.book.c[e & 15], p.book.c[e >> 4], hi, lo);
@@ -328,9 +342,12 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
         if (w_end > p.tokens) w_end = p.tokens;
 
         const __half* k_ranges = reinterpret_cast<const __half*>(p.k_ranges + seg * p.k_ranges_seg) + 2 * lane;
-        const unsigned char* kp = p.k_codes + seg * p.k_codes_seg + (int64_t)(w_begin + g) * 32 + t * 8;
-        const unsigned char* vp = p.v_codes + seg * p.v_codes_seg + (int64_t)(w_begin + 2 * t) * 32 + g * 4;
-        const float* np = reinterpret_cast<const float*>(p.v_norms + seg * p.v_norms_seg) + w_begin + g;
+        const unsigned char* k_codes = p.k_codes + seg * p.k_codes_seg;
+        const unsigned char* v_codes = p.v_codes + seg * p.v_codes_seg;
+        const float* v_norms = reinterpret_cast<const float*>(p.v_norms + seg * p.v_norms_seg);
+        // this lane's query row (query g); rows beyond n_queries repeat query 0 and are never written out
+        const float* qrow = p.q + (seg * R + (g < R ? g : 0)) * 64;
+        const float qscale = p.scale_log2;
 
         AttnState st;
         st.m0 = st.m1 = -INFINITY;
@@ -341,6 +358,10 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
             for (int i = 0; i < 4; ++i) st.acc[mb][i] = 0.0f;
         float bias0 = 0.0f, bias1 = 0.0f;
 
+        // the first tile is on its way before anything else of the run is fetched
+        __syncwarp();
+        issue_attn_tile(stage0, k_codes, v_codes, v_norms, w_begin, w_end - w_begin, lane);
+
         // the ranges of the first group; those of the following group are fetched a group ahead
         int group = w_begin / p.group_size;
         const int last_group = (w_end - 1) / p.group_size;
@@ -349,49 +370,38 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
         uint32_t hi2 = ldg_stream32(reinterpret_cast<const uint32_t*>(k_ranges + (int64_t)group * 128 + 64));
         bool fold = true;
 
-        AttnTile bufA, bufB;
-        if (w_end - w_begin >= 32) load_attn_tile<true>(bufA, kp, vp, np, 32, g, t);
-        else load_attn_tile<false>(bufA, kp, vp, np, w_end - w_begin, g, t);
-
-        // the run's queries, scaled, into shared memory (issued after the first tile's loads so that
-        // the three round trips to memory at the start of a run overlap)
-        float qv[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const int idx = i * 32 + lane;
-            qv[i] = (idx >> 6) < R ? __uint_as_float(ldg_stream32(reinterpret_cast<const uint32_t*>(p.q + seg * R * 64 + idx))) : 0.0f;
-        }
-        __syncwarp();
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {                                // row r = i / 2, channel c; chunk layout as in fold_group
-            const int idx = i * 32 + lane, r = idx >> 6, c = idx & 63;
-            const int chunk = (4 * ((c >> 2) & 3) + (c >> 4)) ^ (4 * (r & 1));
-            qs[r * 64 + 4 * chunk + (c & 3)] = qv[i] * p.scale_log2;
-        }
-
-        // two tiles per trip so that the prefetch alternates between two register sets
-#define PITCH_TILE(CUR, NXT)                                                                            \
+        // this lane's places in tile buffer 0; buffer 1 is AT_STAGE_BYTES further
+        const unsigned char* kb = stage0 + g * 32 + t * 8;
+        const unsigned char* vb = stage0 + AT_STAGE_K + 2 * t * 48 + g * 4;
+        const unsigned char* nb = stage0 + AT_STAGE_K + AT_STAGE_V + g * 4;
+#define PITCH_TILE(BUF)                                                                                  \
         {                                                                                               \
-            const int nvalid = w_end - t0;                                                              \
-            kp += 1024; vp += 1024; np += 32;                                                           \
-            if (nvalid >= 64) load_attn_tile<true>(NXT, kp, vp, np, 32, g, t);                          \
-            else if (nvalid > 32) load_attn_tile<false>(NXT, kp, vp, np, nvalid - 32, g, t);            \
+            const int nvalid = w_end - t0;                            /* >= 32 for a whole tile */      \
+            if (nvalid > 32) {                                                                          \
+                issue_attn_tile(stage0 + (1 - BUF) * AT_STAGE_BYTES, k_codes, v_codes, v_norms, t0 + 32, nvalid - 32, lane); \
+                cp_async_wait<1>();                                                                     \
+            } else {                                                                                    \
+                cp_async_wait<0>();                                                                     \
+            }                                                                                           \
+            __syncwarp();                                                                               \
             if (t0 >= group_end) { ++group; group_end += p.group_size; fold = true; }                  \
             if (fold) {                                                                                 \
                 fold = false;                                                                           \
-                fold_group(lo2, hi2, qs, gstep, goff, qf, bias0, bias1, lane, g, t);                    \
+                fold_group(lo2, hi2, qrow, qscale, gstep, goff, qf, bias0, bias1, lane, g, t);          \
                 if (group < last_group) {                                                               \
                     lo2 = ldg_stream32(reinterpret_cast<const uint32_t*>(k_ranges + (int64_t)(group + 1) * 128));      \
                     hi2 = ldg_stream32(reinterpret_cast<const uint32_t*>(k_ranges + (int64_t)(group + 1) * 128 + 64)); \
                 }                                                                                       \
             }                                                                                           \
-            attn_tile(CUR, st, qf + lane, bias0, bias1, nvalid, table, slot, g);                               \
+            attn_tile(kb + BUF * AT_STAGE_BYTES, vb + BUF * AT_STAGE_BYTES, nb + BUF * AT_STAGE_BYTES, st, qf + lane,  \
+                      bias0, bias1, nvalid, table, slot, g);                                            \
+            __syncwarp();                                             /* this buffer is refilled two tiles on */ \
         }
         for (int t0 = w_begin; t0 < w_end; t0 += 32) {
-            PITCH_TILE(bufA, bufB)
+            PITCH_TILE(0)
             t0 += 32;
             if (t0 >= w_end) break;
-            PITCH_TILE(bufB, bufA)
+            PITCH_TILE(1)
         }
 #undef PITCH_TILE
 

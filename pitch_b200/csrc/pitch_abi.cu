@@ -1051,9 +1051,9 @@ int pitch_enqueue_cache_attention(const pitch_cache_desc* d, const pitch_attenti
                 return launch_status(false, "cache_attention (shared memory opt-in)");
             configured[dev].store(true, std::memory_order_release);
         }
-        // two CTAs of eight warps per SM; a warp takes runs warp, warp + all warps, ...
+        // one CTA of sixteen warps per SM; a warp takes runs warp, warp + all warps, ...
         int64_t ctas = ceil_div((int64_t)p.segments * p.splits, AT_WARPS);
-        if (ctas > 2 * sm_count()) ctas = 2 * sm_count();
+        if (ctas > sm_count()) ctas = sm_count();
         // Both launches are programmatic dependent launches: each grid may be scheduled while the
         // kernel before it in the stream is still running, sets itself up, then waits for that
         // kernel to complete before it reads what it wrote.
