@@ -34,10 +34,12 @@
 // output coordinates in the second is chosen to match how codes sit in their words.
 // Thread (g, t) = (lane / 4, lane % 4).  Rows >= n_queries repeat query 0 and are discarded.
 //
-// Kernel 1 (attention_partial_kernel): every warp is on its own.  The tokens of a segment are cut
-// into runs of whole tiles, about one run per resident warp of the GPU; a warp walks its run with
-// online softmax (running maximum and sum per query, base-2 exponentials) and writes (max, sum,
-// 64 accumulators) per query to a workspace.  Apart from the table build there is no barrier.
+// Kernel 1 (attention_partial_kernel): one CTA of 16 warps per SM, every warp on its own.  The
+// tokens of a segment are cut into runs of whole tiles, about one run per resident warp of the
+// GPU; a warp walks its run with online softmax (running maximum and sum per query, base-2
+// exponentials), its next tile arriving by asynchronous copies in the second of two shared-memory
+// buffers, and writes (max, sum, 64 accumulators) per query to a workspace.  Apart from the table
+// build there is no barrier.
 // Kernel 2 (attention_combine_kernel): merges the runs of a segment, normalises, un-rotates.
 #pragma once
 
