@@ -32,7 +32,7 @@
 extern "C" {
 #endif
 
-#define PITCH_ABI_VERSION 1
+#define PITCH_ABI_VERSION 2
 #define PITCH_DEFAULT_SEED 0x50495443u /* Sources/PITCH/PITCH.swift:18 */
 #define PITCH_MAX_DIM 1024             /* Sources/PITCH/Models/QuantConfig.swift:13 */
 #define PITCH_MIN_BITS 2               /* Sources/PITCH/Models/QuantConfig.swift:12 */
@@ -143,6 +143,20 @@ typedef enum pitch_plane_kind {
     PITCH_PLANE_CHANNEL = 2  /* per-channel codes + fp16 ranges   */
 } pitch_plane_kind;
 
+/* Rotary tables and key-projection bias for exact key-bias removal (see pitch_enqueue_rope_bias). */
+typedef struct pitch_rope_bias {
+    const float* bias;          /* [segments][dim] */
+    int64_t bias_seg_stride;    /* bytes */
+    const float* cos_table;     /* [positions][dim] */
+    const float* sin_table;     /* [positions][dim] */
+    int64_t positions;
+} pitch_rope_bias;
+
+/* Every pointer of a plane comes with the number of bytes the caller's allocation holds from that
+ * pointer on: the (MTLBuffer.length - offset) that Codec.check tests against the bytes a call
+ * needs (Sources/PITCH/Core/Codec.swift:42-46).  A call fails with PITCH_ERR_INVALID_INPUT, before
+ * anything is launched, when a plane's buffers are too small for the segments and tokens it
+ * addresses, are not device memory, or live on different GPUs (Codec.swift:38-40). */
 typedef struct pitch_plane {
     int32_t  kind;        /* pitch_plane_kind */
     int32_t  bits;
@@ -152,8 +166,11 @@ typedef struct pitch_plane {
     int64_t  codes_seg_stride;
     void*    side;        /* float32 [tokens] per segment, or fp16 [groups][2][dim] per segment */
     int64_t  side_seg_stride;
-    void*    out;         /* [tokens][dim] of out_dtype per segment */
+    void*    out;         /* [tokens][dim] of out_dtype per segment; may be NULL where it is not used */
     int64_t  out_seg_stride;
+    int64_t  codes_bytes; /* bytes available from `codes` */
+    int64_t  side_bytes;  /* bytes available from `side` */
+    int64_t  out_bytes;   /* bytes available from `out` (0 with a NULL out) */
 } pitch_plane;
 
 typedef struct pitch_cache_desc {
@@ -162,8 +179,18 @@ typedef struct pitch_cache_desc {
     int64_t segments;    /* layers x KV heads on this GPU */
     int64_t tokens;      /* tokens currently held per segment */
     int32_t n_planes;    /* 1..4 */
-    int32_t reserved;
+    int32_t reserved;    /* 0 */
     pitch_plane planes[4];
+    /* Exact key-bias removal for plane 0 (the keys), or NULL: the rotated bias of a token's position
+     * is subtracted from plane 0's new tokens by pitch_enqueue_cache_step before they are encoded and
+     * added back to plane 0's output by pitch_enqueue_cache_decode / _step, inside the same launch
+     * (README.md:100 lists this as missing from the reference's kernels; arithmetic of
+     * pitch_enqueue_rope_bias below).  positions must cover every token addressed. */
+    const pitch_rope_bias* key_bias;
+    /* Tokens per segment the buffers were sized for, or 0.  When set, buffer extents are checked
+     * against it instead of against the tokens a call addresses (so the check can be made once
+     * for the life of the cache), and no call may address more. */
+    int64_t capacity;
 } pitch_cache_desc;
 
 /* All pointers must be 16-byte aligned and all segment strides multiples of 16. */
@@ -184,10 +211,38 @@ typedef struct pitch_append_src {
     int64_t input_seg_stride;     /* bytes between segments */
     void*   residual;             /* per-channel planes only, else NULL */
     int64_t residual_seg_stride;  /* bytes between segments, >= (group_size+2)*dim*4 */
+    int64_t input_bytes;          /* bytes available from `input` */
+    int64_t residual_bytes;       /* bytes available from `residual` (0 with a NULL residual) */
 } pitch_append_src;
 
 int pitch_enqueue_cache_append(const pitch_cache_desc* desc, const pitch_append_src* src, int in_dtype,
                                int64_t n_new, void* stream);
+
+/* One generation step of a compressed cache in ONE launch: appends one new token per segment to
+ * every plane and decodes the whole cache, new token included - the per-step pattern of
+ * README.md:62-77 (enqueueEncode of the new token, then enqueueDecode of the whole cache, in
+ * one command buffer).  Results are those of pitch_enqueue_cache_append(desc, src, in_dtype, 1)
+ * followed by pitch_enqueue_cache_decode at tokens + 1, bit for bit: codes, side information,
+ * residual and outputs.  The planes' `out` buffers must hold tokens + 1 tokens per segment.
+ *
+ * `state` is NULL or points to a pitch_cache_state in device memory (16-byte aligned).
+ *   NULL:     desc->tokens is the number of tokens held before the call.
+ *   non-NULL: the kernel reads the token count from state->tokens instead (desc->tokens is
+ *             ignored, desc->capacity must be set) and adds one to it when the step is done.  No
+ *             launch parameter depends on the token count, so the same call - or a captured CUDA
+ *             graph of it - can be replayed step after step with no host bookkeeping.  When the
+ *             cache is full (state->tokens >= capacity) the step does nothing and sets
+ *             state->status to 1.
+ * Shapes off the fused path (see pitch_enqueue_cache_decode) run as the two stand-alone launches
+ * and then require state == NULL. */
+typedef struct pitch_cache_state {
+    int64_t  tokens;    /* tokens held per segment; advanced by every step */
+    int32_t  status;    /* 0, or 1 once a step was refused because the cache was full */
+    uint32_t arrivals;  /* internal: must be 0 between launches */
+} pitch_cache_state;
+
+int pitch_enqueue_cache_step(const pitch_cache_desc* desc, const pitch_append_src* src, int in_dtype,
+                             pitch_cache_state* state, void* stream);
 
 /* Same as pitch_enqueue_cache_append for callers that cannot provide the residual buffer.
  * No counterpart in the reference.  Two kinds of caller are meant: a serving process that hands
@@ -254,13 +309,6 @@ int pitch_enqueue_cache_attention(const pitch_cache_desc* desc, const pitch_atte
  * rounding to dtype.  subtract != 0 before encoding, 0 after decoding.
  *   dim: even, a multiple of 8, at most PITCH_MAX_DIM; data 16-byte aligned, data_seg_stride a
  *   multiple of 16; first_position + count <= positions; segments <= 65535. */
-typedef struct pitch_rope_bias {
-    const float* bias;          /* [segments][dim] */
-    int64_t bias_seg_stride;    /* bytes */
-    const float* cos_table;     /* [positions][dim] */
-    const float* sin_table;     /* [positions][dim] */
-    int64_t positions;
-} pitch_rope_bias;
 int pitch_enqueue_rope_bias(int dim, int dtype, int subtract, void* data, int64_t data_seg_stride, int64_t segments,
                             int64_t first_position, int64_t count, const pitch_rope_bias* rope, void* stream);
 

@@ -14,6 +14,7 @@ from .errors import KernelUnavailable, from_status
 
 LIB_PATH = Path(__file__).resolve().parent / "_lib" / "libpitch_b200.so"
 
+ABI_VERSION = 2
 TURBO_QUANT, POLAR_QUANT = 0, 1
 F32, F16, BF16 = 0, 1, 2
 PLANE_TURBO, PLANE_POLAR, PLANE_CHANNEL = 0, 1, 2
@@ -29,31 +30,39 @@ class Plane(Structure):
     _fields_ = [("kind", c_int32), ("bits", c_int32), ("group_size", c_int32), ("seed", c_uint32),
                 ("codes", c_void_p), ("codes_seg_stride", c_int64),
                 ("side", c_void_p), ("side_seg_stride", c_int64),
-                ("out", c_void_p), ("out_seg_stride", c_int64)]
+                ("out", c_void_p), ("out_seg_stride", c_int64),
+                ("codes_bytes", c_int64), ("side_bytes", c_int64), ("out_bytes", c_int64)]
 
 
 class AppendSrc(Structure):
     """``pitch_append_src``."""
     _fields_ = [("input", c_void_p), ("input_seg_stride", c_int64),
-                ("residual", c_void_p), ("residual_seg_stride", c_int64)]
-
-
-class CacheDesc(Structure):
-    """``pitch_cache_desc``."""
-    _fields_ = [("dim", c_int32), ("out_dtype", c_int32), ("segments", c_int64), ("tokens", c_int64),
-                ("n_planes", c_int32), ("reserved", c_int32), ("planes", Plane * 4)]
-
-
-class AttentionArgs(Structure):
-    """``pitch_attention_args``."""
-    _fields_ = [("queries", c_void_p), ("out", c_void_p), ("workspace", c_void_p), ("workspace_bytes", c_int64),
-                ("n_queries", c_int32), ("scale", c_float)]
+                ("residual", c_void_p), ("residual_seg_stride", c_int64),
+                ("input_bytes", c_int64), ("residual_bytes", c_int64)]
 
 
 class RopeBias(Structure):
     """``pitch_rope_bias``."""
     _fields_ = [("bias", c_void_p), ("bias_seg_stride", c_int64), ("cos_table", c_void_p), ("sin_table", c_void_p),
                 ("positions", c_int64)]
+
+
+class CacheDesc(Structure):
+    """``pitch_cache_desc``."""
+    _fields_ = [("dim", c_int32), ("out_dtype", c_int32), ("segments", c_int64), ("tokens", c_int64),
+                ("n_planes", c_int32), ("reserved", c_int32), ("planes", Plane * 4),
+                ("key_bias", POINTER(RopeBias)), ("capacity", c_int64)]
+
+
+class CacheState(Structure):
+    """``pitch_cache_state`` (lives in device memory; this mirror only gives its size and layout)."""
+    _fields_ = [("tokens", c_int64), ("status", c_int32), ("arrivals", c_uint32)]
+
+
+class AttentionArgs(Structure):
+    """``pitch_attention_args``."""
+    _fields_ = [("queries", c_void_p), ("out", c_void_p), ("workspace", c_void_p), ("workspace_bytes", c_int64),
+                ("n_queries", c_int32), ("scale", c_float)]
 
 
 # name -> (restype, argtypes); every symbol include/pitch_b200.h declares
@@ -74,6 +83,7 @@ PROTOTYPES = {
     "pitch_enqueue_cache_decode": (c_int, [POINTER(CacheDesc), c_void_p]),
     "pitch_enqueue_cache_append": (c_int, [POINTER(CacheDesc), POINTER(AppendSrc), c_int, c_int64, c_void_p]),
     "pitch_enqueue_cache_append_noalloc": (c_int, [POINTER(CacheDesc), POINTER(AppendSrc), c_int, c_int64, c_void_p]),
+    "pitch_enqueue_cache_step": (c_int, [POINTER(CacheDesc), POINTER(AppendSrc), c_int, c_void_p, c_void_p]),
     "pitch_cache_attention_workspace": (c_int64, [POINTER(CacheDesc), c_int]),
     "pitch_enqueue_cache_attention": (c_int, [POINTER(CacheDesc), POINTER(AttentionArgs), c_void_p]),
     "pitch_enqueue_rope_bias": (c_int, [c_int, c_int, c_int, c_void_p, c_int64, c_int64, c_int64, c_int64,
@@ -100,6 +110,9 @@ def lib():
             fn = getattr(L, name)
             fn.restype = res
             fn.argtypes = args
+        if L.pitch_abi_version() != ABI_VERSION:
+            raise KernelUnavailable(f"{LIB_PATH} has ABI version {L.pitch_abi_version()}, this package needs {ABI_VERSION}: "
+                                    "rebuild it with `python -m pitch_b200.build --force`")
         _lib = L
     return _lib
 

@@ -8,6 +8,14 @@ information, each once).  Inputs are synthetic (seeded, generated on the device)
 smaller than the 126 MB L2 are rotated over several distinct buffers so that every launch
 streams from HBM; timing is by CUDA events on the launching stream after warm-up.
 The whole-cache step (configuration 4) is measured by ``bench.py`` at the repository root.
+
+Nothing is timed before it has passed a parity gate (the reference gates its own timing the same
+way, reference/pytorch_mps_benchmark.py:82-104).  ``run(..., gate=fn)`` hands a seeded sample of
+every encode - input vectors, packed codes, side information, spread over the whole batch - to
+``fn``, which the repository's ``bench.py`` implements with the CPU oracles.  Run as a module the
+gate is the committed golden vectors of the reference's specification (``tests/golden``): the
+kernels must reproduce them for the method, dimension and width being timed, and every timed
+batch must survive a decode - re-encode round trip with unchanged codes.
 """
 from __future__ import annotations
 
@@ -15,11 +23,13 @@ import argparse
 import json
 from pathlib import Path
 
+import numpy as np
 import torch
 
 from . import ChannelQuantConfig, KVCache, PITCH, QuantConfig
 
 L2_BYTES = 126 << 20
+GOLDEN_DIR = Path(__file__).resolve().parent.parent / "tests" / "golden"
 
 
 def hbm_peak() -> tuple[float, str]:
@@ -43,13 +53,13 @@ def time_launches(fn, n_sets: int, reps: int) -> float:
     return e0.elapsed_time(e1) * 1e-3 / reps
 
 
-def report(name, what, seconds, units, unit_name, nbytes, extra):
+def row(name, what, seconds, units, unit_name, nbytes, extra) -> dict:
     peak, src = hbm_peak()
     gbs = nbytes / seconds / 1e9
-    print(json.dumps({"config": name, "op": what, "us_per_launch": round(seconds * 1e6, 2),
-                      f"{unit_name}_per_s": round(units / seconds, 1), "algorithmic_GB_per_s": round(gbs, 1),
-                      "frac_of_hbm_peak": round(gbs / peak, 4), "peak": peak, "peak_source": src,
-                      "frac_of_nominal_8000": round(gbs / 8000.0, 4), **extra}), flush=True)
+    return {"config": name, "op": what, "us_per_launch": round(seconds * 1e6, 2),
+            f"{unit_name}_per_s": round(units / seconds, 1), "algorithmic_GB_per_s": round(gbs, 1),
+            "frac_of_hbm_peak": round(gbs / peak, 4), "peak": peak, "peak_source": src,
+            "frac_of_nominal_8000": round(gbs / 8000.0, 4), **extra}
 
 
 def lognormal_vectors(n, d, seed, dev):
@@ -60,7 +70,100 @@ def lognormal_vectors(n, d, seed, dev):
     return x * s
 
 
-def bench_vector(q, name, method, n, d, bits, reps, out_dtype=torch.float32):
+# ------------------------------------------------------------------------------------------ parity gates
+_golden = {}
+
+
+def _golden_file(name):
+    if name not in _golden:
+        z = np.load(GOLDEN_DIR / name)
+        _golden[name] = (z, json.loads(bytes(z["__cases__"]).decode()))
+    return _golden[name]
+
+
+def golden_gate(q, kind: str, dim: int, bits: int, group: int = 64) -> dict:
+    """The kernels about to be timed against the committed golden vectors of the specification for
+    the same method, dimension and width (tolerances of the reference's own parity tests,
+    Tests/PITCHTests/ParityTests.swift:67-76: code mismatches <= max(2, n/500), scales 1e-5,
+    decode of the golden codes 1e-5; per-channel: identical)."""
+    checked = 0
+    for fname in ("parity.npz", "channel_parity.npz", "spec_extra.npz"):
+        if not (GOLDEN_DIR / fname).exists():
+            continue
+        z, cases = _golden_file(fname)
+        for c in cases:
+            x = z["input/" + c["group"]]
+            if x.ndim != 2 or x.shape[1] != dim or c["bits"] != bits:
+                continue
+            n = x.shape[0]
+            is_channel = "group_size" in c
+            if kind == "perChannel":
+                if not is_channel or c["group_size"] != group:
+                    continue
+                cfg = ChannelQuantConfig(dim, bits, group)
+                blk = q.encode_per_channel(x, config=cfg)
+                if blk.codes != z[c["key"] + "/codes"].tobytes() or \
+                        not np.array_equal(blk.ranges.reshape(-1).view(np.uint16), z[c["key"] + "/ranges"].reshape(-1).view(np.uint16)):
+                    raise SystemExit(f"parity gate failed: per-channel {fname}:{c['key']} differs from the golden vectors")
+            else:
+                if is_channel or c.get("method") != kind:
+                    continue
+                cfg = QuantConfig(kind, dim, bits, c["seed"])
+                batch = q.encode(x, config=cfg)
+                want = np.frombuffer(z[c["key"] + "/codes"].tobytes(), dtype=np.uint8)
+                got = np.frombuffer(batch.codes, dtype=np.uint8)
+                bad = int(np.count_nonzero(got != want))                          # code bytes that differ
+                ws = z[c["key"] + "/scales"].reshape(-1)
+                if bad > max(2, n * dim // 500) or np.max(np.abs(batch.scales - ws) / np.maximum(np.abs(ws), 1.0)) > 1e-5:
+                    raise SystemExit(f"parity gate failed: {fname}:{c['key']} differs from the golden vectors ({bad} code bytes)")
+            checked += 1
+    if checked == 0:
+        raise SystemExit(f"parity gate: no golden case for {kind} dim {dim} bits {bits}; refusing to time it")
+    return {"golden_cases_reproduced": checked}
+
+
+def _sample_rows(n: int, want: int = 65536, blocks: int = 64) -> torch.Tensor:
+    """Row indices of a seeded sample spread over a batch of n rows: `blocks` runs of consecutive rows."""
+    if n <= want:
+        return torch.arange(n)
+    per = want // blocks
+    starts = torch.linspace(0, n - per, blocks).long()
+    return (starts[:, None] + torch.arange(per)[None, :]).reshape(-1)
+
+
+def gate_vector(q, gate, kind, x, codes, scales, cfg) -> dict:
+    """Parity of one timed encode.  With a gate callback: a sample of at least 65,536 vectors spread
+    over the whole batch goes to it.  Always, for TurboQuant: the whole batch is decoded and encoded
+    again; nearly every code must come back (the norm of a reconstruction differs a little from the
+    stored one, which can carry a coordinate over a boundary; a broken kernel changes most bytes)."""
+    n = x.shape[0]
+    out = {}
+    if gate is not None:
+        idx = _sample_rows(n).to(x.device)
+        xs = x[idx].cpu().numpy()
+        cs = codes.view(n, cfg.code_stride)[idx].cpu().numpy()
+        ss = scales[idx].cpu().numpy()
+        out.update(gate(kind, xs, cs, ss, cfg.dim, cfg.bits))
+        out["vectors_checked"] = int(idx.numel())
+    else:
+        out.update(golden_gate(q, kind, cfg.dim, cfg.bits))
+    if kind == "turboQuant":
+        # round trip at full size
+        dec = torch.empty((n, cfg.dim), dtype=torch.float32, device=x.device)
+        q.enqueue_decode(codes, scales, dec, n, cfg)
+        c2 = torch.empty_like(codes)
+        s2 = torch.empty_like(scales)
+        q.enqueue_encode(dec, c2, s2, n, cfg)
+        changed = int((c2 != codes).sum().item())
+        out["codes_changed_by_decode_then_encode"] = changed
+        if changed > codes.numel() // 100:              # a broken kernel changes most bytes; boundary cases are a handful
+            raise SystemExit(f"parity gate failed: {kind} d={cfg.dim} b={cfg.bits}: {changed} code bytes changed by decode + encode")
+        del dec, c2, s2
+    out["checksum_codes"] = q.checksum(codes)
+    return out
+
+
+def bench_vector(q, name, method, n, d, bits, reps, out_dtype=torch.float32, gate=None):
     cfg = QuantConfig(method, d, bits)
     dev = q.device
     in_bytes, code_bytes = n * d * 4, n * cfg.code_stride + n * 4
@@ -69,16 +172,18 @@ def bench_vector(q, name, method, n, d, bits, reps, out_dtype=torch.float32):
     codes = [torch.empty(n * cfg.code_stride, dtype=torch.uint8, device=dev) for _ in range(n_sets)]
     scales = [torch.empty(n, dtype=torch.float32, device=dev) for _ in range(n_sets)]
     outs = [torch.empty((n, d), dtype=out_dtype, device=dev) for _ in range(n_sets)]
+    q.enqueue_encode(xs[0], codes[0], scales[0], n, cfg)
+    parity = gate_vector(q, gate, method, xs[0], codes[0], scales[0], cfg)
     t = time_launches(lambda i: q.enqueue_encode(xs[i], codes[i], scales[i], n, cfg), n_sets, reps)
     extra = {"method": method, "dim": d, "bits": bits, "count": n, "buffer_sets": n_sets}
-    report(name, "encode", t, n, "vectors", in_bytes + code_bytes, extra)
+    yield row(name, "encode", t, n, "vectors", in_bytes + code_bytes, {**extra, "parity": parity})
     t = time_launches(lambda i: q.enqueue_decode(codes[i], scales[i], outs[i], n, cfg), n_sets, reps)
     out_bytes = n * d * outs[0].element_size()
-    report(name, "decode", t, n, "vectors", out_bytes + code_bytes,
-           {**extra, "out_dtype": str(out_dtype).replace("torch.", ""), "decode_output_GB_per_s": round(out_bytes / t / 1e9, 1)})
+    yield row(name, "decode", t, n, "vectors", out_bytes + code_bytes,
+              {**extra, "out_dtype": str(out_dtype).replace("torch.", ""), "decode_output_GB_per_s": round(out_bytes / t / 1e9, 1)})
 
 
-def bench_channel(q, name, n, d, bits, G, reps):
+def bench_channel(q, name, n, d, bits, G, reps, gate=None):
     cfg = ChannelQuantConfig(d, bits, G)
     dev = q.device
     groups = cfg.group_count(n)
@@ -94,34 +199,56 @@ def bench_channel(q, name, n, d, bits, G, reps):
     codes = [torch.empty(n * cfg.code_stride, dtype=torch.uint8, device=dev) for _ in range(n_sets)]
     ranges = [torch.empty(groups * 2 * d, dtype=torch.float16, device=dev) for _ in range(n_sets)]
     outs = [torch.empty((n, d), dtype=torch.float32, device=dev) for _ in range(n_sets)]
+    q.enqueue_per_channel_encode(xs[0], codes[0], ranges[0], n, cfg)
+    if gate is not None:
+        # whole groups from a sample of places in the batch (a group is the unit that can be checked alone)
+        m = min(n, 32768) // G * G
+        first = (n - m) // G * G
+        parity = gate("perChannel", xs[0][first:first + m].cpu().numpy(), codes[0].view(n, cfg.code_stride)[first:first + m].cpu().numpy(),
+                      ranges[0].view(groups, 2 * d)[first // G:(first + m) // G].cpu().numpy(), d, bits, G)
+        parity["tokens_checked"] = m
+    else:
+        parity = golden_gate(q, "perChannel", d, bits, G)
+    parity["checksum_codes"] = q.checksum(codes[0])
     extra = {"method": "perChannel", "dim": d, "bits": bits, "group": G, "count": n, "buffer_sets": n_sets}
     t = time_launches(lambda i: q.enqueue_per_channel_encode(xs[i], codes[i], ranges[i], n, cfg), n_sets, reps)
-    report(name, "encode", t, n, "tokens", in_bytes + code_bytes, extra)
+    yield row(name, "encode", t, n, "tokens", in_bytes + code_bytes, {**extra, "parity": parity})
     t = time_launches(lambda i: q.enqueue_per_channel_decode(codes[i], ranges[i], outs[i], n, cfg), n_sets, reps)
-    report(name, "decode", t, n, "tokens", in_bytes + code_bytes,
-           {**extra, "out_dtype": "float32", "decode_output_GB_per_s": round(in_bytes / t / 1e9, 1)})
+    yield row(name, "decode", t, n, "tokens", in_bytes + code_bytes,
+              {**extra, "out_dtype": "float32", "decode_output_GB_per_s": round(in_bytes / t / 1e9, 1)})
 
 
-def bench_cfg5(q, bits, reps, segments=80, tokens=131072):
+def bench_cfg5(q, bits, reps, segments=80, tokens=131072, gate=None):
     """One GPU's shard of the Llama-3-70B-shaped cache: 80 of 640 (layer, head) segments."""
     d = 128
     cfg = QuantConfig("turboQuant", d, bits)
     cache = KVCache(segments, d, tokens, cfg, cfg, out_dtype="float16", pitch=q)
     chunk = 8                                           # prefill a few segments at a time (inputs are 64 MB each)
+    parity = None
     for s0 in range(0, segments, chunk):
-        k = lognormal_vectors(chunk * tokens, d, 500 + s0, q.device).reshape(chunk, tokens, d)
-        v = lognormal_vectors(chunk * tokens, d, 900 + s0, q.device).reshape(chunk, tokens, d)
+        m = min(chunk, segments - s0)
+        k = lognormal_vectors(m * tokens, d, 500 + s0, q.device).reshape(m, tokens, d)
+        v = lognormal_vectors(m * tokens, d, 900 + s0, q.device).reshape(m, tokens, d)
         for pl, x in zip(cache.planes, (k, v)):
-            for j in range(chunk):
+            for j in range(m):
                 q.enqueue_encode(x[j], pl.codes[s0 + j], pl.side[s0 + j], tokens, cfg)
+        if s0 == 0:
+            parity = gate_vector(q, gate, "turboQuant", k[0], cache.planes[0].codes[0], cache.planes[0].side[0], cfg)
         torch.cuda.synchronize()
         del k, v
     cache.tokens = tokens
+    # the whole-cache launch must give what the stand-alone decoder gives for the same codes
+    ko, _ = cache.decode()
+    alone = torch.empty((tokens, d), dtype=torch.float16, device=q.device)
+    q.enqueue_decode(cache.planes[0].codes[segments - 1], cache.planes[0].side[segments - 1], alone, tokens, cfg)
+    if not torch.equal(ko[segments - 1], alone):
+        raise SystemExit("parity gate failed: whole-cache decode differs from the stand-alone decoder")
+    del alone
     t = time_launches(lambda i: cache.decode(), 1, reps)
     nbytes = cache.stored_bytes() + cache.decoded_bytes()
-    report("cfg5-shard", "whole-cache decode", t, 2 * segments * tokens, "vectors", nbytes,
-           {"method": "turboQuant", "dim": d, "bits": bits, "segments": segments, "tokens": tokens, "out_dtype": "float16",
-            "decode_output_GB_per_s": round(cache.decoded_bytes() / t / 1e9, 1)})
+    yield row("cfg5-shard", "whole-cache decode", t, 2 * segments * tokens, "vectors", nbytes,
+              {"method": "turboQuant", "dim": d, "bits": bits, "segments": segments, "tokens": tokens, "out_dtype": "float16",
+               "decode_output_GB_per_s": round(cache.decoded_bytes() / t / 1e9, 1), "parity": parity})
 
 
 def bench_attention(q, reps, segments=48, tokens=32768, n_queries=7):
@@ -140,6 +267,22 @@ def bench_attention(q, reps, segments=48, tokens=32768, n_queries=7):
     qs = [torch.randn((segments, n_queries, d), generator=g, device=q.device) for _ in range(4)]
     out = torch.empty_like(qs[0])
     flush = torch.empty(L2_BYTES * 2, dtype=torch.uint8, device=q.device)       # the compressed cache (113 MB) fits L2
+
+    # parity gate: the fused result against float64 attention over this cache's own decoded float32 planes
+    ko, vo = None, None
+    ref_cache_k = torch.empty((tokens, d), dtype=torch.float32, device=q.device)
+    ref_cache_v = torch.empty((tokens, d), dtype=torch.float32, device=q.device)
+    got = cache.attend(qs[0])
+    worst = 0.0
+    for s in (0, segments // 2, segments - 1):
+        q.enqueue_per_channel_decode(cache.planes[0].codes[s], cache.planes[0].side[s], ref_cache_k, tokens, cache.planes[0].config)
+        q.enqueue_decode(cache.planes[1].codes[s], cache.planes[1].side[s], ref_cache_v, tokens, cache.planes[1].config)
+        sc = (qs[0][s].double() @ ref_cache_k.double().T) * d ** -0.5
+        ref = torch.softmax(sc, dim=1) @ ref_cache_v.double()
+        worst = max(worst, float(((got[s].double() - ref).norm(dim=1) / ref.norm(dim=1)).max()))
+    if worst > 5e-5:
+        raise SystemExit(f"parity gate failed: cache attention differs from attention over the decoded cache by {worst}")
+    del ref_cache_k, ref_cache_v
 
     def timed(fn):
         for i in range(3):
@@ -160,19 +303,40 @@ def bench_attention(q, reps, segments=48, tokens=32768, n_queries=7):
     stored = cache.stored_bytes()
     extra = {"dim": d, "segments": segments, "tokens": tokens, "n_queries": n_queries, "l2": "flushed before every launch",
              "tokens_per_s": round(segments * tokens / t, 1)}
-    report("cfg4 attention", "attention from the compressed cache", t, segments * tokens, "kv_tokens", stored, extra)
+    yield row("cfg4 attention", "attention from the compressed cache", t, segments * tokens, "kv_tokens", stored,
+              {**extra, "parity": {"max_rel_l2_vs_float64_attention_over_decoded_cache": worst}})
 
     def two_step(i):
         ko, vo = cache.decode()
         torch.nn.functional.scaled_dot_product_attention(qs[i % 4].to(torch.bfloat16).unsqueeze(0), ko.unsqueeze(0), vo.unsqueeze(0))
     t2 = timed(two_step)
-    report("cfg4 attention", "decode, then torch SDPA over the decoded cache", t2, segments * tokens, "kv_tokens",
-           stored + 2 * cache.decoded_bytes(), {**extra, "speedup_of_fused": round(t2 / t, 2)})
+    yield row("cfg4 attention", "decode, then torch SDPA over the decoded cache", t2, segments * tokens, "kv_tokens",
+              stored + 2 * cache.decoded_bytes(), {**extra, "speedup_of_fused": round(t2 / t, 2)})
+
+    # end to end with host buffers: queries from pinned host memory, result back to pinned host memory, waited for
+    hq = torch.randn((8, segments, n_queries, d)).pin_memory()
+    ho = torch.empty((segments, n_queries, d)).pin_memory()
+    dq = torch.empty((segments, n_queries, d), device=q.device)
+    stream = torch.cuda.current_stream(q.device)
+
+    def e2e(i):
+        dq.copy_(hq[i % 8], non_blocking=True)
+        cache.attend(dq, out=out)
+        ho.copy_(out, non_blocking=True)
+        stream.synchronize()
+    for i in range(3):
+        e2e(i)
+    import time as _time
+    t0 = _time.perf_counter()
+    for i in range(reps):
+        e2e(i)
+    te = (_time.perf_counter() - t0) / reps
+    yield row("cfg4 attention", "end to end: queries from host memory, result to host memory, every call waited for", te,
+              segments * tokens, "kv_tokens", stored, {**extra, "l2": "not flushed", "h2d_bytes": int(dq.numel() * 4), "d2h_bytes": int(out.numel() * 4)})
 
 
 def bench_key_bias(q, reps, segments=48, tokens=32768):
-    """Whole-cache decode with exact key-bias removal (TurboQuant keys and values, d=64, bf16 out):
-    the rotated bias is added back to the decoded keys by one extra element-wise launch."""
+    """Whole-cache decode with exact key-bias removal (TurboQuant keys and values, d=64, bf16 out)."""
     d = 64
     cfg = QuantConfig("turboQuant", d, 4)
     dev = q.device
@@ -189,11 +353,52 @@ def bench_key_bias(q, reps, segments=48, tokens=32768):
                     q.enqueue_encode(x[j], pl.codes[s0 + j], pl.side[s0 + j], tokens, cfg)
             torch.cuda.synchronize()
         cache.tokens = tokens
+        parity = None
+        if bias is not None:
+            # parity gate: the one-launch result equals decode without the option followed by the separate element-wise pass
+            ko, _ = cache.decode()
+            got = ko[segments - 1].clone()
+            plain = KVCache(1, d, tokens, cfg, cfg, out_dtype="bfloat16", pitch=q)
+            plain.planes[0].codes.copy_(cache.planes[0].codes[segments - 1:segments])
+            plain.planes[0].side.copy_(cache.planes[0].side[segments - 1:segments])
+            plain.tokens = tokens
+            po, _ = plain.decode()
+            q.enqueue_rope_bias(po, kb[0][segments - 1:segments].contiguous(), kb[1], kb[2], first_position=0, subtract=False)
+            if not torch.equal(got, po[0]):
+                raise SystemExit("parity gate failed: decode with key-bias removal differs from decode + separate bias pass")
+            parity = {"equals_decode_plus_separate_pass": True}
+            del plain, po, got
         t = time_launches(lambda i: cache.decode(), 1, reps)
         nbytes = cache.stored_bytes() + cache.decoded_bytes()
-        report("cfg4-shape TurboQuant keys", "whole-cache decode " + name, t, 2 * segments * tokens, "vectors", nbytes,
-               {"dim": d, "segments": segments, "tokens": tokens, "out_dtype": "bfloat16",
-                "extra_pass_bytes": 0 if bias is None else cache.decoded_bytes()})
+        yield row("cfg4-shape TurboQuant keys", "whole-cache decode " + name, t, 2 * segments * tokens, "vectors", nbytes,
+                  {"dim": d, "segments": segments, "tokens": tokens, "out_dtype": "bfloat16", "parity": parity})
+        del cache
+
+
+def run(q, which, reps=50, gate=None, cfg5_segments=80):
+    """Yields one dict per measurement of the configurations named in `which`."""
+    few = max(5, reps // 5)
+    if "cfg1" in which:
+        yield from bench_vector(q, "cfg1", "turboQuant", 65536, 64, 4, reps, gate=gate)
+        yield from bench_vector(q, "cfg1 x64 batch", "turboQuant", 65536 * 64, 64, 4, few, gate=gate)
+        yield from bench_vector(q, "cfg1 x64 batch", "turboQuant", 65536 * 64, 64, 4, few, torch.bfloat16, gate=gate)
+    if "cfg2" in which:
+        yield from bench_channel(q, "cfg2", 32768, 64, 4, 64, reps, gate=gate)
+        yield from bench_channel(q, "cfg2 x48 heads", 32768 * 48, 64, 4, 64, few, gate=gate)
+    if "cfg3" in which:
+        for bits in (3, 4):
+            yield from bench_vector(q, "cfg3", "polarQuant", 1 << 20, 128, bits, few, gate=gate)
+    if "sweep" in which:
+        for method in ("turboQuant", "polarQuant"):
+            for d in (64, 128, 256, 512, 1024):
+                yield from bench_vector(q, "cfg3 sweep", method, (1 << 27) // d, d, 4, few, gate=gate)
+    if "attn" in which:
+        yield from bench_attention(q, few)
+    if "bias" in which:
+        yield from bench_key_bias(q, few)
+    if "cfg5" in which:
+        for bits in (4, 3):
+            yield from bench_cfg5(q, bits, max(3, reps // 10), segments=cfg5_segments, gate=gate)
 
 
 def main():
@@ -202,29 +407,8 @@ def main():
     ap.add_argument("--reps", type=int, default=50)
     ap.add_argument("--cfg5-segments", type=int, default=80, help="segments of the config 5 shard (80 = one GPU's share of 640)")
     args = ap.parse_args()
-    which = set(args.only.split(","))
-    q = PITCH()
-    if "cfg1" in which:
-        bench_vector(q, "cfg1", "turboQuant", 65536, 64, 4, args.reps)
-        bench_vector(q, "cfg1 x64 batch", "turboQuant", 65536 * 64, 64, 4, max(5, args.reps // 5))
-        bench_vector(q, "cfg1 x64 batch", "turboQuant", 65536 * 64, 64, 4, max(5, args.reps // 5), torch.bfloat16)
-    if "cfg2" in which:
-        bench_channel(q, "cfg2", 32768, 64, 4, 64, args.reps)
-        bench_channel(q, "cfg2 x48 heads", 32768 * 48, 64, 4, 64, max(5, args.reps // 5))
-    if "cfg3" in which:
-        for bits in (3, 4):
-            bench_vector(q, "cfg3", "polarQuant", 1 << 20, 128, bits, max(5, args.reps // 5))
-    if "sweep" in which:
-        for method in ("turboQuant", "polarQuant"):
-            for d in (64, 128, 256, 512, 1024):
-                bench_vector(q, "cfg3 sweep", method, (1 << 27) // d, d, 4, max(5, args.reps // 5))
-    if "attn" in which:
-        bench_attention(q, max(5, args.reps // 5))
-    if "bias" in which:
-        bench_key_bias(q, max(5, args.reps // 5))
-    if "cfg5" in which:
-        for bits in (4, 3):
-            bench_cfg5(q, bits, max(3, args.reps // 10), segments=args.cfg5_segments)
+    for r in run(PITCH(), set(args.only.split(",")), args.reps, None, args.cfg5_segments):
+        print(json.dumps(r), flush=True)
 
 
 if __name__ == "__main__":

@@ -10,7 +10,8 @@ newest partial group being re-encoded as it grows.  ``KVCache`` packages that pa
 * a *plane* is one tensor of the cache (keys or values) with its codec: per-channel
   (``ChannelQuantConfig``) or per-vector (``QuantConfig``, TurboQuant or PolarQuant);
 * ``append`` encodes new tokens for all segments and planes (one launch);
-* ``decode`` reconstructs every token of every segment and plane (one launch).
+* ``decode`` reconstructs every token of every segment and plane (one launch);
+* ``step`` does both for one new token per segment in a single launch - the per-token path.
 
 Layout in device memory, per plane, segment-major and token-major:
 codes ``[segments][capacity * code_stride]`` bytes, side information
@@ -19,6 +20,7 @@ codes ``[segments][capacity * code_stride]`` bytes, side information
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 from dataclasses import dataclass
 
@@ -77,9 +79,11 @@ class KVCache:
         self.out_dtype = torch_dtype(out_dtype)
         self.tokens = 0
         self._desc_cache = None
+        self._state = None                  # device-side token counter (use_device_counter)
         self._float_dtypes = (torch.float32, torch.float16, torch.bfloat16)
         self.planes = [self._make_plane("keys", key_config), self._make_plane("values", value_config)]
         self._piece_limit = min([pl.config.group_size for pl in self.planes if pl.is_channel] + [65535])
+        self._fused = self._fused_ok()
         self.key_bias = None
         if key_bias is not None:
             bias, cos_table, sin_table = key_bias
@@ -113,6 +117,7 @@ class KVCache:
             d.out_dtype = native_dtype(self.out_dtype)
             d.segments = self.segments
             d.n_planes = len(self.planes)
+            d.capacity = self.capacity
             for i, pl in enumerate(self.planes):
                 q = d.planes[i]
                 q.kind = pl.kind
@@ -121,10 +126,13 @@ class KVCache:
                 q.seed = 0 if pl.is_channel else pl.config.seed
                 q.codes = pl.codes.data_ptr()
                 q.codes_seg_stride = pl.codes.stride(0) * pl.codes.element_size()
+                q.codes_bytes = pl.codes.numel() * pl.codes.element_size()
                 q.side = pl.side.data_ptr()
                 q.side_seg_stride = pl.side.stride(0) * pl.side.element_size()
+                q.side_bytes = pl.side.numel() * pl.side.element_size()
                 q.out = pl.out.data_ptr()
                 q.out_seg_stride = pl.out.stride(0) * pl.out.element_size()
+                q.out_bytes = pl.out.numel() * pl.out.element_size()
             self._desc_cache = d
             self._desc_ref = ctypes.byref(d)
             src = (_native.AppendSrc * 4)()
@@ -132,10 +140,32 @@ class KVCache:
                 if pl.residual is not None:
                     src[i].residual = pl.residual.data_ptr()
                     src[i].residual_seg_stride = pl.residual.stride(0) * 4
+                    src[i].residual_bytes = pl.residual.numel() * 4
             self._src_cache = src
             self._lib = _native.lib()
         d.tokens = tokens
         return d
+
+    def _fill_src(self, keys, values, first: int, n: int):
+        """Points the cached ``pitch_append_src`` array at tokens ``[first, first + n)`` of the inputs."""
+        src = self._src_cache
+        esz = keys.element_size()
+        off = first * self.dim * esz
+        for i, x in enumerate((keys, values)):
+            src[i].input = x.data_ptr() + off
+            src[i].input_seg_stride = x.stride(0) * esz
+            src[i].input_bytes = x.numel() * esz - off
+        return src
+
+    def _stream_context(self, stream):
+        """Context manager that makes ``stream`` (a torch stream, a raw handle or None) torch's
+        current stream, so that tensors made inside are ordered and owned like the kernels."""
+        torch = _torch()
+        if stream is None:
+            return contextlib.nullcontext()
+        if isinstance(stream, int):
+            stream = torch.cuda.ExternalStream(stream, device=self.device)
+        return torch.cuda.stream(stream)
 
     # ------------------------------------------------------------------ writing
     def _check_new(self, x, name: str):
@@ -161,7 +191,8 @@ class KVCache:
         if self.tokens + n_new > self.capacity:
             raise InvalidInput(f"cache holds {self.tokens} of {self.capacity} tokens; cannot append {n_new}")
         if self.key_bias is not None:
-            keys = keys.clone()
+            with self._stream_context(stream):          # the copy is made, and later freed, on the launching stream
+                keys = keys.clone()
             self.pitch.enqueue_rope_bias(keys, *self.key_bias, first_position=self.tokens, subtract=True, stream=stream)
         limit = self._piece_limit           # new tokens of one launch must fall into one per-channel group
         done = 0
@@ -171,20 +202,103 @@ class KVCache:
             self._append_piece(keys, values, done, step, stream)
             self.tokens += step
             done += step
+        self._push_counter()
 
     def _append_piece(self, keys, values, first: int, n: int, stream) -> None:
         self._desc(self.tokens)
-        src = self._src_cache
-        esz = keys.element_size()
-        off = first * self.dim * esz
-        src[0].input = keys.data_ptr() + off
-        src[0].input_seg_stride = keys.stride(0) * esz
-        src[1].input = values.data_ptr() + off
-        src[1].input_seg_stride = values.stride(0) * esz
+        src = self._fill_src(keys, values, first, n)
         st = self._lib.pitch_enqueue_cache_append(self._desc_ref, src, native_dtype(keys.dtype), n,
                                                   stream_handle(stream, self.device))
         if st:
             _native.check(st)
+
+    # ------------------------------------------------------------------ the per-token path
+    def step(self, keys, values, stream=None):
+        """One generation step: appends ONE new token per segment (tensors ``[segments, 1, dim]``)
+        and decodes the whole cache, new token included, in a single launch; returns the decoded
+        views like ``decode``.  Results are exactly those of ``append`` followed by ``decode``.
+        Cache shapes the one-launch kernel does not cover run as those two calls."""
+        if self.key_bias is not None or not self._fused:
+            self.append(keys, values, stream)
+            return self.decode(stream)
+        keys, values = self._check_new(keys, "keys"), self._check_new(values, "values")
+        if keys.shape[1] != 1 or keys.shape != values.shape or keys.dtype != values.dtype:
+            raise InvalidInput("step takes one new token per segment: keys and values of shape [segments, 1, dim], same dtype")
+        if self.tokens >= self.capacity:
+            raise InvalidInput(f"cache holds {self.tokens} of {self.capacity} tokens; cannot append 1")
+        self._desc(self.tokens)
+        src = self._fill_src(keys, values, 0, 1)
+        st = self._lib.pitch_enqueue_cache_step(self._desc_ref, src, native_dtype(keys.dtype),
+                                                self._state.data_ptr() if self._state is not None else None,
+                                                stream_handle(stream, self.device))
+        if st:
+            _native.check(st)
+        self.tokens += 1
+        return tuple(pl.out[:, :self.tokens] for pl in self.planes)
+
+    def _fused_ok(self) -> bool:
+        """Whether the one-launch step kernel covers this cache (dim 64 or 128; TurboQuant planes of
+        one width, 3 or 4 bits; per-channel planes of 4 bits with whole items per group)."""
+        if self.dim not in (64, 128):
+            return False
+        widths = set()
+        for pl in self.planes:
+            if pl.is_channel:
+                if pl.config.bits != 4 or pl.config.group_size % (2048 // self.dim):
+                    return False
+            elif pl.kind != _native.PLANE_TURBO or pl.config.bits not in (3, 4):
+                return False
+            else:
+                widths.add(pl.config.bits)
+        return len(widths) <= 1
+
+    def use_device_counter(self) -> None:
+        """Keeps the token count in device memory as well (``pitch_cache_state``): ``step`` then
+        launches with parameters that do not depend on the count, so one captured CUDA graph of a
+        step can be replayed token after token (``capture_step`` / ``replay``).  Needs a cache shape
+        the one-launch step covers and no key-bias removal."""
+        torch = _torch()
+        if not self._fused or self.key_bias is not None:
+            raise InvalidInput("the device-side token counter needs a cache shape the one-launch step covers")
+        if self._state is None:
+            self._state = torch.zeros(2, dtype=torch.int64, device=self.device)     # tokens | status, arrivals
+        self._push_counter()
+
+    def _push_counter(self) -> None:
+        if self._state is not None:
+            torch = _torch()
+            self._state.copy_(torch.tensor([self.tokens, 0], dtype=torch.int64))
+
+    def counter(self) -> tuple[int, int]:
+        """(tokens, status) as the device-side counter holds them (waits for the stream)."""
+        if self._state is None:
+            raise InvalidInput("no device-side counter: call use_device_counter() first")
+        tokens, rest = (int(v) for v in self._state.cpu())
+        return tokens, rest & 0xFFFFFFFF
+
+    def capture_step(self, keys, values):
+        """Captures one ``step`` reading the new token from the given tensors (whose storage the
+        caller refills before every replay) into a CUDA graph.  Returns the graph; run it with
+        ``replay``."""
+        torch = _torch()
+        self.use_device_counter()
+        if self.tokens >= 1:
+            self.decode()                        # first use of the kernel configures it: keep that out of the capture
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        held = self.tokens
+        with torch.cuda.graph(graph):
+            self.step(keys, values)
+        self.tokens = held                       # capturing queues nothing
+        return graph
+
+    def replay(self, graph):
+        """Replays a graph made by ``capture_step``: one more token per segment."""
+        if self.tokens >= self.capacity:
+            raise InvalidInput(f"cache holds {self.tokens} of {self.capacity} tokens; cannot append 1")
+        graph.replay()
+        self.tokens += 1
+        return tuple(pl.out[:, :self.tokens] for pl in self.planes)
 
     def prefill(self, keys, values, stream=None) -> None:
         """Bulk-encodes ``[segments, T, dim]`` tensors into an empty cache with the stand-alone
@@ -203,7 +317,8 @@ class KVCache:
         p = self.pitch
         key_bias, self.key_bias = self.key_bias, None          # applied once here, not again by append() below
         if key_bias is not None:
-            keys = keys.clone()
+            with self._stream_context(stream):
+                keys = keys.clone()
             p.enqueue_rope_bias(keys, *key_bias, first_position=0, subtract=True, stream=stream)
         esz = keys.element_size()
         for pl, x in zip(self.planes, (keys, values)):
@@ -225,6 +340,7 @@ class KVCache:
                 self.append(keys[:, bulk:].contiguous(), values[:, bulk:].contiguous(), stream)
         finally:
             self.key_bias = key_bias
+        self._push_counter()
 
     def truncate(self, tokens: int) -> None:
         """Forgets every token from ``tokens`` on (host-side bookkeeping only).  The new length
@@ -235,6 +351,7 @@ class KVCache:
             if pl.is_channel and tokens % pl.config.group_size:
                 raise InvalidInput("truncate to a multiple of the group size")
         self.tokens = int(tokens)
+        self._push_counter()
 
     # ------------------------------------------------------------------ reading
     def decode(self, stream=None):

@@ -360,27 +360,231 @@ struct Plane64 {
     int64_t out_seg_stride;
 };
 
+// What a step (append one token, then decode) needs on top of Plane64.
+struct StepPlane {
+    const unsigned char* in;      // new token of segment s at in + s * in_seg_stride: dim elements of in_dtype
+    int64_t in_seg_stride;
+    float* residual;              // per-channel planes: [segments][group + 2][dim] float32 (tokens, running min, running max)
+    int64_t residual_seg_elems;
+};
+
+// Device-side token counter of a cache (pitch_cache_state of the C interface).
+struct CacheState {
+    long long tokens;
+    int status;
+    unsigned arrivals;
+};
+
 struct Cache64Params {
     int n_planes;
     int segments;
-    int full_items;           // whole items per segment (tokens / tokens per item)
-    int tail;                 // tokens in the partial last item of every segment
+    int append;               // 0: decode `tokens` tokens.  1: append one token at position `tokens`, then decode tokens + 1
+    int in_dtype;             // element type of the new tokens (0 float32, 1 float16, 2 bfloat16)
+    int64_t tokens;           // tokens held before the launch (read from *state instead when state is set)
+    int64_t capacity;         // append with a device-side counter: refuse when tokens >= capacity
+    CacheState* state;
     float rs;                 // 1/sqrt(dim), correctly rounded
     Plane64 plane[4];
+    StepPlane step[4];
     Book16 book;              // TurboQuant centroids for (dim, bits)
 };
 
 constexpr int CD_SIGN_BYTES = 4 * 64 * 4;      // [plane][pair of the vector] sign words
+constexpr int CD_EDGE_BYTES = 16 * 4;          // TurboQuant decision boundaries (append)
 template <typename T>
-constexpr int cache64_smem_bytes() { return CD_TABLE_BYTES + CD_SIGN_BYTES + CD_WARPS * WarpStage<T, 64>::BYTES; }
+constexpr int cache64_smem_bytes() { return CD_TABLE_BYTES + CD_SIGN_BYTES + CD_EDGE_BYTES + CD_WARPS * WarpStage<T, 64>::BYTES; }
 
 // A work item: 2048 coordinates of one plane of one segment.
 struct Cursor64 {
     int pl, seg, item;
 };
 
+__device__ __forceinline__ float load_elem_f32(const unsigned char* p, int dtype, int idx) {
+    if (dtype == 0) return reinterpret_cast<const float*>(p)[idx];
+    if (dtype == 1) return __half2float(reinterpret_cast<const __half*>(p)[idx]);
+    return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[idx]);
+}
+
+// TurboQuant encode of ONE vector by a whole warp (the token a step appends): lane l owns the
+// D/32 consecutive coordinates l*D/32 ...; the float operations and their order are those of
+// turbo_encode_kernel (balanced adjacent-pair sum of squares, unit vector, sign flip,
+// Walsh-Hadamard stages from the lowest coordinate bit up, 1/sqrt(D), number of decision
+// boundaries strictly below).  Writes the packed codes and the norm to the cache and patches
+// them into the prefetch registers of the lanes that decode this token, so the decode that
+// follows does not depend on reading back what was just written.
+template <int D, int BITS>
+__device__ __forceinline__ void turbo_append_warp(Prefetch64& f, const unsigned char* __restrict__ in, int in_dtype,
+                                                  uint32_t* __restrict__ codes_tok, float* __restrict__ norm_out,
+                                                  int tok_in_item, const uint32_t* neg, const float* s_edges, float rs,
+                                                  unsigned char* stage, int lane) {
+    constexpr int E = D / 32, LPV = Item64<D>::LPV, WPV = D * BITS / 32;
+    float x[E], t[E];
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+        x[i] = load_elem_f32(in, in_dtype, lane * E + i);
+        t[i] = x[i] * x[i];
+    }
+    const float norm = sqrtf(lanes_sum(tree_sum_regs(t), 32));
+    const float inv = norm > 0.0f ? 1.0f / norm : 0.0f;
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+        const int c = lane * E + i;
+        x[i] = flip_if(x[i], neg[c >> 5], c & 31) * inv;
+    }
+    wht_regs(x, E);
+    wht_lanes(x, 32, lane);
+    uint32_t* s_code = reinterpret_cast<uint32_t*>(stage);          // D code values, then WPV packed words
+    uint32_t* s_word = s_code + D;
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+        const float u = x[i] * rs;
+        uint32_t code = 0;
+#pragma unroll
+        for (int step = (1 << BITS) >> 1; step > 0; step >>= 1) {
+            const uint32_t cand = code + step;
+            if (u > s_edges[cand - 1]) code = cand;
+        }
+        s_code[lane * E + i] = code;
+    }
+    __syncwarp();
+    if (lane < WPV) {
+        const int bit0 = lane * 32;
+        const int i0 = bit0 / BITS;
+        int i1 = (bit0 + 31) / BITS;
+        if (i1 > D - 1) i1 = D - 1;
+        uint32_t word = 0;
+        for (int i = i0; i <= i1; ++i) {
+            const int shift = i * BITS - bit0;
+            word |= shift >= 0 ? (s_code[i] << shift) : (s_code[i] >> (-shift));
+        }
+        s_word[lane] = word;
+        codes_tok[lane] = word;
+    }
+    if (lane == 0) *norm_out = norm;
+    __syncwarp();
+    if (lane / LPV == tok_in_item) {
+        const uint32_t* mine = s_word + (lane % LPV) * 2 * BITS;
+        f.a = make_uint4(mine[0], mine[1], mine[2], mine[3]);
+        f.b = BITS == 4 ? make_uint4(mine[4], mine[5], mine[6], mine[7]) : make_uint4(mine[4], mine[5], 0, 0);
+        f.c.x = __float_as_uint(norm);
+    }
+    __syncwarp();
+}
+
+// The newest group of a per-channel plane during a step, one item of it per warp: fold the new
+// token into the group's running range, re-quantise the item's tokens from the float32 residual
+// against the new fp16 range (4-bit codes), store the codes, and decode them in the same breath.
+// A group that spans several items is handled by several warps; each derives the new range on its
+// own (minimum and maximum are idempotent, so it does not matter whether a warp sees the running
+// range before or after the holder of the new token has updated it), and only the holder writes
+// the residual row, the running range and the fp16 range.  Arithmetic as channel_encode_slab_kernel.
+template <typename T, int D>
+__device__ __forceinline__ void channel_step_warp(const Plane64& P, const StepPlane& S, int in_dtype, int64_t seg,
+                                                  int item, int64_t t_old, T* __restrict__ out, int nvalid, int lane) {
+    constexpr int SLABS = Item64<D>::SLABS, TOK_LANES = Item64<D>::TOK_LANES, TOKENS = Item64<D>::TOKENS;
+    const int slab = lane & (SLABS - 1), tok_lane = lane / SLABS;
+    const int G = P.group_items * TOKENS;
+    const int64_t g = t_old / G;
+    const int pos = (int)(t_old - g * G);                              // index of the new token inside its group
+    const int j = item - (int)(g * P.group_items);                     // this item inside the group
+    const bool holder = j == pos / TOKENS;
+    float* res = S.residual + seg * S.residual_seg_elems;
+    const unsigned char* in = S.in + seg * S.in_seg_stride;
+
+    float xn[8], lo[8], hi[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) xn[i] = load_elem_f32(in, in_dtype, slab * 8 + i);
+    if (pos > 0) {
+        const float4 l0 = *reinterpret_cast<const float4*>(res + (int64_t)G * D + slab * 8);
+        const float4 l1 = *reinterpret_cast<const float4*>(res + (int64_t)G * D + slab * 8 + 4);
+        const float4 h0 = *reinterpret_cast<const float4*>(res + (int64_t)(G + 1) * D + slab * 8);
+        const float4 h1 = *reinterpret_cast<const float4*>(res + (int64_t)(G + 1) * D + slab * 8 + 4);
+        const float rl[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+        const float rh[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            lo[i] = fminf(rl[i], xn[i]);
+            hi[i] = fmaxf(rh[i], xn[i]);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) lo[i] = hi[i] = xn[i];
+    }
+    const bool writer = holder && tok_lane == 0;
+    if (writer) {
+        *reinterpret_cast<float4*>(res + (int64_t)G * D + slab * 8) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+        *reinterpret_cast<float4*>(res + (int64_t)G * D + slab * 8 + 4) = make_float4(lo[4], lo[5], lo[6], lo[7]);
+        *reinterpret_cast<float4*>(res + (int64_t)(G + 1) * D + slab * 8) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<float4*>(res + (int64_t)(G + 1) * D + slab * 8 + 4) = make_float4(hi[4], hi[5], hi[6], hi[7]);
+    }
+    Prefetch64 f;
+    float step[8], rcp[8];
+    {
+        uint32_t lo_w[4], hi_w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __half2 l = __floats2half2_rn(lo[2 * i], lo[2 * i + 1]);
+            const __half2 h = __floats2half2_rn(hi[2 * i], hi[2 * i + 1]);
+            lo_w[i] = *reinterpret_cast<const uint32_t*>(&l);
+            hi_w[i] = *reinterpret_cast<const uint32_t*>(&h);
+            const float2 lf = __half22float2(l), hf = __half22float2(h);
+            lo[2 * i] = lf.x;
+            lo[2 * i + 1] = lf.y;
+            step[2 * i] = step_of(lf.x, hf.x, 15.0f);
+            step[2 * i + 1] = step_of(lf.y, hf.y, 15.0f);
+        }
+        f.c = make_uint4(lo_w[0], lo_w[1], lo_w[2], lo_w[3]);
+        f.d = make_uint4(hi_w[0], hi_w[1], hi_w[2], hi_w[3]);
+        if (writer) {
+            __half* ranges = reinterpret_cast<__half*>(const_cast<unsigned char*>(P.side) + seg * P.side_seg_stride) + g * 2 * D;
+            *reinterpret_cast<uint4*>(ranges + slab * 8) = f.c;
+            *reinterpret_cast<uint4*>(ranges + D + slab * 8) = f.d;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) rcp[i] = __frcp_rn(step[i]);
+
+    uint32_t* item_codes = reinterpret_cast<uint32_t*>(const_cast<unsigned char*>(P.codes) + seg * P.codes_seg_stride +
+                                                       (int64_t)item * 1024);
+    uint32_t w[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const int tg = j * TOKENS + k * TOK_LANES + tok_lane;          // token index inside the group
+        w[k] = 0;
+        if (tg <= pos) {
+            float row[8];
+            if (tg == pos) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) row[i] = xn[i];
+                *reinterpret_cast<float4*>(res + (int64_t)pos * D + slab * 8) = make_float4(xn[0], xn[1], xn[2], xn[3]);
+                *reinterpret_cast<float4*>(res + (int64_t)pos * D + slab * 8 + 4) = make_float4(xn[4], xn[5], xn[6], xn[7]);
+            } else {
+                const float4 r0 = *reinterpret_cast<const float4*>(res + (int64_t)tg * D + slab * 8);
+                const float4 r1 = *reinterpret_cast<const float4*>(res + (int64_t)tg * D + slab * 8 + 4);
+                row[0] = r0.x; row[1] = r0.y; row[2] = r0.z; row[3] = r0.w;
+                row[4] = r1.x; row[5] = r1.y; row[6] = r1.z; row[7] = r1.w;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) w[k] |= quantise_rcp(row[i], lo[i], step[i], rcp[i], 15.0f) << (4 * i);
+            item_codes[k * 32 + lane] = w[k];
+        }
+    }
+    f.a = make_uint4(w[0], w[1], w[2], w[3]);
+    f.b = make_uint4(w[4], w[5], w[6], w[7]);
+    channel64_decode_warp<T, D, false>(f, out, nvalid, lane);
+}
+
 // grid = number of SMs (persistent), CD_THREADS threads, cache64_smem_bytes<T>() dynamic shared memory.
 // D in {64, 128}; BITS in {3, 4} is the width of the TurboQuant planes (per-channel planes are 4-bit).
+//
+// Work of a launch that holds `total` tokens per segment after an optional append at position t_old:
+//   * main items  - items [0, main) of every segment and plane, none touched by the append: the
+//     software-pipelined, unchecked path.  main = total / tokens-per-item without an append; with
+//     one it is the first item of the newest group of the per-channel planes (or of the new token).
+//   * edge items  - items [main, ceil(total / tokens-per-item)): the partial last item, the items
+//     of a per-channel plane's newest group (re-quantised from the residual) and the item that
+//     receives the new TurboQuant vector (encoded by the warp that decodes it).  One warp each,
+//     taken first, by the warps that come last in the round-robin of the main items.
 template <typename T, int D, int BITS>
 __global__ void __launch_bounds__(CD_THREADS, 1)
 cache_decode_kernel(const __grid_constant__ Cache64Params p) {
@@ -390,7 +594,8 @@ cache_decode_kernel(const __grid_constant__ Cache64Params p) {
     extern __shared__ __align__(1024) unsigned char smem[];
     unsigned char* table = smem;
     uint32_t* s_sign = reinterpret_cast<uint32_t*>(smem + CD_TABLE_BYTES);           // [4][64]
-    unsigned char* stage_base = smem + CD_TABLE_BYTES + CD_SIGN_BYTES;
+    float* s_edges = reinterpret_cast<float*>(smem + CD_TABLE_BYTES + CD_SIGN_BYTES);
+    unsigned char* stage_base = smem + CD_TABLE_BYTES + CD_SIGN_BYTES + CD_EDGE_BYTES;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
     bool any_turbo = false;
@@ -411,12 +616,16 @@ cache_decode_kernel(const __grid_constant__ Cache64Params p) {
             const int bit = (2 * i) & 31;
             s_sign[threadIdx.x] = (((m >> bit) & 1u) << 15) | (((m >> (bit + 1)) & 1u) << 31);
         }
+        if (threadIdx.x < (1 << BITS) - 1) s_edges[threadIdx.x] = 0.5f * (p.book.c[threadIdx.x] + p.book.c[threadIdx.x + 1]);
     }
     __syncthreads();
     // Everything above touched only kernel parameters and shared memory.  Under programmatic
     // dependent launch this grid may have started before the previous kernel of the stream ended:
-    // wait for it (and for its memory to be visible) before reading the cache.
+    // wait for it (and for its memory to be visible) before reading the cache, then let the next
+    // kernel of the stream be scheduled as soon as multiprocessors free up (it waits for this grid
+    // in the same way before it touches memory).
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
     unsigned char* stage = stage_base + warp * WarpStage<T, 64>::BYTES;
     // warp w of CTA c is worker w * gridDim + c: when the item count is not a multiple of the worker
     // count, the workers that take one item more are spread evenly over the SMs
@@ -424,17 +633,34 @@ cache_decode_kernel(const __grid_constant__ Cache64Params p) {
     const int warp_stride = gridDim.x * CD_WARPS;
     const uint32_t* my_sign_base = s_sign + (LPV == 2 ? (lane & 1) * 32 : 0);
 
+    // ---- geometry of this launch (uniform over the grid)
+    const int64_t t_old = p.state != nullptr ? p.state->tokens : p.tokens;
+    const bool refuse = p.append && p.state != nullptr && t_old >= p.capacity;
+    const int64_t total = t_old + (p.append ? 1 : 0);
+    const int last_items = (int)((total + TOKENS - 1) / TOKENS);          // items per segment and plane, partial one included
+    int full_items = (int)(total / TOKENS);
+    if (p.append) {
+        full_items = (int)(t_old / TOKENS);
+        for (int pl = 0; pl < p.n_planes; ++pl)
+            if (p.plane[pl].kind == 1) {
+                const int G = p.plane[pl].group_items * TOKENS;
+                const int first = (int)(t_old / G) * p.plane[pl].group_items;
+                full_items = first < full_items ? first : full_items;
+            }
+    }
+    const int edge_items = last_items - full_items;
+
     // Addresses of an item.  Whole items take the FULL (unchecked) paths.
     auto fetch = [&](const Cursor64& c, Prefetch64& f) {
         const Plane64& P = p.plane[c.pl];
         const unsigned char* side = P.side + c.seg * P.side_seg_stride;
         if (P.kind == 0)
             prefetch_turbo64<D, BITS, true>(f, P.codes + c.seg * P.codes_seg_stride + (int64_t)c.item * ITEM_CODE_BYTES,
-                                            reinterpret_cast<const float*>(side) + c.item * TOKENS, TOKENS, lane);
+                                            reinterpret_cast<const float*>(side) + (int64_t)c.item * TOKENS, TOKENS, lane);
         else
             prefetch_channel64<D, true>(
                 f, reinterpret_cast<const uint32_t*>(P.codes + c.seg * P.codes_seg_stride + (int64_t)c.item * CH_ITEM_CODE_BYTES),
-                reinterpret_cast<const __half*>(side) + (c.item / P.group_items) * (2 * D), TOKENS, lane);
+                reinterpret_cast<const __half*>(side) + (int64_t)(c.item / P.group_items) * (2 * D), TOKENS, lane);
     };
     auto decode = [&](const Cursor64& c, const Prefetch64& f) {
         const Plane64& P = p.plane[c.pl];
@@ -449,20 +675,56 @@ cache_decode_kernel(const __grid_constant__ Cache64Params p) {
         if (++c.pl < p.n_planes) return true;
         c.pl = 0;
         c.item += warp_stride;
-        if (c.item >= p.full_items) {
-            const int q = c.item / p.full_items;
+        if (c.item >= full_items) {
+            const int q = c.item / full_items;
             c.seg += q;
-            c.item -= q * p.full_items;
+            c.item -= q * full_items;
         }
         return c.seg < p.segments;
     };
 
-    // ---- whole items, software pipelined with two register buffers used alternately
-    if (p.full_items > 0) {
+    if (!refuse) {
+    // ---- edge items: the partial last item and everything an append touches
+    if (edge_items > 0) {
+        const int per_seg = p.n_planes * edge_items;
+        for (int work = warp_stride - 1 - warp_id; work < p.segments * per_seg; work += warp_stride) {
+            const int seg = work / per_seg, r = work - seg * per_seg;
+            const int pl = r / edge_items, item = full_items + (r - pl * edge_items);
+            const Plane64& P = p.plane[pl];
+            const int64_t left = total - (int64_t)item * TOKENS;
+            const int nvalid = left < TOKENS ? (int)left : TOKENS;
+            const unsigned char* side = P.side + seg * P.side_seg_stride;
+            T* out = reinterpret_cast<T*>(P.out + seg * P.out_seg_stride) + (int64_t)item * 2048;
+            Prefetch64 f;
+            if (P.kind == 0) {
+                const bool has_new = p.append && item == (int)(t_old / TOKENS);
+                const unsigned char* item_codes = P.codes + seg * P.codes_seg_stride + (int64_t)item * ITEM_CODE_BYTES;
+                const float* item_norms = reinterpret_cast<const float*>(side) + (int64_t)item * TOKENS;
+                prefetch_turbo64<D, BITS, false>(f, item_codes, item_norms, has_new ? nvalid - 1 : nvalid, lane);
+                if (has_new) {
+                    const int tok = nvalid - 1;
+                    turbo_append_warp<D, BITS>(f, p.step[pl].in + seg * p.step[pl].in_seg_stride, p.in_dtype,
+                                               reinterpret_cast<uint32_t*>(const_cast<unsigned char*>(item_codes)) + tok * (D * BITS / 32),
+                                               const_cast<float*>(item_norms) + tok, tok, P.neg, s_edges, p.rs, stage, lane);
+                }
+                turbo64_decode_warp<T, D, BITS, false>(f, out, nvalid, table, my_sign_base + pl * 64, stage, lane, p.rs);
+            } else if (p.append && item / P.group_items == (int)(t_old / (P.group_items * TOKENS))) {
+                channel_step_warp<T, D>(P, p.step[pl], p.in_dtype, seg, item, t_old, out, nvalid, lane);
+            } else {
+                prefetch_channel64<D, false>(
+                    f, reinterpret_cast<const uint32_t*>(P.codes + seg * P.codes_seg_stride + (int64_t)item * CH_ITEM_CODE_BYTES),
+                    reinterpret_cast<const __half*>(side) + (int64_t)(item / P.group_items) * (2 * D), nvalid, lane);
+                channel64_decode_warp<T, D, false>(f, out, nvalid, lane);
+            }
+        }
+    }
+
+    // ---- main items, software pipelined with two register buffers used alternately
+    if (full_items > 0) {
         Cursor64 cur;
         cur.pl = 0;
-        cur.seg = warp_id / p.full_items;
-        cur.item = warp_id - cur.seg * p.full_items;
+        cur.seg = warp_id / full_items;
+        cur.item = warp_id - cur.seg * full_items;
         if (cur.seg < p.segments) {
             Prefetch64 fa, fb;
             fetch(cur, fa);
@@ -482,24 +744,23 @@ cache_decode_kernel(const __grid_constant__ Cache64Params p) {
             }
         }
     }
+    }
 
-    // ---- the partial last item of every segment (at most one per segment and plane)
-    if (p.tail > 0) {
-        for (int work = warp_id; work < p.segments * p.n_planes; work += warp_stride) {
-            const int seg = work / p.n_planes, pl = work - seg * p.n_planes;
-            const Plane64& P = p.plane[pl];
-            const unsigned char* side = P.side + seg * P.side_seg_stride;
-            T* out = reinterpret_cast<T*>(P.out + seg * P.out_seg_stride) + (int64_t)p.full_items * 2048;
-            Prefetch64 f;
-            if (P.kind == 0) {
-                prefetch_turbo64<D, BITS, false>(f, P.codes + seg * P.codes_seg_stride + (int64_t)p.full_items * ITEM_CODE_BYTES,
-                                                 reinterpret_cast<const float*>(side) + p.full_items * TOKENS, p.tail, lane);
-                turbo64_decode_warp<T, D, BITS, false>(f, out, p.tail, table, my_sign_base + pl * 64, stage, lane, p.rs);
+    // ---- device-side token counter: the last CTA to finish publishes the new count.  The counter is
+    // read again here (nothing has changed it since the start of the grid: only the last arrival
+    // writes) so that no register has to carry it through the main loop.
+    if (p.append && p.state != nullptr) {
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const long long held = p.state->tokens;
+            if (held >= p.capacity) {
+                p.state->status = 1;
             } else {
-                prefetch_channel64<D, false>(
-                    f, reinterpret_cast<const uint32_t*>(P.codes + seg * P.codes_seg_stride + (int64_t)p.full_items * CH_ITEM_CODE_BYTES),
-                    reinterpret_cast<const __half*>(side) + (p.full_items / P.group_items) * (2 * D), p.tail, lane);
-                channel64_decode_warp<T, D, false>(f, out, p.tail, lane);
+                __threadfence();
+                if (atomicAdd(&p.state->arrivals, 1u) == gridDim.x - 1) {
+                    p.state->arrivals = 0;
+                    p.state->tokens = held + 1;
+                }
             }
         }
     }

@@ -1,6 +1,6 @@
 """Appending to a ``KVCache`` through the allocation-free entry point.
 
-``append_noalloc`` does what ``KVCache.append`` does, but the float32 residual of the per-channel
+``append_noalloc`` does what ``KVCache.append`` does (key-bias removal included), but the float32 residual of the per-channel
 planes (the newest, still growing group of every segment) is kept in a fixed array inside the
 native library instead of a tensor the caller allocated.  It exists for hosts that are not
 allowed, or not able, to allocate device memory: a serving loop whose device memory is one
@@ -36,6 +36,11 @@ def append_noalloc(cache: KVCache, keys, values, stream=None) -> None:
         raise InvalidInput("n_new must be at least 1")
     if cache.tokens + n_new > cache.capacity:
         raise InvalidInput(f"cache holds {cache.tokens} of {cache.capacity} tokens; cannot append {n_new}")
+    if cache.key_bias is not None:
+        # same as KVCache.append: the rotated key bias of each position comes off a copy of the keys
+        with cache._stream_context(stream):
+            keys = keys.clone()
+        cache.pitch.enqueue_rope_bias(keys, *cache.key_bias, first_position=cache.tokens, subtract=True, stream=stream)
     limit = min([pl.config.group_size for pl in cache.planes if pl.is_channel] + [65535])
     done = 0
     while done < n_new:
@@ -47,8 +52,10 @@ def append_noalloc(cache: KVCache, keys, values, stream=None) -> None:
             esz = x.element_size()
             src[i].input = x.data_ptr() + done * cache.dim * esz
             src[i].input_seg_stride = x.stride(0) * esz
+            src[i].input_bytes = x.numel() * esz - done * cache.dim * esz
         st = _native.lib().pitch_enqueue_cache_append_noalloc(ctypes.byref(desc), src, native_dtype(keys.dtype), step,
                                                               stream_handle(stream, cache.device))
         _native.check(st)
         cache.tokens += step
         done += step
+    cache._push_counter()

@@ -29,7 +29,7 @@ def test_library_exports_every_declared_symbol(lib):
     assert declared == set(_native.PROTOTYPES), declared ^ set(_native.PROTOTYPES)
     for name in declared:
         assert hasattr(lib, name), name
-    assert lib.pitch_abi_version() == 1
+    assert lib.pitch_abi_version() == 2
     assert lib.pitch_status_string(3) == b"invalid dimension"
 
 
@@ -74,7 +74,81 @@ def _cache_desc(dim=64, segments=48, tokens=32768, k=(2, 4, 64), v=(0, 4, 0)):
         pl.kind, pl.bits, pl.group_size = kind, bits, group
         pl.codes = pl.side = pl.out = 0x10000
         pl.codes_seg_stride = pl.side_seg_stride = pl.out_seg_stride = 1 << 30
+        pl.codes_bytes = pl.side_bytes = pl.out_bytes = 1 << 40
     return d
+
+
+def test_cache_entry_points_check_extents_before_any_device_work(lib):
+    """Codec.check for the whole-cache calls (Sources/PITCH/Core/Codec.swift:37-47): every plane's
+    buffers must cover the segments and tokens addressed; refusals come before any launch."""
+    import ctypes as C
+    from pitch_b200 import _native
+    dec, app, step = lib.pitch_enqueue_cache_decode, lib.pitch_enqueue_cache_append, lib.pitch_enqueue_cache_step
+    err = lib.pitch_last_error
+
+    def src_for(d, n_new=1, residual=True):
+        src = (_native.AppendSrc * 4)()
+        for i in range(2):
+            src[i].input, src[i].input_seg_stride, src[i].input_bytes = 0x20000, d.dim * 4 * n_new, 1 << 30
+            if residual and d.planes[i].kind == 2:
+                src[i].residual, src[i].residual_seg_stride, src[i].residual_bytes = 0x30000, (d.planes[i].group_size + 2) * d.dim * 4, 1 << 30
+        return src
+
+    # decode: each buffer of each plane, one byte short of what 48 segments x 32768 tokens need
+    for plane, field, what in ((0, "codes_bytes", b"codes buffer"), (1, "codes_bytes", b"codes buffer"),
+                               (0, "side_bytes", b"side-information"), (1, "side_bytes", b"side-information"),
+                               (0, "out_bytes", b"output buffer"), (1, "out_bytes", b"output buffer")):
+        d = _cache_desc()
+        pl = d.planes[plane]
+        need = {"codes_bytes": 32768 * 32, "side_bytes": 512 * 2 * 64 * 2 if plane == 0 else 32768 * 4, "out_bytes": 32768 * 64 * 2}[field]
+        setattr(pl, field, 47 * (1 << 30) + need - 1)
+        assert dec(C.byref(d), None) == 1 and what in err() and str(47 * (1 << 30) + need).encode() in err(), err()
+    d = _cache_desc()
+    d.planes[1].out_seg_stride = 32768 * 64 * 2 - 16
+    assert dec(C.byref(d), None) == 1 and b"segment stride" in err()
+    d = _cache_desc()
+    d.planes[0].side = 0x10008
+    assert dec(C.byref(d), None) == 1 and b"multiples of 16" in err()
+    d = _cache_desc()
+    d.planes[1].out = 0
+    assert dec(C.byref(d), None) == 1 and b"null pointer" in err()
+    d = _cache_desc()
+    d.capacity = 32000                                      # the cache was sized for fewer tokens than the call addresses
+    assert dec(C.byref(d), None) == 1 and b"sized for 32000" in err()
+    d = _cache_desc(tokens=100)
+    d.capacity = 32768                                      # extents are checked against the capacity, not the tokens held
+    d.planes[0].codes_bytes = 47 * (1 << 30) + 100 * 32
+    assert dec(C.byref(d), None) == 1 and b"codes buffer" in err()
+
+    # append / step: the cache must have room for the new tokens, inputs and residual must be long enough
+    d = _cache_desc(tokens=32768)
+    d.planes[1].side_bytes = 47 * (1 << 30) + 32768 * 4     # room for exactly the tokens held
+    assert app(C.byref(d), src_for(d), 0, 1, None) == 1 and b"side-information" in err()
+    assert step(C.byref(d), src_for(d), 0, None, None) == 1 and b"side-information" in err()
+    d = _cache_desc(tokens=63)
+    assert app(C.byref(d), src_for(d, 2), 0, 2, None) == 1 and b"one group" in err()
+    d = _cache_desc(tokens=10)
+    src = src_for(d)
+    src[1].input_bytes = 47 * 256 + 255
+    assert app(C.byref(d), src, 0, 1, None) == 1 and b"input buffer" in err()
+    src = src_for(d)
+    src[0].residual_bytes = 47 * 66 * 256 + 66 * 256 - 1
+    assert app(C.byref(d), src, 0, 1, None) == 1 and b"residual buffer" in err()
+    src = src_for(d, residual=False)
+    assert app(C.byref(d), src, 0, 1, None) == 1 and b"residual buffer is null" in err()
+    src = src_for(d)
+    src[0].input = 0x20002
+    assert step(C.byref(d), src, 0, None, None) == 1 and b"multiples of 4" in err()
+    # a device-side counter needs the capacity in the descriptor and an aligned counter
+    assert step(C.byref(d), src_for(d), 0, 0x40000, None) == 1 and b"capacity" in err()
+    d.capacity = 32768
+    assert step(C.byref(d), src_for(d), 0, 0x40008, None) == 1 and b"16-byte aligned" in err()
+    # the allocation-free append range-checks every factor of the residual size before multiplying
+    d = _cache_desc(tokens=0)
+    d.segments = 1 << 40
+    assert lib.pitch_enqueue_cache_append_noalloc(C.byref(d), src_for(d), 0, 1, None) == 1 and b"segments" in err()
+    d = _cache_desc(tokens=0, k=(2, 4, 1 << 20))
+    assert lib.pitch_enqueue_cache_append_noalloc(C.byref(d), src_for(d), 0, 1, None) == 1 and b"group size" in err()
 
 
 def test_attention_workspace_and_shape_rules(lib):

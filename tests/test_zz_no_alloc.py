@@ -26,6 +26,7 @@ def _call_noalloc(cache, keys, values):
     for i, x in enumerate((keys, values)):
         src[i].input = x.data_ptr()
         src[i].input_seg_stride = x.stride(0) * x.element_size()
+        src[i].input_bytes = x.numel() * x.element_size()
     st = _native.lib().pitch_enqueue_cache_append_noalloc(ctypes.byref(desc), src, native_dtype(keys.dtype),
                                                           int(keys.shape[1]), stream_handle(None, cache.device))
     return st
