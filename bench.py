@@ -297,14 +297,17 @@ class StepTimer:
 
     def graph_pass(self, warmup: int, steps: int) -> tuple[float, int]:
         """`warmup` steps issued directly, then `steps` steps captured into ONE CUDA graph that is
-        launched twice: once untimed (the captured steps are idempotent: each rewrites the same token
-        with the same data), once between two events.  Returns (ms per step, bytes of the timed steps)."""
+        launched twice: once untimed (after which the compressed cache is put back to where it was:
+        the steps are not repeatable as they stand, a per-channel plane keeps only its newest group in
+        full precision), once between two events.  Returns (ms per step, bytes of the timed steps)."""
         import torch
         c = self.cache
         for i in range(warmup):
             c.step(self.new_k[i], self.new_v[i])
         torch.cuda.synchronize(self.dev)
         first = c.tokens
+        state = [t for pl in c.planes for t in (pl.codes, pl.side, pl.residual) if t is not None]
+        saved = [t.clone() for t in state]
         graph = torch.cuda.CUDAGraph()
         nbytes = 0
         with torch.cuda.graph(graph):
@@ -312,6 +315,9 @@ class StepTimer:
                 c.step(self.new_k[warmup + i], self.new_v[warmup + i])
                 nbytes += sum(step_bytes(c.segments, c.tokens))
         graph.replay()
+        for t, keep in zip(state, saved):
+            t.copy_(keep)
+        del saved
         self.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -502,7 +508,7 @@ def run_ours(args) -> None:
                        "l2": "inputs larger than L2 (516 MB touched per step per GPU)" if segments == SEGMENTS else
                              f"{(rd + wr) / 1e6:.0f} MB touched per step per GPU: may stay in the 126 MB L2; reported as is",
                        "parallelism": f"24 layers of one cache sharded over {n_gpus} gpu(s) ({segments} segments each), no data-path collective",
-                       "timed_region": "the K steps captured into one CUDA graph, launched once between two events, after W direct steps and one untimed launch of the graph"},
+                       "timed_region": "the K steps captured into one CUDA graph, launched once between two events, after W direct steps and one untimed launch of the graph (cache state restored in between)"},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "traffic": None,
                          "traffic_source": "not measured in this run; an ncu capture of the kernel is summarised under profiles/",

@@ -234,13 +234,6 @@ __device__ __forceinline__ void stg_stream(uint4* p, const uint4& v) {
                  : "memory");
 }
 
-// ------------------------------------------------------------------------------------------
-// Warp tile <-> registers.  The tile is 32 rows of E contiguous elements of T (32*E contiguous
-// elements of global memory); lane r ends up with (or starts from) row r in registers while
-// every global access is a contiguous 512-byte warp transaction.  Row r lives at r * PITCHB
-// bytes of a warp-private shared buffer; the 16-byte pad keeps both the row-owner accesses
-// and the transposed accesses free of bank conflicts.
-// ------------------------------------------------------------------------------------------
 // PolarQuant angle code of the pair (x, y): floor(atan2(y, x) * 2^bits / 2pi + 1/2) mod 2^bits
 // (reference/pitch_reference.py:116-119).  For 2, 3 and 4 bits no arctangent is needed: the
 // first-quadrant angle atan2(|y|, |x|) has reached bin j once |y| >= |x| * tan((j - 1/2) * 2pi/N), so j
@@ -270,6 +263,13 @@ __device__ __forceinline__ uint32_t angle_bin(float x, float y, int bits) {
 
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
 
+// ------------------------------------------------------------------------------------------
+// Warp tile <-> registers.  The tile is 32 rows of E contiguous elements of T (32*E contiguous
+// elements of global memory); lane r ends up with (or starts from) row r in registers while
+// every global access is a contiguous 512-byte warp transaction.  Row r lives at r * PITCHB
+// bytes of a warp-private shared buffer; the 16-byte pad keeps both the row-owner accesses
+// and the transposed accesses free of bank conflicts.
+// ------------------------------------------------------------------------------------------
 template <typename T, int E> struct WarpStage {
     static constexpr int ROWB = E * (int)sizeof(T);
     static constexpr int PITCHB = ROWB + 16;

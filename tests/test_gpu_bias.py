@@ -47,6 +47,25 @@ def test_elementwise_pass_is_bit_exact(q, dtype, S, count, dim, first):
         assert torch.equal(data.cpu(), torch.from_numpy(ref).to(tdt)), (dtype, subtract)
 
 
+def test_elementwise_pass_reproduces_the_reference_rotated_bias(q):
+    """The kernel against the reference's own ``rotated_bias`` (reference/mechanism_eval.py:82-91,
+    fixtures of tests/golden/make_bias_golden.py): adding R_t b to zeros must give the reference's
+    R_t b bit for bit, and subtracting it again must give zeros."""
+    import torch
+    from conftest import Golden
+    g = Golden("rotated_bias.npz")
+    for c in g.cases:
+        k = c["key"]
+        dev = q.device
+        bias, cos, sin = (torch.from_numpy(g[f"{k}/{n}"]).to(dev) for n in ("bias", "cos", "sin"))
+        want = torch.from_numpy(g[f"{k}/rotated_bias"])
+        data = torch.zeros((c["heads"], c["positions"], c["dim"]), device=dev)
+        q.enqueue_rope_bias(data, bias, cos, sin, subtract=False)
+        assert torch.equal(data.cpu(), want), k
+        q.enqueue_rope_bias(data, bias, cos, sin, subtract=True)
+        assert torch.count_nonzero(data) == 0, k
+
+
 def test_strided_segments_leave_the_gap_untouched(q):
     import torch
     dev = q.device

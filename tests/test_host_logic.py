@@ -333,7 +333,7 @@ def test_gather_fails_cleanly_when_a_rank_is_missing():
 
 # ---------------------------------------------------------------- benchmark bookkeeping
 def test_bench_byte_accounting_matches_the_published_workload():
-    """Algorithmic bytes of one whole-cache decode of configuration 4."""
+    """Algorithmic bytes of one whole-cache decode of configuration 4 (the figures the benchmark's roofline is computed from)."""
     import importlib.util
     spec = importlib.util.spec_from_file_location("bench", ROOT / "bench.py")
     bench = importlib.util.module_from_spec(spec)

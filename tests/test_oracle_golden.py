@@ -139,3 +139,18 @@ def test_f32_oracle_half_conversion():
         assert L.pitch_oracle_f32_to_f16(float(v)) == int(np.float16(v).view(np.uint16)), v
     for h in (0x3C00, 0xC000, 0x7BFF, 0x0001, 0x0400, 0x83FF):                      # PerChannelTests.swift:214-221
         assert L.pitch_oracle_f16_to_f32(h) == float(np.uint16(h).view(np.float16))
+
+
+def test_rotated_bias_oracle_reproduces_the_reference():
+    """``oracle.spec_np.rotated_bias`` against the output of the reference's own ``rotated_bias``
+    (reference/mechanism_eval.py:82-91), produced by tests/golden/make_bias_golden.py: bit for bit."""
+    from conftest import Golden
+    from oracle import spec_np
+    g = Golden("rotated_bias.npz")
+    assert len(g.cases) == 3
+    for c in g.cases:
+        k = c["key"]
+        bias, cos, sin, want = g[f"{k}/bias"], g[f"{k}/cos"], g[f"{k}/sin"], g[f"{k}/rotated_bias"]
+        assert want.shape == (c["heads"], c["positions"], c["dim"]) and want.dtype == np.float32
+        for h in range(c["heads"]):
+            assert spec_np.rotated_bias(bias[h], cos, sin).tobytes() == want[h].tobytes(), (k, h)
