@@ -60,12 +60,15 @@ class KVCache:
     ``capacity`` tokens of dimension ``dim``."""
 
     def __init__(self, segments: int, dim: int, capacity: int, key_config, value_config, *,
-                 out_dtype="bfloat16", device=None, pitch: PITCH | None = None, key_bias=None):
+                 out_dtype="bfloat16", device=None, pitch: PITCH | None = None, key_bias=None,
+                 fuse_key_bias: bool = True):
         """``key_bias=(bias, cos_table, sin_table)`` turns on exact key-bias removal
         (reference/mechanism_eval.py:4-7): ``bias`` float32 ``[segments, dim]`` is the key
         projection's bias per KV head, the tables float32 ``[positions, dim]`` are the model's
         rotary tables.  The rotated bias of a token's position is subtracted from the keys before
-        they are encoded and added back to the decoded keys, at no storage cost."""
+        they are encoded and added back to the decoded keys, at no storage cost.  On cache shapes
+        the one-launch kernel covers, ``decode`` and ``step`` do this inside their launch;
+        ``fuse_key_bias=False`` keeps it as separate element-wise launches (same results)."""
         torch = _torch()
         self.pitch = pitch if pitch is not None else PITCH(device)
         self.device = self.pitch.device
@@ -83,13 +86,18 @@ class KVCache:
         self._float_dtypes = (torch.float32, torch.float16, torch.bfloat16)
         self.planes = [self._make_plane("keys", key_config), self._make_plane("values", value_config)]
         self._piece_limit = min([pl.config.group_size for pl in self.planes if pl.is_channel] + [65535])
-        self._fused = self._fused_ok()
         self.key_bias = None
+        self._fused = self._fused_ok()
+        self._fuse_bias = False
         if key_bias is not None:
             bias, cos_table, sin_table = key_bias
             if tuple(bias.shape) != (self.segments, self.dim) or cos_table.shape[0] < self.capacity:
                 raise InvalidInput(f"key_bias needs bias [{self.segments}, {self.dim}] and tables with at least {self.capacity} rows")
+            for t, name in ((bias, "bias"), (cos_table, "cos_table"), (sin_table, "sin_table")):
+                if not (t.is_cuda and t.is_contiguous() and t.dtype == torch.float32 and t.dim() == 2 and t.shape[1] == self.dim):
+                    raise InvalidInput(f"key_bias {name} must be a contiguous float32 CUDA tensor with {self.dim} columns")
             self.key_bias = (bias, cos_table, sin_table)
+            self._fuse_bias = bool(fuse_key_bias) and self._fused
         codebooks.register_all()
 
     def _make_plane(self, name: str, cfg) -> _Plane:
@@ -107,9 +115,17 @@ class KVCache:
         return _Plane(name, cfg, codes, side, out, residual)
 
     # ------------------------------------------------------------------ descriptors
-    def _desc(self, tokens: int) -> _native.CacheDesc:
+    def _desc(self, tokens: int, with_bias: bool = False) -> _native.CacheDesc:
         """The C descriptor of this cache.  Buffers never move, so it is filled once and only the
-        token count changes from call to call (this runs on the per-token path)."""
+        token count changes from call to call (this runs on the per-token path).  ``with_bias``
+        selects the twin that also carries the key-bias tables (what ``decode`` and ``step`` pass
+        when the bias is handled inside their launch)."""
+        if with_bias:
+            if self._desc_cache is None:
+                self._desc(tokens)
+            d = self._desc_bias
+            d.tokens = tokens
+            return d
         d = self._desc_cache
         if d is None:
             d = _native.CacheDesc()
@@ -143,6 +159,15 @@ class KVCache:
                     src[i].residual_bytes = pl.residual.numel() * 4
             self._src_cache = src
             self._lib = _native.lib()
+            # twin descriptor with the key-bias tables
+            b = _native.CacheDesc.from_buffer_copy(d)
+            if self.key_bias is not None:
+                bias, cos_table, sin_table = self.key_bias
+                self._rope = _native.RopeBias(bias.data_ptr(), self.dim * 4, cos_table.data_ptr(), sin_table.data_ptr(),
+                                              int(cos_table.shape[0]))
+                b.key_bias = ctypes.pointer(self._rope)
+            self._desc_bias = b
+            self._desc_bias_ref = ctypes.byref(b)
         d.tokens = tokens
         return d
 
@@ -218,7 +243,7 @@ class KVCache:
         and decodes the whole cache, new token included, in a single launch; returns the decoded
         views like ``decode``.  Results are exactly those of ``append`` followed by ``decode``.
         Cache shapes the one-launch kernel does not cover run as those two calls."""
-        if self.key_bias is not None or not self._fused:
+        if not self._fused or (self.key_bias is not None and not self._fuse_bias):
             self.append(keys, values, stream)
             return self.decode(stream)
         keys, values = self._check_new(keys, "keys"), self._check_new(values, "values")
@@ -226,9 +251,9 @@ class KVCache:
             raise InvalidInput("step takes one new token per segment: keys and values of shape [segments, 1, dim], same dtype")
         if self.tokens >= self.capacity:
             raise InvalidInput(f"cache holds {self.tokens} of {self.capacity} tokens; cannot append 1")
-        self._desc(self.tokens)
+        self._desc(self.tokens, self._fuse_bias)
         src = self._fill_src(keys, values, 0, 1)
-        st = self._lib.pitch_enqueue_cache_step(self._desc_ref, src, native_dtype(keys.dtype),
+        st = self._lib.pitch_enqueue_cache_step(self._desc_bias_ref if self._fuse_bias else self._desc_ref, src, native_dtype(keys.dtype),
                                                 self._state.data_ptr() if self._state is not None else None,
                                                 stream_handle(stream, self.device))
         if st:
@@ -258,7 +283,7 @@ class KVCache:
         step can be replayed token after token (``capture_step`` / ``replay``).  Needs a cache shape
         the one-launch step covers and no key-bias removal."""
         torch = _torch()
-        if not self._fused or self.key_bias is not None:
+        if not self._fused or (self.key_bias is not None and not self._fuse_bias):
             raise InvalidInput("the device-side token counter needs a cache shape the one-launch step covers")
         if self._state is None:
             self._state = torch.zeros(2, dtype=torch.int64, device=self.device)     # tokens | status, arrivals
@@ -360,11 +385,12 @@ class KVCache:
         once the stream reaches this point)."""
         if self.tokens < 1:
             raise InvalidInput("the cache is empty")
-        self._desc(self.tokens)
-        st = self._lib.pitch_enqueue_cache_decode(self._desc_ref, stream_handle(stream, self.device))
+        self._desc(self.tokens, self._fuse_bias)
+        st = self._lib.pitch_enqueue_cache_decode(self._desc_bias_ref if self._fuse_bias else self._desc_ref,
+                                                  stream_handle(stream, self.device))
         if st:
             _native.check(st)
-        if self.key_bias is not None:
+        if self.key_bias is not None and not self._fuse_bias:
             self.pitch.enqueue_rope_bias(self.planes[0].out[:, :self.tokens], *self.key_bias, first_position=0,
                                          subtract=False, stream=stream)
         return tuple(pl.out[:, :self.tokens] for pl in self.planes)

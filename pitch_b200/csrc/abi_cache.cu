@@ -307,6 +307,12 @@ int fill_cache64(Cache64Params& p, const pitch_cache_desc* d, int turbo_bits) {
     }
     if (any_turbo && !book_get(dim, turbo_bits, p.book.c))
         return fail(PITCH_ERR_INVALID_INPUT, "no TurboQuant codebook for dim %d, bits %d", dim, turbo_bits);
+    if (d->key_bias != nullptr) {
+        p.bias = reinterpret_cast<const unsigned char*>(d->key_bias->bias);
+        p.bias_seg_stride = d->key_bias->bias_seg_stride;
+        p.cos_table = d->key_bias->cos_table;
+        p.sin_table = d->key_bias->sin_table;
+    }
     return PITCH_OK;
 }
 
@@ -358,6 +364,11 @@ int pitch_enqueue_cache_decode(const pitch_cache_desc* d, void* stream) {
     if (fused_shape(d, d->tokens, &turbo_bits)) {
         Cache64Params p;
         if ((st = fill_cache64(p, d, turbo_bits))) return st;
+        if (d->key_bias != nullptr) {
+            // the rotated key bias is added to plane 0 inside the launch
+            if ((st = launch_cache64_bias(p, dim, turbo_bits, d->out_dtype, d->tokens, s))) return st;
+            return launch_status(false, "cache_decode with key bias");
+        }
         PITCH_DISPATCH_DTYPE(d->out_dtype, st = (launch_cache64<T>(p, dim, turbo_bits, d->tokens, s)));
         if (st) return st;
         if ((st = launch_status(false, "cache_decode"))) return st;
@@ -475,7 +486,7 @@ int pitch_enqueue_cache_step(const pitch_cache_desc* d, const pitch_append_src* 
     if ((st = check_append_src(d, src, in_dtype, 1, dev, nullptr))) return st;
 
     int turbo_bits = 4;
-    const bool fused = fused_shape(d, after, &turbo_bits) && d->key_bias == nullptr;
+    const bool fused = fused_shape(d, after, &turbo_bits);
     if (!fused) {
         if (state != nullptr)
             return fail(PITCH_ERR_INVALID_INPUT, "a device-side token counter needs a cache shape the one-launch step covers "
@@ -504,6 +515,10 @@ int pitch_enqueue_cache_step(const pitch_cache_desc* d, const pitch_append_src* 
         p.step[i].residual_seg_elems = src[i].residual_seg_stride / 4;
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (d->key_bias != nullptr) {
+        if ((st = launch_cache64_bias(p, d->dim, turbo_bits, d->out_dtype, after, s))) return st;
+        return launch_status(false, "cache_step with key bias");
+    }
     PITCH_DISPATCH_DTYPE(d->out_dtype, st = (launch_cache64<T>(p, d->dim, turbo_bits, after, s)));
     if (st) return st;
     return launch_status(false, "cache_step");

@@ -1,0 +1,61 @@
+// The whole-cache launch with exact key-bias removal (cache_decode_bias_kernel): its template
+// instances live in a translation unit of their own so that they compile beside the others.
+#include "abi_internal.h"
+
+#include <atomic>
+
+#include "cache_kernels.cuh"
+#include "common.cuh"
+
+using namespace pitch;
+using namespace pitch_abi;
+
+namespace {
+
+template <typename T, int D, int BITS>
+int launch_bias_impl(const Cache64Params& p, int64_t tokens_for_grid, cudaStream_t s) {
+    static std::atomic<bool> configured[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    constexpr int smem = cache64_bias_smem_bytes<T>();
+    if (dev >= 0 && dev < 64 && !configured[dev].load(std::memory_order_acquire)) {
+        if (cudaFuncSetAttribute(cache_decode_bias_kernel<T, D, BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return launch_status(false, "cache_decode with key bias (shared memory opt-in)");
+        configured[dev].store(true, std::memory_order_release);
+    }
+    // one CTA per multiprocessor, each taking whole token blocks (one item's worth of tokens for every segment and plane)
+    int64_t ctas = ceil_div(tokens_for_grid, 2048 / D);
+    if (ctas > sm_count()) ctas = sm_count();
+    if (ctas < 1) ctas = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)ctas);
+    cfg.blockDim = dim3(CD_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, cache_decode_bias_kernel<T, D, BITS>, p);
+    return PITCH_OK;
+}
+
+template <typename T>
+int launch_bias(const Cache64Params& p, int dim, int bits, int64_t tokens_for_grid, cudaStream_t s) {
+    if (dim == 64)
+        return bits == 4 ? launch_bias_impl<T, 64, 4>(p, tokens_for_grid, s) : launch_bias_impl<T, 64, 3>(p, tokens_for_grid, s);
+    return bits == 4 ? launch_bias_impl<T, 128, 4>(p, tokens_for_grid, s) : launch_bias_impl<T, 128, 3>(p, tokens_for_grid, s);
+}
+
+}  // namespace
+
+namespace pitch_abi {
+
+int launch_cache64_bias(const Cache64Params& p, int dim, int bits, int dtype, int64_t tokens_for_grid, cudaStream_t s) {
+    int st = 0;
+    PITCH_DISPATCH_DTYPE(dtype, st = (launch_bias<T>(p, dim, bits, tokens_for_grid, s)));
+    return st;
+}
+
+}  // namespace pitch_abi

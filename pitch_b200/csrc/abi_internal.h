@@ -12,6 +12,10 @@
 
 #include <cmath>
 
+namespace pitch {
+struct Cache64Params;
+}
+
 namespace pitch_abi {
 
 // Records the detail of a failure for pitch_last_error() on this thread and returns `status`.
@@ -63,6 +67,10 @@ unsigned vec_grid_looping(int64_t count, int dim);
 // kind: PITCH_PLANE_TURBO (bits 3 or 4) or PITCH_PLANE_CHANNEL (bits 4, group_size a multiple of 2048/dim).
 int cache64_single_plane(int kind, int dim, int bits, int group_size, uint32_t seed, int dtype, const void* codes,
                          const void* side, void* out, int64_t count, cudaStream_t s);
+
+// The same kernel family with exact key-bias removal on plane 0 (abi_cache_bias.cu); `p` carries the
+// bias row pointer and the rotary tables.  dim in {64, 128}, bits (of the TurboQuant planes) in {3, 4}.
+int launch_cache64_bias(const pitch::Cache64Params& p, int dim, int bits, int dtype, int64_t tokens_for_grid, cudaStream_t s);
 
 }  // namespace pitch_abi
 

@@ -178,14 +178,63 @@ __device__ __forceinline__ uint32_t pair_offset(const uint32_t (&w)[8], int p, u
     }
 }
 
+// ---- exact key-bias removal inside the decode (reference/mechanism_eval.py:82-91) -----------------
+// R_t b for coordinate c: fl(fl(b[c] * cos[t][c]) + fl(rh[c] * sin[t][c])), rh = rotate_half(b) =
+// (-b[D/2:], b[:D/2]): the arithmetic of rope_bias_kernel, one rounding per operation.
+__device__ __forceinline__ float rotated_bias_at(float b, float rh, float c, float s) {
+    return __fadd_rn(__fmul_rn(b, c), __fmul_rn(rh, s));
+}
+
+// The rotary tables of one token block (TOKENS tokens) staged in shared memory: token t, table j
+// (0 cosine, 1 sine), 4-float chunk q at chunk index (t*2 + j) * D/4 + (q ^ ((q >> 3) & 1)).  The
+// swizzle makes the two access patterns of the decoders (8 lanes reading every second chunk, or 8
+// lanes reading 8 consecutive chunks) free of bank conflicts.
+template <int D>
+__device__ __forceinline__ float4 tile_chunk(const float* tile, int t, int j, int q) {
+    return reinterpret_cast<const float4*>(tile)[(t * 2 + j) * (D / 4) + (q ^ ((q >> 3) & 1))];
+}
+
+// b and rotate_half(b) for N consecutive coordinates starting at c0 (a multiple of N, N <= 8, so the
+// block lies in one half of the vector); brow is the segment's bias row in global memory.
+template <int D, int N>
+__device__ __forceinline__ void load_bias_block(const float* __restrict__ brow, int c0, float (&b)[N], float (&rh)[N]) {
+    const bool low = c0 < D / 2;
+    const float* partner = brow + (low ? c0 + D / 2 : c0 - D / 2);
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+        b[i] = __ldg(brow + c0 + i);
+        const float o = __ldg(partner + i);
+        rh[i] = low ? -o : o;
+    }
+}
+
+// x[i] -> T(T(x[i]) + R_t b): what a separate pass over the stored (already rounded) output gives.
+// cq = index of this lane's N-coordinate block inside the vector, t = token inside the block's tile.
+template <typename T, int D, int N>
+__device__ __forceinline__ void add_bias_block(float (&x)[N], const float* tile, int t, int cq, const float (&b)[N],
+                                               const float (&rh)[N]) {
+    float c[N], s[N];
+#pragma unroll
+    for (int h = 0; h < N / 4; ++h) {
+        const float4 c4 = tile_chunk<D>(tile, t, 0, cq * (N / 4) + h), s4 = tile_chunk<D>(tile, t, 1, cq * (N / 4) + h);
+        c[4 * h] = c4.x; c[4 * h + 1] = c4.y; c[4 * h + 2] = c4.z; c[4 * h + 3] = c4.w;
+        s[4 * h] = s4.x; s[4 * h + 1] = s4.y; s[4 * h + 2] = s4.z; s[4 * h + 3] = s4.w;
+    }
+#pragma unroll
+    for (int i = 0; i < N; ++i) x[i] = __fadd_rn(x[i], rotated_bias_at(b[i], rh[i], c[i], s[i]));
+}
+
 // 64 coordinates per lane (BITS-bit codes): a whole vector at D = 64, half of one at D = 128.
 // `table` is the pair table, `sign` 32 words for this lane's 64 coordinates whose bit 15 / bit 31 say
 // whether coordinate 2p / 2p+1 is negated by the rotation's diagonal.  `out` points at the item's
 // first output element.
-template <typename T, int D, int BITS, bool FULL>
+// BIAS: the rotated key bias of each token (tables of the token block in `tile`, the segment's bias row
+// at `brow`) is added to the rounded output on its way from the staging tile to global memory.
+template <typename T, int D, int BITS, bool FULL, bool BIAS = false>
 __device__ __forceinline__ void turbo64_decode_warp(const Prefetch64& f, T* __restrict__ out, int nvalid,
                                                     const unsigned char* table, const uint32_t* sign,
-                                                    unsigned char* stage, int lane, float rs) {
+                                                    unsigned char* stage, int lane, float rs,
+                                                    const float* tile = nullptr, const float* brow = nullptr) {
     typedef WarpStage<T, 64> Stage;
     const uint32_t w[8] = {f.a.x, f.a.y, f.a.z, f.a.w, f.b.x, f.b.y, f.b.z, f.b.w};
     const float norm = __uint_as_float(f.c.x);
@@ -247,10 +296,29 @@ __device__ __forceinline__ void turbo64_decode_warp(const Prefetch64& f, T* __re
     const unsigned char* src = stage + (lane / Stage::CPR) * Stage::PITCHB + (lane % Stage::CPR) * 16;
     uint4* dst = reinterpret_cast<uint4*>(out) + lane;
     const int valid_chunks = nvalid * (D / Stage::EPC);
+    if constexpr (BIAS) {
+        constexpr int EPC = Stage::EPC, CPT = D / EPC;            // elements per 16-byte chunk, chunks per token
+        const int cq = lane % CPT;                                // this lane's coordinate block, the same for every k
+        float bb[EPC], rh[EPC];
+        load_bias_block<D, EPC>(brow, cq * EPC, bb, rh);
 #pragma unroll
-    for (int k = 0; k < Stage::CPR; ++k) {
-        const uint4 q = *reinterpret_cast<const uint4*>(src + k * (32 / Stage::CPR) * Stage::PITCHB);
-        if (FULL || k * 32 + lane < valid_chunks) stg_stream(dst + k * 32, q);
+        for (int k = 0; k < Stage::CPR; ++k) {
+            const uint4 q = *reinterpret_cast<const uint4*>(src + k * (32 / Stage::CPR) * Stage::PITCHB);
+            if (FULL || k * 32 + lane < valid_chunks) {
+                uint32_t w4[4] = {q.x, q.y, q.z, q.w};
+                float x[EPC];
+                Packer<T, EPC>::unpack(w4, x);
+                add_bias_block<T, D, EPC>(x, tile, (k * 32 + lane) / CPT, cq, bb, rh);
+                Packer<T, EPC>::pack(x, w4);
+                stg_stream(dst + k * 32, make_uint4(w4[0], w4[1], w4[2], w4[3]));
+            }
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < Stage::CPR; ++k) {
+            const uint4 q = *reinterpret_cast<const uint4*>(src + k * (32 / Stage::CPR) * Stage::PITCHB);
+            if (FULL || k * 32 + lane < valid_chunks) stg_stream(dst + k * 32, q);
+        }
     }
     __syncwarp();
 }
@@ -324,10 +392,11 @@ __device__ __forceinline__ float step15(float lo, float hi) {
 
 // TOKENS tokens (4-bit codes, all inside one group) per warp: lane = (token lane, slab).
 // code * step + lo with one rounding per operation.
-template <typename T, int D, bool FULL>
-__device__ __forceinline__ void channel64_decode_warp(const Prefetch64& f, T* __restrict__ out, int nvalid, int lane) {
+template <typename T, int D, bool FULL, bool BIAS = false>
+__device__ __forceinline__ void channel64_decode_warp(const Prefetch64& f, T* __restrict__ out, int nvalid, int lane,
+                                                      const float* tile = nullptr, const float* brow = nullptr) {
     constexpr int SLABS = Item64<D>::SLABS, TOK_LANES = Item64<D>::TOK_LANES;
-    const int tok_lane = lane / SLABS;
+    const int tok_lane = lane / SLABS, slab = lane & (SLABS - 1);
     const uint32_t w[8] = {f.a.x, f.a.y, f.a.z, f.a.w, f.b.x, f.b.y, f.b.z, f.b.w};
     const uint32_t lo16[4] = {f.c.x, f.c.y, f.c.z, f.c.w}, hi16[4] = {f.d.x, f.d.y, f.d.z, f.d.w};
     float2 lo[4], step[4];
@@ -337,6 +406,8 @@ __device__ __forceinline__ void channel64_decode_warp(const Prefetch64& f, T* __
         const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&hi16[i]));
         step[i] = make_float2(step15(lo[i].x, hi.x), step15(lo[i].y, hi.y));
     }
+    float bb[8], rh[8];
+    if constexpr (BIAS) load_bias_block<D, 8>(brow, slab * 8, bb, rh);
     T* mine = out + lane * 8;                 // token k*TOK_LANES + tok_lane, slab: element k*256 + lane*8
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
@@ -344,6 +415,18 @@ __device__ __forceinline__ void channel64_decode_warp(const Prefetch64& f, T* __
         codes8_to_pairs(w[k], v);
 #pragma unroll
         for (int i = 0; i < 4; ++i) v[i] = mul2_then_add(v[i], step[i], lo[i]);
+        if constexpr (BIAS) {
+            // the value as stored by a decode without the option (rounded to T), plus R_t b
+            float x[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                x[2 * i] = Elem<T>::to_f32(Elem<T>::from_f32(v[i].x));
+                x[2 * i + 1] = Elem<T>::to_f32(Elem<T>::from_f32(v[i].y));
+            }
+            add_bias_block<T, D, 8>(x, tile, TOK_LANES * k + tok_lane, slab, bb, rh);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[i] = make_float2(x[2 * i], x[2 * i + 1]);
+        }
         Pairs8<T>::store(mine + 256 * k, v, FULL || TOK_LANES * k + tok_lane < nvalid);
     }
 }
@@ -387,6 +470,11 @@ struct Cache64Params {
     Plane64 plane[4];
     StepPlane step[4];
     Book16 book;              // TurboQuant centroids for (dim, bits)
+    // exact key-bias removal on plane 0 (cache_decode_bias_kernel only)
+    const unsigned char* bias;      // float32 [segments][dim]
+    int64_t bias_seg_stride;
+    const float* cos_table;         // float32 [positions][dim]
+    const float* sin_table;
 };
 
 constexpr int CD_SIGN_BYTES = 4 * 64 * 4;      // [plane][pair of the vector] sign words
@@ -404,6 +492,28 @@ __device__ __forceinline__ float load_elem_f32(const unsigned char* p, int dtype
     if (dtype == 1) return __half2float(reinterpret_cast<const __half*>(p)[idx]);
     return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[idx]);
 }
+__device__ __forceinline__ float round_to_dtype(float v, int dtype) {
+    if (dtype == 0) return v;
+    if (dtype == 1) return __half2float(__float2half_rn(v));
+    return __bfloat162float(__float2bfloat16_rn(v));
+}
+
+// Key-bias removal for the token a step appends: the segment's bias row and the rotary table rows of
+// the token's position (all in global memory).  A null brow means "no bias".
+struct RopeNew {
+    const float* brow;
+    const float* cos_row;
+    const float* sin_row;
+};
+
+// x - R_t b for coordinate c of the new token, rounded to the element type the token arrived in
+// (what subtracting in place from a copy of the input gives).
+template <int D>
+__device__ __forceinline__ float remove_bias(float x, int c, const RopeNew& rn, int in_dtype) {
+    const float b = __ldg(rn.brow + c);
+    const float rh = c < D / 2 ? -__ldg(rn.brow + c + D / 2) : __ldg(rn.brow + c - D / 2);
+    return round_to_dtype(__fsub_rn(x, rotated_bias_at(b, rh, __ldg(rn.cos_row + c), __ldg(rn.sin_row + c))), in_dtype);
+}
 
 // TurboQuant encode of ONE vector by a whole warp (the token a step appends): lane l owns the
 // D/32 consecutive coordinates l*D/32 ...; the float operations and their order are those of
@@ -416,12 +526,13 @@ template <int D, int BITS>
 __device__ __forceinline__ void turbo_append_warp(Prefetch64& f, const unsigned char* __restrict__ in, int in_dtype,
                                                   uint32_t* __restrict__ codes_tok, float* __restrict__ norm_out,
                                                   int tok_in_item, const uint32_t* neg, const float* s_edges, float rs,
-                                                  unsigned char* stage, int lane) {
+                                                  unsigned char* stage, int lane, const RopeNew rn = RopeNew{nullptr, nullptr, nullptr}) {
     constexpr int E = D / 32, LPV = Item64<D>::LPV, WPV = D * BITS / 32;
     float x[E], t[E];
 #pragma unroll
     for (int i = 0; i < E; ++i) {
         x[i] = load_elem_f32(in, in_dtype, lane * E + i);
+        if (rn.brow != nullptr) x[i] = remove_bias<D>(x[i], lane * E + i, rn, in_dtype);
         t[i] = x[i] * x[i];
     }
     const float norm = sqrtf(lanes_sum(tree_sum_regs(t), 32));
@@ -478,9 +589,10 @@ __device__ __forceinline__ void turbo_append_warp(Prefetch64& f, const unsigned 
 // own (minimum and maximum are idempotent, so it does not matter whether a warp sees the running
 // range before or after the holder of the new token has updated it), and only the holder writes
 // the residual row, the running range and the fp16 range.  Arithmetic as channel_encode_slab_kernel.
-template <typename T, int D>
+template <typename T, int D, bool BIAS = false>
 __device__ __forceinline__ void channel_step_warp(const Plane64& P, const StepPlane& S, int in_dtype, int64_t seg,
-                                                  int item, int64_t t_old, T* __restrict__ out, int nvalid, int lane) {
+                                                  int item, int64_t t_old, T* __restrict__ out, int nvalid, int lane,
+                                                  const RopeNew rn = RopeNew{nullptr, nullptr, nullptr}, const float* tile = nullptr) {
     constexpr int SLABS = Item64<D>::SLABS, TOK_LANES = Item64<D>::TOK_LANES, TOKENS = Item64<D>::TOKENS;
     const int slab = lane & (SLABS - 1), tok_lane = lane / SLABS;
     const int G = P.group_items * TOKENS;
@@ -493,7 +605,10 @@ __device__ __forceinline__ void channel_step_warp(const Plane64& P, const StepPl
 
     float xn[8], lo[8], hi[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) xn[i] = load_elem_f32(in, in_dtype, slab * 8 + i);
+    for (int i = 0; i < 8; ++i) {
+        xn[i] = load_elem_f32(in, in_dtype, slab * 8 + i);
+        if (BIAS) xn[i] = remove_bias<D>(xn[i], slab * 8 + i, rn, in_dtype);
+    }
     if (pos > 0) {
         const float4 l0 = *reinterpret_cast<const float4*>(res + (int64_t)G * D + slab * 8);
         const float4 l1 = *reinterpret_cast<const float4*>(res + (int64_t)G * D + slab * 8 + 4);
@@ -571,7 +686,7 @@ __device__ __forceinline__ void channel_step_warp(const Plane64& P, const StepPl
     }
     f.a = make_uint4(w[0], w[1], w[2], w[3]);
     f.b = make_uint4(w[4], w[5], w[6], w[7]);
-    channel64_decode_warp<T, D, false>(f, out, nvalid, lane);
+    channel64_decode_warp<T, D, false, BIAS>(f, out, nvalid, lane, tile, rn.brow);
 }
 
 // grid = number of SMs (persistent), CD_THREADS threads, cache64_smem_bytes<T>() dynamic shared memory.
@@ -749,6 +864,206 @@ cache_decode_kernel(const __grid_constant__ Cache64Params p) {
     // ---- device-side token counter: the last CTA to finish publishes the new count.  The counter is
     // read again here (nothing has changed it since the start of the grid: only the last arrival
     // writes) so that no register has to carry it through the main loop.
+    if (p.append && p.state != nullptr) {
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const long long held = p.state->tokens;
+            if (held >= p.capacity) {
+                p.state->status = 1;
+            } else {
+                __threadfence();
+                if (atomicAdd(&p.state->arrivals, 1u) == gridDim.x - 1) {
+                    p.state->arrivals = 0;
+                    p.state->tokens = held + 1;
+                }
+            }
+        }
+    }
+}
+
+// --------------------------------------------------------------------------------------------------
+// The same launch with exact key-bias removal on plane 0 (README.md:100 of the reference lists it as
+// missing from its kernels; arithmetic of rope_bias_kernel): the rotated bias R_t b of every token is
+// added to the decoded keys on their way out, and taken off the new key before it is encoded, so the
+// decoded keys never make a second trip through memory.  R_t b needs the rotary tables of the token:
+// 2 x dim floats per token, four times the bf16 output of that token.  Read per item they would
+// dominate the traffic, so the work is arranged by TOKEN BLOCK instead: a CTA takes one block of
+// tokens (one item's worth), stages the block's cos/sin rows in shared memory once (asynchronous
+// copies, the next block's rows in flight while this one is used), and its 16 warps then decode that
+// block for every segment and plane.  The tables are read once per launch instead of once per segment.
+// Results equal the launch without the option followed by the separate element-wise pass, bit for bit.
+// --------------------------------------------------------------------------------------------------
+constexpr int CD_TILE_BYTES = 2048 * 2 * 4;                   // cos and sin of one item's 2048 coordinates
+template <typename T> struct TileBuffers { static constexpr int N = sizeof(T) == 2 ? 2 : 1; };
+template <typename T>
+constexpr int cache64_bias_smem_bytes() { return cache64_smem_bytes<T>() + TileBuffers<T>::N * CD_TILE_BYTES; }
+
+template <typename T, int D, int BITS>
+__global__ void __launch_bounds__(CD_THREADS, 1)
+cache_decode_bias_kernel(const __grid_constant__ Cache64Params p) {
+    constexpr int TOKENS = Item64<D>::TOKENS, LPV = Item64<D>::LPV;
+    constexpr int ITEM_CODE_BYTES = 32 * 8 * BITS;
+    constexpr int CH_ITEM_CODE_BYTES = 1024;
+    constexpr int NBUF = TileBuffers<T>::N;
+    extern __shared__ __align__(1024) unsigned char smem[];
+    unsigned char* table = smem;
+    uint32_t* s_sign = reinterpret_cast<uint32_t*>(smem + CD_TABLE_BYTES);
+    float* s_edges = reinterpret_cast<float*>(smem + CD_TABLE_BYTES + CD_SIGN_BYTES);
+    unsigned char* stage_base = smem + CD_TABLE_BYTES + CD_SIGN_BYTES + CD_EDGE_BYTES;
+    float* tiles = reinterpret_cast<float*>(stage_base + CD_WARPS * WarpStage<T, 64>::BYTES);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+    bool any_turbo = false;
+    for (int pl = 0; pl < p.n_planes; ++pl) any_turbo |= p.plane[pl].kind == 0;
+    if (any_turbo) {
+        constexpr int ENTRIES = 1 << (2 * BITS);
+        for (int idx = threadIdx.x; idx < ENTRIES * 32; idx += CD_THREADS) {
+            const int e = idx >> 5;
+            const float a = p.book.c[e & ((1 << BITS) - 1)], b = p.book.c[e >> BITS];
+            if (D == 128 && BITS == 4)
+                *reinterpret_cast<float*>(table + e * 256 + (idx & 31) * 4) = (idx & 1) ? b - a : a + b;
+            else
+                *reinterpret_cast<float2*>(table + idx * 8) = make_float2(a + b, a - b);
+        }
+        if (threadIdx.x < 4 * 64) {
+            const int pl = threadIdx.x >> 6, i = threadIdx.x & 63;
+            const uint32_t m = p.plane[pl].neg[i >> 4];
+            const int bit = (2 * i) & 31;
+            s_sign[threadIdx.x] = (((m >> bit) & 1u) << 15) | (((m >> (bit + 1)) & 1u) << 31);
+        }
+        if (threadIdx.x < (1 << BITS) - 1) s_edges[threadIdx.x] = 0.5f * (p.book.c[threadIdx.x] + p.book.c[threadIdx.x + 1]);
+    }
+    __syncthreads();
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
+    unsigned char* stage = stage_base + warp * WarpStage<T, 64>::BYTES;
+    const uint32_t* my_sign_base = s_sign + (LPV == 2 ? (lane & 1) * 32 : 0);
+
+    // ---- geometry of this launch (as in cache_decode_kernel)
+    const int64_t t_old = p.state != nullptr ? p.state->tokens : p.tokens;
+    const bool refuse = p.append && p.state != nullptr && t_old >= p.capacity;
+    const int64_t total = t_old + (p.append ? 1 : 0);
+    const int last_items = (int)((total + TOKENS - 1) / TOKENS);
+    int full_items = (int)(total / TOKENS);
+    if (p.append) {
+        full_items = (int)(t_old / TOKENS);
+        for (int pl = 0; pl < p.n_planes; ++pl)
+            if (p.plane[pl].kind == 1) {
+                const int G = p.plane[pl].group_items * TOKENS;
+                const int first = (int)(t_old / G) * p.plane[pl].group_items;
+                full_items = first < full_items ? first : full_items;
+            }
+    }
+    const int units = p.segments * p.n_planes;               // (segment, plane) pairs, all at the CTA's token block
+
+    // cos and sin rows of token block tb -> shared memory (16-byte asynchronous copies, swizzled chunks)
+    auto load_tile = [&](int tb, float* dst) {
+        const uint32_t base = (uint32_t)__cvta_generic_to_shared(dst);
+        constexpr int CPRW = D / 4;                            // 4-float chunks per table row
+        for (int c = threadIdx.x; c < TOKENS * 2 * CPRW; c += CD_THREADS) {
+            const int t = c / (2 * CPRW), r = c - t * (2 * CPRW), j = r / CPRW, q = r - j * CPRW;
+            const int64_t tok = (int64_t)tb * TOKENS + t;
+            const bool live = tok < total;
+            const float* src = (j ? p.sin_table : p.cos_table) + (live ? tok * D + q * 4 : 0);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                         :: "r"(base + (uint32_t)(((t * 2 + j) * CPRW + (q ^ ((q >> 3) & 1))) * 16)), "l"(src), "r"(live ? 16 : 0) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    // one (segment, plane) of token block `item`: prefetch ...
+    auto fetch = [&](int u, int item, Prefetch64& f) {
+        const int seg = u / p.n_planes, pl = u - seg * p.n_planes;
+        const Plane64& P = p.plane[pl];
+        const unsigned char* side = P.side + seg * P.side_seg_stride;
+        const bool whole = item < full_items;
+        const int64_t left = total - (int64_t)item * TOKENS;
+        const int nvalid = left < TOKENS ? (int)left : TOKENS;
+        if (P.kind == 0) {
+            const unsigned char* codes = P.codes + seg * P.codes_seg_stride + (int64_t)item * ITEM_CODE_BYTES;
+            const float* norms = reinterpret_cast<const float*>(side) + (int64_t)item * TOKENS;
+            if (whole) prefetch_turbo64<D, BITS, true>(f, codes, norms, TOKENS, lane);
+            else prefetch_turbo64<D, BITS, false>(f, codes, norms, (p.append && item == (int)(t_old / TOKENS)) ? nvalid - 1 : nvalid, lane);
+        } else {
+            const uint32_t* codes = reinterpret_cast<const uint32_t*>(P.codes + seg * P.codes_seg_stride + (int64_t)item * CH_ITEM_CODE_BYTES);
+            const __half* ranges = reinterpret_cast<const __half*>(side) + (int64_t)(item / P.group_items) * (2 * D);
+            if (whole) prefetch_channel64<D, true>(f, codes, ranges, TOKENS, lane);
+            else if (!(p.append && item / P.group_items == (int)(t_old / (P.group_items * TOKENS))))
+                prefetch_channel64<D, false>(f, codes, ranges, nvalid, lane);
+        }
+    };
+    // ... and decode (with the append work where the item is touched by it)
+    auto decode = [&](int u, int item, Prefetch64& f, const float* tile) {
+        const int seg = u / p.n_planes, pl = u - seg * p.n_planes;
+        const Plane64& P = p.plane[pl];
+        const bool whole = item < full_items;
+        const int64_t left = total - (int64_t)item * TOKENS;
+        const int nvalid = left < TOKENS ? (int)left : TOKENS;
+        T* out = reinterpret_cast<T*>(P.out + seg * P.out_seg_stride) + (int64_t)item * 2048;
+        const float* brow = reinterpret_cast<const float*>(p.bias + seg * p.bias_seg_stride);
+        RopeNew rn = RopeNew{nullptr, nullptr, nullptr};
+        if (pl == 0) rn = RopeNew{brow, p.cos_table + t_old * D, p.sin_table + t_old * D};
+        if (P.kind == 0) {
+            if (whole) {
+                if (pl == 0) turbo64_decode_warp<T, D, BITS, true, true>(f, out, TOKENS, table, my_sign_base + pl * 64, stage, lane, p.rs, tile, brow);
+                else turbo64_decode_warp<T, D, BITS, true>(f, out, TOKENS, table, my_sign_base + pl * 64, stage, lane, p.rs);
+                return;
+            }
+            if (p.append && item == (int)(t_old / TOKENS)) {
+                const int tok = nvalid - 1;
+                unsigned char* item_codes = const_cast<unsigned char*>(P.codes) + seg * P.codes_seg_stride + (int64_t)item * ITEM_CODE_BYTES;
+                float* item_norms = reinterpret_cast<float*>(const_cast<unsigned char*>(P.side) + seg * P.side_seg_stride) + (int64_t)item * TOKENS;
+                turbo_append_warp<D, BITS>(f, p.step[pl].in + seg * p.step[pl].in_seg_stride, p.in_dtype,
+                                           reinterpret_cast<uint32_t*>(item_codes) + tok * (D * BITS / 32), item_norms + tok, tok,
+                                           P.neg, s_edges, p.rs, stage, lane, rn);
+            }
+            if (pl == 0) turbo64_decode_warp<T, D, BITS, false, true>(f, out, nvalid, table, my_sign_base + pl * 64, stage, lane, p.rs, tile, brow);
+            else turbo64_decode_warp<T, D, BITS, false>(f, out, nvalid, table, my_sign_base + pl * 64, stage, lane, p.rs);
+        } else {
+            if (whole) {
+                if (pl == 0) channel64_decode_warp<T, D, true, true>(f, out, TOKENS, lane, tile, brow);
+                else channel64_decode_warp<T, D, true>(f, out, TOKENS, lane);
+            } else if (p.append && item / P.group_items == (int)(t_old / (P.group_items * TOKENS))) {
+                if (pl == 0) channel_step_warp<T, D, true>(P, p.step[pl], p.in_dtype, seg, item, t_old, out, nvalid, lane, rn, tile);
+                else channel_step_warp<T, D, false>(P, p.step[pl], p.in_dtype, seg, item, t_old, out, nvalid, lane);
+            } else {
+                if (pl == 0) channel64_decode_warp<T, D, false, true>(f, out, nvalid, lane, tile, brow);
+                else channel64_decode_warp<T, D, false>(f, out, nvalid, lane);
+            }
+        }
+    };
+
+    if (!refuse) {
+        int tb = blockIdx.x, buf = 0;
+        Prefetch64 fa, fb;
+        if (tb < last_items) {
+            load_tile(tb, tiles);
+            if (warp < units) fetch(warp, tb, fa);
+        }
+        for (; tb < last_items; tb += gridDim.x) {
+            cp_async_wait<0>();
+            __syncthreads();                                   // this block's rows are in place; nobody still reads the other buffer
+            const int tb_next = tb + gridDim.x;
+            if (NBUF == 2 && tb_next < last_items) load_tile(tb_next, tiles + (buf ^ 1) * (CD_TILE_BYTES / 4));
+            const float* tile = tiles + buf * (CD_TILE_BYTES / 4);
+#pragma unroll 1
+            for (int u = warp; u < units; u += CD_WARPS) {
+                int nu = u + CD_WARPS, ntb = tb;
+                if (nu >= units) { nu = warp; ntb = tb_next; }
+                const bool more = ntb < last_items;
+                if (more) fetch(nu, ntb, fb);
+                decode(u, tb, fa, tile);
+                fa = fb;
+            }
+            if (NBUF == 1) {
+                __syncthreads();                               // everyone is done with the only buffer
+                if (tb_next < last_items) load_tile(tb_next, tiles);
+            } else {
+                buf ^= 1;
+            }
+        }
+    }
+
     if (p.append && p.state != nullptr) {
         __syncthreads();
         if (threadIdx.x == 0) {

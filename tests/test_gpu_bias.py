@@ -115,6 +115,89 @@ def test_cache_with_key_bias(q):
     assert torch.equal(cache.decode()[1], plain.decode()[1])
 
 
+def _bias_pair(q, S, d, cap, kcfg, vcfg, out_dtype, seed):
+    """Two caches with the same key bias: one handles it inside the decode / step launch, the
+    other with separate element-wise launches (the arrangement the other tests pin to the oracle)."""
+    import torch
+    from pitch_b200 import KVCache
+    rng = np.random.default_rng(seed)
+    cos, sin = rotary_tables(cap, d, base=1000000.0)
+    kb = tuple(torch.from_numpy(a).to(q.device) for a in ((6.0 * rng.standard_normal((S, d))).astype(np.float32), cos, sin))
+    fused = KVCache(S, d, cap, kcfg, vcfg, out_dtype=out_dtype, pitch=q, key_bias=kb)
+    split = KVCache(S, d, cap, kcfg, vcfg, out_dtype=out_dtype, pitch=q, key_bias=kb, fuse_key_bias=False)
+    assert fused._fuse_bias and not split._fuse_bias
+    return fused, split, rng
+
+
+def _same_cache(a, b, what):
+    import torch
+    assert a.tokens == b.tokens
+    for pa, pb in zip(a.planes, b.planes):
+        assert torch.equal(pa.codes, pb.codes), f"{what}: {pa.name} codes at {a.tokens} tokens"
+        assert torch.equal(pa.side.view(torch.int16), pb.side.view(torch.int16)), f"{what}: {pa.name} side information"
+        view = torch.int16 if pa.out.element_size() == 2 else torch.int32
+        diff = pa.out[:, :a.tokens].view(view) != pb.out[:, :b.tokens].view(view)
+        assert not bool(diff.any()), f"{what}: decoded {pa.name} differ at {int(diff.sum())} places, {a.tokens} tokens"
+
+
+@pytest.mark.parametrize("out_dtype,in_dtype", [("bfloat16", "float32"), ("float16", "bfloat16"), ("float32", "float16")])
+@pytest.mark.parametrize("shape", ["turbo64", "turbo128b3", "channel64", "channel128"])
+def test_key_bias_inside_the_launch_equals_separate_passes(q, shape, out_dtype, in_dtype):
+    """README.md:100 of the reference asks for the bias removal inside the kernels: decode and step
+    with the option must give, bit for bit, what decode / append give with the bias handled by
+    separate passes before and after."""
+    import torch
+    from pitch_b200 import ChannelQuantConfig, QuantConfig
+    d, kcfg, vcfg = {"turbo64": (64, QuantConfig("turboQuant", 64, 4), QuantConfig("turboQuant", 64, 4)),
+                     "turbo128b3": (128, QuantConfig("turboQuant", 128, 3), QuantConfig("turboQuant", 128, 3)),
+                     "channel64": (64, ChannelQuantConfig(64, 4, 64), QuantConfig("turboQuant", 64, 4)),
+                     "channel128": (128, ChannelQuantConfig(128, 4, 32), QuantConfig("turboQuant", 128, 3))}[shape]
+    S, T0, steps, cap = 21, 77, 100, 256                     # 42 (segment, plane) pairs: more than the 16 warps of a CTA
+    fused, split, rng = _bias_pair(q, S, d, cap, kcfg, vcfg, out_dtype, 31)
+    tin = getattr(torch, in_dtype)
+    K = torch.from_numpy((rng.standard_normal((S, T0 + steps, d)) * 2 + 5).astype(np.float32)).to(q.device).to(tin)
+    V = torch.from_numpy(rng.standard_normal((S, T0 + steps, d)).astype(np.float32)).to(q.device).to(tin)
+    for c in (fused, split):
+        c.prefill(K[:, :T0].contiguous(), V[:, :T0].contiguous())
+        c.decode()
+    torch.cuda.synchronize()
+    _same_cache(fused, split, shape + " decode")
+    for t in range(T0, T0 + steps):
+        k, v = K[:, t:t + 1].contiguous(), V[:, t:t + 1].contiguous()
+        fused.step(k, v)
+        split.step(k, v)                                     # append (bias taken off a copy) + decode + separate pass
+        if t % 9 == 0 or t > T0 + steps - 3:
+            torch.cuda.synchronize()
+            _same_cache(fused, split, shape + " step")
+    torch.cuda.synchronize()
+    _same_cache(fused, split, shape + " step")
+
+
+def test_key_bias_inside_the_launch_over_many_token_blocks(q):
+    """More token blocks than multiprocessors: every CTA walks several blocks and the table rows of
+    the next block arrive while the current one is decoded."""
+    import torch
+    from pitch_b200 import ChannelQuantConfig, QuantConfig
+    S, d, T = 3, 64, 9000
+    fused, split, rng = _bias_pair(q, S, d, 9216, ChannelQuantConfig(d, 4, 64), QuantConfig("turboQuant", d, 4), "bfloat16", 32)
+    K = torch.from_numpy((rng.standard_normal((S, T + 3, d)) + 4).astype(np.float32)).to(q.device)
+    V = torch.from_numpy(rng.standard_normal((S, T + 3, d)).astype(np.float32)).to(q.device)
+    for c in (fused, split):
+        c.prefill(K[:, :T].contiguous(), V[:, :T].contiguous())
+    for t in range(T, T + 3):
+        fused.step(K[:, t:t + 1].contiguous(), V[:, t:t + 1].contiguous())
+        split.step(K[:, t:t + 1].contiguous(), V[:, t:t + 1].contiguous())
+    torch.cuda.synchronize()
+    _same_cache(fused, split, "many blocks")
+    # float32 output takes the single-buffer arrangement of the table rows
+    f32, s32, rng = _bias_pair(q, 2, d, 9216, QuantConfig("turboQuant", d, 4), QuantConfig("turboQuant", d, 4), "float32", 33)
+    for c in (f32, s32):
+        c.prefill(K[:2, :T].contiguous(), V[:2, :T].contiguous())
+        c.decode()
+    torch.cuda.synchronize()
+    _same_cache(f32, s32, "many blocks, float32")
+
+
 def test_bad_arguments(q):
     import torch
     from pitch_b200.errors import InvalidDimension, InvalidInput
