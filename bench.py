@@ -585,8 +585,13 @@ def _oracle_gate(kind: str, x, codes, scales, dim: int, bits: int, group: int = 
     rel = float(np.max(np.abs(scales.reshape(-1) - ss.reshape(-1)) / np.maximum(np.abs(ss.reshape(-1)), 1e-30)))
     if rel > 1e-5:
         raise SystemExit(f"parity gate failed: scales differ from the specification by {rel}")
-    return {"mismatches_vs_float32_oracle": vs_f32, "ties_vs_float64_spec": ties, "codes_compared": int(diff.size),
-            "scales_max_rel_vs_spec": rel}
+    out = {"mismatches_vs_float32_oracle": vs_f32, "ties_vs_float64_spec": ties, "codes_compared": int(diff.size),
+           "scales_max_rel_vs_spec": rel}
+    if kind == "polarQuant":
+        # the float32 oracle written as the Metal kernel writes it (a division per pair), as a second opinion
+        mc, _ = kernel_f32.encode(kind, x, bits, metal_literal=True)
+        out["mismatches_vs_metal_literal_float32_oracle"] = int((mine != spec_np.unpack_codes(mc.tobytes(), n, dim, bits)).sum())
+    return out
 
 
 def other_configs(q) -> list:

@@ -19,10 +19,14 @@
  *    over GPU lanes.
  *  - 1/sqrt(dim) is the correctly rounded float32 of the exact value (Metal's
  *    rsqrt is approximate).
- *  - PolarQuant encode scales the radius by levels/rmax (one division per
- *    vector) and the angle by bins/(2*pi) (one multiplication, a negative bin
- *    index wrapping around) where PITCHKernels.metal:207-214 divides per pair;
- *    the same real-number formula, two float roundings placed differently.
+ *  - PolarQuant encode exists in two variants.  pitch_oracle_polar_encode scales
+ *    the radius by levels/rmax (one division per vector) and the angle by
+ *    bins/(2*pi) (one multiplication, a negative bin index wrapping around), the
+ *    way a GPU kernel that avoids per-pair divisions does; the same real-number
+ *    formula, two float roundings placed differently.  pitch_oracle_polar_encode_metal
+ *    follows PITCHKernels.metal:207-214 to the letter (r / rmax * levels, theta made
+ *    non-negative, theta / (2*pi) * bins).  Tests report a kernel's code mismatches
+ *    against both, and against the float64 specification.
  *
  * Parity status: PINNED against the reference's golden fixtures within the
  * reference's own float32-vs-float64 tolerances (tests/test_oracle_golden.py):
@@ -175,6 +179,43 @@ void pitch_oracle_polar_encode(const float* in, int64_t count, int dim, int bits
             /* theta in (-pi, pi]: a negative bin index wraps to the bin of theta + 2*pi */
             const float turns = atan2f(b, a) * angle_scale;
             c[2 * p + 1] = (uint32_t)(int32_t)floorf(turns + 0.5f) & (angle_bins - 1u);
+        }
+        pack_vector(c, codes + v * words, dim, bits);
+        scales[v] = rmax;
+    }
+}
+
+/* PITCHKernels.metal:178-222, operation for operation (lines 207-214 for the two codes) */
+void pitch_oracle_polar_encode_metal(const float* in, int64_t count, int dim, int bits, uint32_t seed,
+                                     uint32_t* codes, float* scales) {
+    const int words = words_per_vector(dim, bits);
+    const float rs = rsqrt_dim(dim);
+    const uint32_t radius_levels = (1u << bits) - 1u, angle_bins = 1u << bits;
+    for (int64_t v = 0; v < count; ++v) {
+        float s[PITCH_MAX_DIM], r[PITCH_MAX_DIM / 2];
+        uint32_t c[PITCH_MAX_DIM];
+        for (int i = 0; i < dim; ++i) s[i] = rand_sign(seed, (uint32_t)i) * in[v * dim + i];
+        wht_f32(s, dim);
+        float rmax = 0.0f;
+        for (int p = 0; p < dim / 2; ++p) {
+            const float a = s[2 * p] * rs, b = s[2 * p + 1] * rs;
+            const float aa = a * a, bb = b * b;
+            r[p] = sqrtf(aa + bb);
+            rmax = fmaxf(rmax, r[p]);
+        }
+        const float safe = (rmax > 0.0f) ? rmax : 1.0f;
+        for (int p = 0; p < dim / 2; ++p) {
+            const float a = s[2 * p] * rs, b = s[2 * p + 1] * rs;
+            const float ratio = r[p] / safe;
+            const float scaled = ratio * (float)radius_levels;
+            float q = floorf(scaled + 0.5f);
+            q = fminf(fmaxf(q, 0.0f), (float)radius_levels);
+            c[2 * p] = (uint32_t)q;
+            float theta = atan2f(b, a);
+            if (theta < 0.0f) theta += TWO_PI_F;
+            const float turns = theta / TWO_PI_F;
+            const float bin = turns * (float)angle_bins;
+            c[2 * p + 1] = (uint32_t)floorf(bin + 0.5f) & (angle_bins - 1u);
         }
         pack_vector(c, codes + v * words, dim, bits);
         scales[v] = rmax;

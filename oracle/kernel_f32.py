@@ -41,6 +41,7 @@ def lib():
         L.pitch_oracle_turbo_encode.argtypes = [_f32p, _i64, _int, _int, _u32, _f32p, _u8p, _f32p]
         L.pitch_oracle_turbo_decode.argtypes = [_u8p, _f32p, _i64, _int, _int, _u32, _f32p, _f32p]
         L.pitch_oracle_polar_encode.argtypes = [_f32p, _i64, _int, _int, _u32, _u8p, _f32p]
+        L.pitch_oracle_polar_encode_metal.argtypes = [_f32p, _i64, _int, _int, _u32, _u8p, _f32p]
         L.pitch_oracle_polar_decode.argtypes = [_u8p, _f32p, _i64, _int, _int, _u32, _f32p]
         L.pitch_oracle_channel_encode.argtypes = [_f32p, _i64, _int, _int, _int, _u8p, _u16p]
         L.pitch_oracle_channel_decode.argtypes = [_u8p, _u16p, _i64, _int, _int, _int, _f32p]
@@ -56,14 +57,17 @@ def _book(d, b):
     return np.ascontiguousarray(spec_np.turbo_codebook(d, b).astype(np.float32))
 
 
-def encode(method: str, X, bits: int, seed: int = spec_np.DEFAULT_SEED):
-    """Returns (packed codes uint8 (n*stride,), scales float32 (n,))."""
+def encode(method: str, X, bits: int, seed: int = spec_np.DEFAULT_SEED, metal_literal: bool = False):
+    """Returns (packed codes uint8 (n*stride,), scales float32 (n,)).  ``metal_literal`` selects, for
+    PolarQuant, the variant that follows the Metal kernel's divisions per pair to the letter."""
     X = np.ascontiguousarray(X, dtype=np.float32)
     n, d = X.shape
     codes = np.zeros(n * spec_np.code_stride_bytes(d, bits), dtype=np.uint8)
     scales = np.zeros(n, dtype=np.float32)
     if method == "turboQuant":
         lib().pitch_oracle_turbo_encode(X, n, d, bits, seed & 0xFFFFFFFF, _book(d, bits), codes, scales)
+    elif metal_literal:
+        lib().pitch_oracle_polar_encode_metal(X, n, d, bits, seed & 0xFFFFFFFF, codes, scales)
     else:
         lib().pitch_oracle_polar_encode(X, n, d, bits, seed & 0xFFFFFFFF, codes, scales)
     return codes, scales

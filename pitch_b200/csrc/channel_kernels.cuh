@@ -31,10 +31,20 @@ __device__ __forceinline__ uint32_t quantise(float x, float lo, float step, floa
     return (uint32_t)q;
 }
 
-// The same code from a precomputed correctly rounded reciprocal of the step: the quotient
-// (x - lo) / step as q0 = d * r, q = fma(fma(-step, q0, d), r, q0) -- one Newton correction with an
-// exact remainder, which yields the IEEE quotient (checked against the division on 4e8 random and
-// adversarial pairs, steps with an all-ones significand and quotients next to k + 1/2 included).
+// The same code from a precomputed reciprocal of the step, without a division per element.
+// With rcp = RN(1 / step) (correctly rounded: __frcp_rn), q0 = RN(d * rcp) lies within one ulp of
+// d / step; the remainder rem = d - step * q0 is then exactly representable and fma(-step, q0, d)
+// returns it without error; and q = RN(q0 + rem * rcp) is the correctly rounded quotient RN(d / step),
+// i.e. the very float the division of `quantise` produces.  This is the final correction step of
+// FMA-based division (P. Markstein, "IA-64 and Elementary Functions", ch. 8: a correctly rounded
+// reciprocal, a quotient estimate within one ulp, an exact remainder and one fused correction give
+// the correctly rounded quotient).  Its premises hold here: step is a normal float in
+// [2^-24 / 255, 131008 / 3] (a difference of two finite fp16 values over the number of levels, or 1),
+// so neither rcp nor step * q0 can overflow; the remainder can lose bits to underflow only when
+// |d| < 2^-100, where the quotient is below 2^-70 and the code is 0 whatever its last bits.  The
+// rounding q + 0.5, the floor and the clamp are those of `quantise` (the conversion saturates).
+// Checked in addition against the division on 4e8 random and adversarial pairs (steps with an
+// all-ones significand, quotients next to k + 1/2).
 __device__ __forceinline__ uint32_t quantise_rcp(float x, float lo, float step, float rcp, float levels) {
     const float d = x - lo;
     const float q0 = d * rcp;

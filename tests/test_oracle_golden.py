@@ -115,6 +115,30 @@ def test_f32_oracle_per_vector(which, golden_parity, golden_extra):
     assert mism <= max(4, total // 10000), (mism, total)
 
 
+@pytest.mark.parametrize("which", ["parity", "extra"])
+def test_f32_oracle_metal_literal_polar_variant(which, golden_parity, golden_extra):
+    """The PolarQuant encoder written as the Metal kernel writes it (a division per pair,
+    PITCHKernels.metal:207-214) meets the reference's float32-vs-float64 tolerance on the golden
+    vectors, and differs from the division-free variant on a handful of codes only."""
+    g = golden_parity if which == "parity" else golden_extra
+    total = mism = between = 0
+    for c in _vector_cases(g):
+        if c["method"] != "polarQuant":
+            continue
+        X = g[f"input/{c['group']}"]
+        n, d = X.shape
+        k, b = c["key"], c["bits"]
+        codes, scales = kernel_f32.encode("polarQuant", X, b, c["seed"], metal_literal=True)
+        other, other_scales = kernel_f32.encode("polarQuant", X, b, c["seed"])
+        assert scales.tobytes() == other_scales.tobytes(), k
+        diff = _unpack(codes, n, d, b) != _unpack(g[f"{k}/codes"], n, d, b)
+        assert diff.sum() <= max(2, diff.size // 500), (k, int(diff.sum()))        # ParityTests.swift:67
+        total += diff.size
+        mism += int(diff.sum())
+        between += int((_unpack(codes, n, d, b) != _unpack(other, n, d, b)).sum())
+    assert total > 0 and mism <= max(4, total // 10000) and between <= max(4, total // 10000), (mism, between, total)
+
+
 @pytest.mark.parametrize("which", ["channel", "extra"])
 def test_f32_oracle_per_channel_is_bit_exact(which, golden_channel, golden_extra):
     g = golden_channel if which == "channel" else golden_extra
