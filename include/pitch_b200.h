@@ -287,6 +287,12 @@ int pitch_enqueue_cache_append_noalloc(const pitch_cache_desc* desc, const pitch
  *   next stream-ordered call.
  * Results agree with attention over the decoded float32 cache to about 1e-5 relative L2 (float32
  * accumulation in a different order, base-2 exponentials). */
+typedef enum pitch_attention_precision {
+    PITCH_ATTENTION_F32 = 0,   /* operands split into bf16 parts so that products are float32-accurate (about 1e-5) */
+    PITCH_ATTENTION_BF16 = 1   /* operands as a bf16 pipeline has them: as accurate as attention over the cache
+                                  decoded to bf16 (about 2e-3), half the tensor-core products and table look-ups */
+} pitch_attention_precision;
+
 typedef struct pitch_attention_args {
     const void* queries;
     void* out;
@@ -294,6 +300,8 @@ typedef struct pitch_attention_args {
     int64_t workspace_bytes;
     int32_t n_queries;
     float scale;               /* softmax scale, usually 1/sqrt(dim) */
+    int32_t precision;         /* pitch_attention_precision */
+    int32_t reserved;          /* 0 */
 } pitch_attention_args;
 int64_t pitch_cache_attention_workspace(const pitch_cache_desc* desc, int n_queries);
 int pitch_enqueue_cache_attention(const pitch_cache_desc* desc, const pitch_attention_args* args, void* stream);

@@ -62,7 +62,7 @@ class CacheState(Structure):
 class AttentionArgs(Structure):
     """``pitch_attention_args``."""
     _fields_ = [("queries", c_void_p), ("out", c_void_p), ("workspace", c_void_p), ("workspace_bytes", c_int64),
-                ("n_queries", c_int32), ("scale", c_float)]
+                ("n_queries", c_int32), ("scale", c_float), ("precision", c_int32), ("reserved", c_int32)]
 
 
 # name -> (restype, argtypes); every symbol include/pitch_b200.h declares

@@ -304,7 +304,15 @@ def bench_attention(q, reps, segments=48, tokens=32768, n_queries=7):
     extra = {"dim": d, "segments": segments, "tokens": tokens, "n_queries": n_queries, "l2": "flushed before every launch",
              "tokens_per_s": round(segments * tokens / t, 1)}
     yield row("cfg4 attention", "attention from the compressed cache", t, segments * tokens, "kv_tokens", stored,
-              {**extra, "parity": {"max_rel_l2_vs_float64_attention_over_decoded_cache": worst}})
+              {**extra, "precision": "float32", "parity": {"max_rel_l2_vs_float64_attention_over_decoded_cache": worst}})
+    got16 = cache.attend(qs[0], precision="bfloat16")
+    worst16 = float(((got16.double() - got.double()).norm(dim=2) / got.double().norm(dim=2)).max())
+    if worst16 > 5e-3:
+        raise SystemExit(f"parity gate failed: bf16-operand cache attention differs from the float32-accurate one by {worst16}")
+    t16 = timed(lambda i: cache.attend(qs[i % 4], out=out, precision="bfloat16"))
+    yield row("cfg4 attention", "attention from the compressed cache, bf16 operands", t16, segments * tokens, "kv_tokens", stored,
+              {**extra, "precision": "bfloat16", "tokens_per_s": round(segments * tokens / t16, 1),
+               "parity": {"max_rel_l2_vs_float32_accurate_mode": worst16}})
 
     def two_step(i):
         ko, vo = cache.decode()

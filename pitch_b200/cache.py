@@ -98,6 +98,8 @@ class KVCache:
                     raise InvalidInput(f"key_bias {name} must be a contiguous float32 CUDA tensor with {self.dim} columns")
             self.key_bias = (bias, cos_table, sin_table)
             self._fuse_bias = bool(fuse_key_bias) and self._fused
+            self._rope = _native.RopeBias(bias.data_ptr(), self.dim * 4, cos_table.data_ptr(), sin_table.data_ptr(),
+                                          int(cos_table.shape[0]))
         codebooks.register_all()
 
     def _make_plane(self, name: str, cfg) -> _Plane:
@@ -161,10 +163,7 @@ class KVCache:
             self._lib = _native.lib()
             # twin descriptor with the key-bias tables
             b = _native.CacheDesc.from_buffer_copy(d)
-            if self.key_bias is not None:
-                bias, cos_table, sin_table = self.key_bias
-                self._rope = _native.RopeBias(bias.data_ptr(), self.dim * 4, cos_table.data_ptr(), sin_table.data_ptr(),
-                                              int(cos_table.shape[0]))
+            if self._rope is not None:
                 b.key_bias = ctypes.pointer(self._rope)
             self._desc_bias = b
             self._desc_bias_ref = ctypes.byref(b)
@@ -395,14 +394,17 @@ class KVCache:
                                          subtract=False, stream=stream)
         return tuple(pl.out[:, :self.tokens] for pl in self.planes)
 
-    def attend(self, queries, scale: float | None = None, out=None, stream=None):
+    def attend(self, queries, scale: float | None = None, out=None, stream=None, precision: str = "float32"):
         """Single-token attention over the compressed cache without decoding it to memory:
         ``queries`` is float32 ``[segments, n_queries, dim]`` (``n_queries`` <= 8: the query
         heads that share a KV head); returns float32 ``[segments, n_queries, dim]`` with
         ``softmax_t(scale * q . K_t) . V_t`` over the ``tokens`` tokens held.  ``scale`` defaults
         to ``1/sqrt(dim)``.  Supported: dim 64, per-channel 4-bit keys (group size a multiple of
-        32), TurboQuant 4-bit values.  Stream-ordered; the scratch buffer is kept by the cache and
-        reused, so calls on one cache must be stream-ordered with respect to each other."""
+        32), TurboQuant 4-bit values.  ``precision="float32"`` keeps products float32-accurate
+        (about 1e-5 against attention over the float32-decoded cache); ``"bfloat16"`` uses operands
+        as a bf16 pipeline has them (as accurate as attention over the cache decoded to bf16, about
+        2e-3) at half the tensor-core work.  Stream-ordered; the scratch buffer is kept by the
+        cache and reused, so calls on one cache must be stream-ordered with respect to each other."""
         torch = _torch()
         if self.tokens < 1:
             raise InvalidInput("the cache is empty")
@@ -427,8 +429,11 @@ class KVCache:
         if ws is None or ws.numel() < need:
             ws = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=self.device)
             self._attention_ws = ws
+        if precision not in ("float32", "bfloat16"):
+            raise InvalidInput(f"precision {precision!r} must be 'float32' or 'bfloat16'")
         args = _native.AttentionArgs(queries.data_ptr(), out.data_ptr(), ws.data_ptr(), ws.numel(), n_q,
-                                     float(scale) if scale is not None else self.dim ** -0.5)
+                                     float(scale) if scale is not None else self.dim ** -0.5,
+                                     1 if precision == "bfloat16" else 0, 0)
         st = self._lib.pitch_enqueue_cache_attention(self._desc_ref, ctypes.byref(args), stream_handle(stream, self.device))
         if st:
             _native.check(st)

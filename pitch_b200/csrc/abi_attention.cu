@@ -77,6 +77,8 @@ int pitch_enqueue_cache_attention(const pitch_cache_desc* d, const pitch_attenti
     int st;
     if ((st = check_attention_shape(d, a->n_queries))) return st;
     if (!(a->scale > 0.0f) || !std::isfinite(a->scale)) return fail(PITCH_ERR_INVALID_INPUT, "scale must be positive and finite");
+    if (a->precision != PITCH_ATTENTION_F32 && a->precision != PITCH_ATTENTION_BF16)
+        return fail(PITCH_ERR_INVALID_INPUT, "unknown attention precision %d", a->precision);
     if (!a->queries || !a->out || !a->workspace) return fail(PITCH_ERR_INVALID_INPUT, "queries, out or workspace is null");
     if (!aligned16(a->queries) || !aligned16(a->out) || !aligned16(a->workspace))
         return fail(PITCH_ERR_INVALID_INPUT, "queries, out and workspace must be 16-byte aligned");
@@ -132,7 +134,8 @@ int pitch_enqueue_cache_attention(const pitch_cache_desc* d, const pitch_attenti
     {
         static std::atomic<bool> configured[64];
         if (dev >= 0 && dev < 64 && !configured[dev].load(std::memory_order_acquire)) {
-            if (cudaFuncSetAttribute(attention_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES) != cudaSuccess)
+            if (cudaFuncSetAttribute(attention_partial_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES) != cudaSuccess ||
+                cudaFuncSetAttribute(attention_partial_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES) != cudaSuccess)
                 return launch_status(false, "cache_attention (shared memory opt-in)");
             configured[dev].store(true, std::memory_order_release);
         }
@@ -152,7 +155,8 @@ int pitch_enqueue_cache_attention(const pitch_cache_desc* d, const pitch_attenti
         cfg.stream = s;
         cfg.attrs = pdl;
         cfg.numAttrs = 1;
-        cudaLaunchKernelEx(&cfg, attention_partial_kernel, p);
+        if (a->precision == PITCH_ATTENTION_BF16) cudaLaunchKernelEx(&cfg, attention_partial_kernel<true>, p);
+        else cudaLaunchKernelEx(&cfg, attention_partial_kernel<false>, p);
         if ((st = launch_status(false, "cache_attention"))) return st;
         cfg.gridDim = dim3((unsigned)p.n_queries, (unsigned)p.segments);
         cfg.blockDim = dim3(32 * AT_COMBINE_WARPS);

@@ -149,6 +149,10 @@ struct AttnState {
 // One tile: scores, online softmax, value accumulation.  kb / vb / nb: this lane's places in the
 // tile buffer (key row g words 2t, 2t+1; value row 2t word g; norm g); qf: its folded-query fragments
 // in shared memory (stride 32 entries); bias0/1: score offsets of queries 2t and 2t + 1.
+// FAST: operands as a bf16 pipeline would have them - the folded query in two bf16 parts instead of
+// three, weights and centroids in one instead of two - which halves the tensor-core products and the
+// table look-ups; the result is then as accurate as attention over the cache decoded to bf16.
+template <bool FAST>
 __device__ __forceinline__ void attn_tile(const unsigned char* kb, const unsigned char* vb, const unsigned char* nb,
                                           AttnState& st, const uint2* qf,
                                           float bias0, float bias1, int nvalid, const unsigned char* table,
@@ -169,14 +173,16 @@ __device__ __forceinline__ void attn_tile(const unsigned char* kb, const unsigne
     }
 #define PITCH_QK(KB)                                                                                 \
     {                                                                                                \
-        const uint2 qh = qf[(0 * 4 + KB) * 32], qm = qf[(1 * 4 + KB) * 32], ql = qf[(2 * 4 + KB) * 32]; \
+        const uint2 qh = qf[(0 * 4 + KB) * 32], qm = qf[(1 * 4 + KB) * 32];                          \
+        uint2 ql = make_uint2(0, 0);                                                                 \
+        if (!FAST) ql = qf[(2 * 4 + KB) * 32];                                                       \
         _Pragma("unroll")                                                                            \
         for (int m = 0; m < 2; ++m) {                                                                \
             const uint32_t a0 = key_pair<KB>(kc[m][0].x), a1 = key_pair<KB>(kc[m][1].x);             \
             const uint32_t a2 = key_pair<KB>(kc[m][0].y), a3 = key_pair<KB>(kc[m][1].y);             \
             mma_bf16(sc[m], a0, a1, a2, a3, qh.x, qh.y);                                             \
             mma_bf16(sm[m], a0, a1, a2, a3, qm.x, qm.y);                                             \
-            mma_bf16(sl[m], a0, a1, a2, a3, ql.x, ql.y);                                             \
+            if (!FAST) mma_bf16(sl[m], a0, a1, a2, a3, ql.x, ql.y);                                  \
         }                                                                                            \
     }
     PITCH_QK(0) PITCH_QK(1) PITCH_QK(2) PITCH_QK(3)
@@ -184,7 +190,7 @@ __device__ __forceinline__ void attn_tile(const unsigned char* kb, const unsigne
 #pragma unroll
     for (int m = 0; m < 2; ++m)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) sc[m][i] += sm[m][i] + sl[m][i];
+        for (int i = 0; i < 4; ++i) sc[m][i] += FAST ? sm[m][i] : sm[m][i] + sl[m][i];
     if (nvalid < 32) {
 #pragma unroll
         for (int m = 0; m < 2; ++m) {
@@ -215,11 +221,16 @@ __device__ __forceinline__ void attn_tile(const unsigned char* kb, const unsigne
         for (int h = 0; h < 2; ++h) {
             const float p0 = fast_exp2(sc[m][2 * h] - st.m0), p1 = fast_exp2(sc[m][2 * h + 1] - st.m1);
             st.l0 += p0; st.l1 += p1;
-            uint32_t hi, lo;
             const float norm = *reinterpret_cast<const float*>(nb + (16 * m + 8 * h) * 4);
-            split_pair(p0 * norm, p1 * norm, hi, lo);
-            wh[m][h] = transpose8x8(hi);
-            wl[m][h] = transpose8x8(lo);
+            if (FAST) {
+                wh[m][h] = transpose8x8(bf16_pair(p0 * norm, p1 * norm));
+                wl[m][h] = 0;
+            } else {
+                uint32_t hi, lo;
+                split_pair(p0 * norm, p1 * norm, hi, lo);
+                wh[m][h] = transpose8x8(hi);
+                wl[m][h] = transpose8x8(lo);
+            }
         }
     }
     // ---- out^T += centroids^T . weights^T
@@ -241,17 +252,25 @@ __device__ __forceinline__ void attn_tile(const unsigned char* kb, const unsigne
             const unsigned char* e1 = table + __byte_perm(oa, slot, 0x5504 | (mb << 4));
             const unsigned char* e2 = table + __byte_perm(eb, slot, 0x5504 | (mb << 4));
             const unsigned char* e3 = table + __byte_perm(ob, slot, 0x5504 | (mb << 4));
-            ch[mb][0] = *reinterpret_cast<const uint32_t*>(e0); cl[mb][0] = *reinterpret_cast<const uint32_t*>(e0 + 128);
-            ch[mb][1] = *reinterpret_cast<const uint32_t*>(e1); cl[mb][1] = *reinterpret_cast<const uint32_t*>(e1 + 128);
-            ch[mb][2] = *reinterpret_cast<const uint32_t*>(e2); cl[mb][2] = *reinterpret_cast<const uint32_t*>(e2 + 128);
-            ch[mb][3] = *reinterpret_cast<const uint32_t*>(e3); cl[mb][3] = *reinterpret_cast<const uint32_t*>(e3 + 128);
+            ch[mb][0] = *reinterpret_cast<const uint32_t*>(e0);
+            ch[mb][1] = *reinterpret_cast<const uint32_t*>(e1);
+            ch[mb][2] = *reinterpret_cast<const uint32_t*>(e2);
+            ch[mb][3] = *reinterpret_cast<const uint32_t*>(e3);
+            if (!FAST) {
+                cl[mb][0] = *reinterpret_cast<const uint32_t*>(e0 + 128);
+                cl[mb][1] = *reinterpret_cast<const uint32_t*>(e1 + 128);
+                cl[mb][2] = *reinterpret_cast<const uint32_t*>(e2 + 128);
+                cl[mb][3] = *reinterpret_cast<const uint32_t*>(e3 + 128);
+            }
         }
 #pragma unroll
         for (int mb = 0; mb < 4; ++mb) mma_bf16(st.acc[mb], ch[mb][0], ch[mb][1], ch[mb][2], ch[mb][3], wh[m][0], wh[m][1]);
+        if (!FAST) {
 #pragma unroll
-        for (int mb = 0; mb < 4; ++mb) mma_bf16(st.acc[mb], ch[mb][0], ch[mb][1], ch[mb][2], ch[mb][3], wl[m][0], wl[m][1]);
+            for (int mb = 0; mb < 4; ++mb) mma_bf16(st.acc[mb], ch[mb][0], ch[mb][1], ch[mb][2], ch[mb][3], wl[m][0], wl[m][1]);
 #pragma unroll
-        for (int mb = 0; mb < 4; ++mb) mma_bf16(st.acc[mb], cl[mb][0], cl[mb][1], cl[mb][2], cl[mb][3], wh[m][0], wh[m][1]);
+            for (int mb = 0; mb < 4; ++mb) mma_bf16(st.acc[mb], cl[mb][0], cl[mb][1], cl[mb][2], cl[mb][3], wh[m][0], wh[m][1]);
+        }
     }
 }
 
@@ -300,6 +319,7 @@ __device__ __forceinline__ void fold_group(uint32_t lo2, uint32_t hi2, const flo
     bias1 = __shfl_sync(0xFFFFFFFFu, b, 8 * t + 4);       // of query 2t + 1
 }
 
+template <bool FAST>
 __global__ void __launch_bounds__(AT_THREADS, 1)
 attention_partial_kernel(const __grid_constant__ AttentionParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -395,7 +415,7 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
                     hi2 = ldg_stream32(reinterpret_cast<const uint32_t*>(k_ranges + (int64_t)(group + 1) * 128 + 64)); \
                 }                                                                                       \
             }                                                                                           \
-            attn_tile(kb + BUF * AT_STAGE_BYTES, vb + BUF * AT_STAGE_BYTES, nb + BUF * AT_STAGE_BYTES, st, qf + lane,  \
+            attn_tile<FAST>(kb + BUF * AT_STAGE_BYTES, vb + BUF * AT_STAGE_BYTES, nb + BUF * AT_STAGE_BYTES, st, qf + lane,  \
                       bias0, bias1, nvalid, table, slot, g);                                            \
             __syncwarp();                                             /* this buffer is refilled two tiles on */ \
         }

@@ -76,6 +76,32 @@ def test_matches_attention_over_spec_decoded_cache(q, S, T, R, G, scale):
         assert rows_rel_l2(got[s], ref) < TOL, (s, rows_rel_l2(got[s], ref))
 
 
+@pytest.mark.parametrize("S,T,R,G", [(3, 333, 7, 64), (2, 9000, 5, 64), (1, 31, 8, 64), (2, 2048 + 17, 4, 128)])
+def test_bf16_operand_mode_is_as_accurate_as_attention_over_the_bf16_cache(q, S, T, R, G):
+    """``precision="bfloat16"``: operands as a bf16 pipeline has them.  Its error against float64
+    attention over the specification-decoded cache must stay within a few bf16 roundings, and must
+    not exceed (by more than a small factor) the error of what it replaces: torch attention over
+    the cache decoded to bf16."""
+    import torch
+    cache, rng = build_cache(q, S, T, G, seed=300 + T)
+    Q = rng.standard_normal((S, R, 64)).astype(np.float32)
+    Qd = torch.from_numpy(Q).to(q.device)
+    fast = cache.attend(Qd, precision="bfloat16").cpu().numpy().astype(np.float64)
+    exact = cache.attend(Qd).cpu().numpy().astype(np.float64)
+    ko, vo = cache.decode()
+    sdpa = torch.nn.functional.scaled_dot_product_attention(Qd.bfloat16().unsqueeze(0), ko.bfloat16().unsqueeze(0),
+                                                            vo.bfloat16().unsqueeze(0))[0].float().cpu().numpy().astype(np.float64)
+    for s in range(S):
+        K, V = spec_decoded(cache, s)
+        ref = attention64(Q[s].astype(np.float64), K, V, 64 ** -0.5)
+        e_fast, e_exact, e_sdpa = rows_rel_l2(fast[s], ref), rows_rel_l2(exact[s], ref), rows_rel_l2(sdpa[s], ref)
+        assert e_exact < TOL
+        assert e_fast < 4e-3, (s, e_fast)
+        assert e_fast < 1.5 * e_sdpa + 1e-3, (s, e_fast, e_sdpa)
+    with pytest.raises(Exception):
+        cache.attend(Qd, precision="float8")
+
+
 def test_grows_with_the_cache(q):
     """Attention after every append of a growing cache (partial groups, tiles and slices)."""
     import torch
