@@ -89,6 +89,7 @@ class KVCache:
         self.key_bias = None
         self._fused = self._fused_ok()
         self._fuse_bias = False
+        self._rope = None
         if key_bias is not None:
             bias, cos_table, sin_table = key_bias
             if tuple(bias.shape) != (self.segments, self.dim) or cos_table.shape[0] < self.capacity:

@@ -954,7 +954,9 @@ cache_decode_bias_kernel(const __grid_constant__ Cache64Params p) {
                 full_items = first < full_items ? first : full_items;
             }
     }
-    const int units = p.segments * p.n_planes;               // (segment, plane) pairs, all at the CTA's token block
+    // (plane, segment) pairs, all at the CTA's token block; plane-major, so that the 16 warps of a CTA,
+    // which take every 16th unit, each get their share of the costlier biased plane
+    const int units = p.segments * p.n_planes;
 
     // cos and sin rows of token block tb -> shared memory (16-byte asynchronous copies, swizzled chunks)
     auto load_tile = [&](int tb, float* dst) {
@@ -973,7 +975,7 @@ cache_decode_bias_kernel(const __grid_constant__ Cache64Params p) {
 
     // one (segment, plane) of token block `item`: prefetch ...
     auto fetch = [&](int u, int item, Prefetch64& f) {
-        const int seg = u / p.n_planes, pl = u - seg * p.n_planes;
+        const int pl = u / p.segments, seg = u - pl * p.segments;
         const Plane64& P = p.plane[pl];
         const unsigned char* side = P.side + seg * P.side_seg_stride;
         const bool whole = item < full_items;
@@ -994,7 +996,7 @@ cache_decode_bias_kernel(const __grid_constant__ Cache64Params p) {
     };
     // ... and decode (with the append work where the item is touched by it)
     auto decode = [&](int u, int item, Prefetch64& f, const float* tile) {
-        const int seg = u / p.n_planes, pl = u - seg * p.n_planes;
+        const int pl = u / p.segments, seg = u - pl * p.segments;
         const Plane64& P = p.plane[pl];
         const bool whole = item < full_items;
         const int64_t left = total - (int64_t)item * TOKENS;
