@@ -94,27 +94,30 @@ __device__ __forceinline__ void append_vector_cta(const T* __restrict__ x_in, ui
             }
         }
     } else {
-        float a = 0.0f, c = 0.0f, r = 0.0f;
+        // same operations as polar_encode_kernel: approximate square root per pair, one correctly
+        // rounded square root of the largest squared radius for the scale
+        float a = 0.0f, c = 0.0f, r = 0.0f, r2 = 0.0f;
         if (active) {
             a = s[tid & ~1] * rs;
             c = s[(tid & ~1) + 1] * rs;
             const float aa = a * a, cc = c * c;
-            r = sqrtf(aa + cc);
+            r2 = aa + cc;
+            asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(r2));
         }
-        float m = r;
+        float m = r2;
         for (int k = 16; k > 0; k >>= 1) m = fmaxf(m, __shfl_xor_sync(FULL, m, k));
         if ((tid & 31) == 0) s_red[tid >> 5] = m;
         __syncthreads();
-        float rmax = 0.0f;
-        for (int k = 0; k < (int)((blockDim.x + 31) >> 5); ++k) rmax = fmaxf(rmax, s_red[k]);
+        float rmax2 = 0.0f;
+        for (int k = 0; k < (int)((blockDim.x + 31) >> 5); ++k) rmax2 = fmaxf(rmax2, s_red[k]);
+        const float rmax = sqrtf(rmax2);
         const float safe = rmax > 0.0f ? rmax : 1.0f;
-        const float RL = (float)((1u << bits) - 1u);
-        const float radius_scale = RL / safe;
+        const int RL = (1 << bits) - 1;
+        const float radius_scale = (float)RL / safe;
         if (active) {
             if ((tid & 1) == 0) {
-                float q = floorf(r * radius_scale + 0.5f);
-                q = fminf(fmaxf(q, 0.0f), RL);
-                code = (uint32_t)q;
+                const int q = __float2int_rd(r * radius_scale + 0.5f);
+                code = (uint32_t)min(q, RL);
             } else {
                 code = angle_bin(a, c, bits);
             }

@@ -426,20 +426,27 @@ polar_encode_kernel(const T* __restrict__ in, uint32_t* __restrict__ codes, floa
     wht_regs(x, g.e());
     wht_lanes(x, g.tpv, lane);
 
+    // Radii.  The scale of the vector is the largest pair radius: sqrt is monotone and correctly
+    // rounded, so sqrt(max r^2) is exactly max sqrt(r^2) and only ONE correctly rounded square root
+    // is needed per vector.  The radius of each pair, which is only ever compared with the
+    // quantiser's steps, comes from the hardware's approximate square root (within an ulp of the
+    // exact one): its code can differ from the exactly rounded radius's only when r * scale + 1/2
+    // lies within rounding distance of an integer - the boundary ties the parity tests count.
     float r[16];
-    float rmax = 0.0f;
+    float rmax2 = 0.0f;
 #pragma unroll
     for (int p = 0; p < 16; ++p) {
         x[2 * p] = x[2 * p] * rs;
         x[2 * p + 1] = x[2 * p + 1] * rs;
         const float aa = x[2 * p] * x[2 * p], cc = x[2 * p + 1] * x[2 * p + 1];
-        r[p] = sqrtf(aa + cc);
-        if (2 * p < g.e()) rmax = fmaxf(rmax, r[p]);
+        const float r2 = aa + cc;
+        asm("sqrt.approx.f32 %0, %1;" : "=f"(r[p]) : "f"(r2));
+        if (2 * p < g.e()) rmax2 = fmaxf(rmax2, r2);
     }
-    rmax = lanes_max(rmax, g.tpv);
+    const float rmax = sqrtf(lanes_max(rmax2, g.tpv));
     const float safe = rmax > 0.0f ? rmax : 1.0f;
-    constexpr float RL = (float)((1 << BITS) - 1);
-    const float radius_scale = RL / safe;                                 // one division per vector
+    constexpr int RL = (1 << BITS) - 1;
+    const float radius_scale = (float)RL / safe;                          // one division per vector
 
     uint32_t w[BITS];
 #pragma unroll
@@ -447,9 +454,10 @@ polar_encode_kernel(const T* __restrict__ in, uint32_t* __restrict__ codes, floa
 #pragma unroll
     for (int p = 0; p < 16; ++p) {
         if (2 * p < g.e()) {
-            float q = floorf(r[p] * radius_scale + 0.5f);
-            q = fminf(fmaxf(q, 0.0f), RL);
-            insert_code<BITS>(w, 2 * p, (uint32_t)q);
+            // floor(r * scale + 1/2), never negative; r <= rmax * (1 + 2^-22) keeps it at most RL, the
+            // minimum only guards the packing against non-finite input
+            const int q = __float2int_rd(r[p] * radius_scale + 0.5f);
+            insert_code<BITS>(w, 2 * p, (uint32_t)min(q, RL));
             insert_code<BITS>(w, 2 * p + 1, angle_bin(x[2 * p], x[2 * p + 1], BITS));
         }
     }
