@@ -290,7 +290,7 @@ int pitch_enqueue_cache_append_noalloc(const pitch_cache_desc* desc, const pitch
 typedef enum pitch_attention_precision {
     PITCH_ATTENTION_F32 = 0,   /* operands split into bf16 parts so that products are float32-accurate (about 1e-5) */
     PITCH_ATTENTION_BF16 = 1   /* operands as a bf16 pipeline has them: as accurate as attention over the cache
-                                  decoded to bf16 (about 2e-3), half the tensor-core products and table look-ups */
+                                  decoded to bf16 (a few bf16 roundings: up to about 5e-3), half the tensor-core products and table look-ups */
 } pitch_attention_precision;
 
 typedef struct pitch_attention_args {

@@ -403,8 +403,8 @@ class KVCache:
         to ``1/sqrt(dim)``.  Supported: dim 64, per-channel 4-bit keys (group size a multiple of
         32), TurboQuant 4-bit values.  ``precision="float32"`` keeps products float32-accurate
         (about 1e-5 against attention over the float32-decoded cache); ``"bfloat16"`` uses operands
-        as a bf16 pipeline has them (as accurate as attention over the cache decoded to bf16, about
-        2e-3) at half the tensor-core work.  Stream-ordered; the scratch buffer is kept by the
+        as a bf16 pipeline has them (as accurate as attention over the cache decoded to bf16: a few
+        bf16 roundings, up to about 5e-3) at half the tensor-core work.  Stream-ordered; the scratch buffer is kept by the
         cache and reused, so calls on one cache must be stream-ordered with respect to each other."""
         torch = _torch()
         if self.tokens < 1:

@@ -220,8 +220,18 @@ __device__ __forceinline__ void add_bias_block(float (&x)[N], const float* tile,
         c[4 * h] = c4.x; c[4 * h + 1] = c4.y; c[4 * h + 2] = c4.z; c[4 * h + 3] = c4.w;
         s[4 * h] = s4.x; s[4 * h + 1] = s4.y; s[4 * h + 2] = s4.z; s[4 * h + 3] = s4.w;
     }
+    // two coordinates at a time on the packed pipe: both products packed, their sum with scalar adds (a
+    // packed add fed only by a packed multiply would be fused into one operation by the assembler and
+    // lose a rounding), the final add packed again.  Same roundings as rotated_bias_at.
 #pragma unroll
-    for (int i = 0; i < N; ++i) x[i] = __fadd_rn(x[i], rotated_bias_at(b[i], rh[i], c[i], s[i]));
+    for (int i = 0; i < N; i += 2) {
+        const float2 pc = __fmul2_rn(make_float2(b[i], b[i + 1]), make_float2(c[i], c[i + 1]));
+        const float2 ps = __fmul2_rn(make_float2(rh[i], rh[i + 1]), make_float2(s[i], s[i + 1]));
+        const float2 rb = make_float2(__fadd_rn(pc.x, ps.x), __fadd_rn(pc.y, ps.y));
+        const float2 y = __fadd2_rn(make_float2(x[i], x[i + 1]), rb);
+        x[i] = y.x;
+        x[i + 1] = y.y;
+    }
 }
 
 // 64 coordinates per lane (BITS-bit codes): a whole vector at D = 64, half of one at D = 128.

@@ -79,7 +79,7 @@ def test_matches_attention_over_spec_decoded_cache(q, S, T, R, G, scale):
 @pytest.mark.parametrize("S,T,R,G", [(3, 333, 7, 64), (2, 9000, 5, 64), (1, 31, 8, 64), (2, 2048 + 17, 4, 128)])
 def test_bf16_operand_mode_is_as_accurate_as_attention_over_the_bf16_cache(q, S, T, R, G):
     """``precision="bfloat16"``: operands as a bf16 pipeline has them.  Its error against float64
-    attention over the specification-decoded cache must stay within a few bf16 roundings, and must
+    attention over the specification-decoded cache must stay within a few bf16 roundings (8e-3), and must
     not exceed (by more than a small factor) the error of what it replaces: torch attention over
     the cache decoded to bf16."""
     import torch
@@ -96,7 +96,7 @@ def test_bf16_operand_mode_is_as_accurate_as_attention_over_the_bf16_cache(q, S,
         ref = attention64(Q[s].astype(np.float64), K, V, 64 ** -0.5)
         e_fast, e_exact, e_sdpa = rows_rel_l2(fast[s], ref), rows_rel_l2(exact[s], ref), rows_rel_l2(sdpa[s], ref)
         assert e_exact < TOL
-        assert e_fast < 4e-3, (s, e_fast)
+        assert e_fast < 8e-3, (s, e_fast)
         assert e_fast < 1.5 * e_sdpa + 1e-3, (s, e_fast, e_sdpa)
     with pytest.raises(Exception):
         cache.attend(Qd, precision="float8")
