@@ -310,7 +310,8 @@ class StepTimer:
         saved = [t.clone() for t in state]
         graph = torch.cuda.CUDAGraph()
         nbytes = 0
-        with torch.cuda.graph(graph):
+        # thread-local capture: other threads of the process (the process group's watchdog) stay free to query events
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
             for i in range(steps):
                 c.step(self.new_k[warmup + i], self.new_v[warmup + i])
                 nbytes += sum(step_bytes(c.segments, c.tokens))

@@ -312,7 +312,7 @@ class KVCache:
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
         held = self.tokens
-        with torch.cuda.graph(graph):
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
             self.step(keys, values)
         self.tokens = held                       # capturing queues nothing
         return graph
