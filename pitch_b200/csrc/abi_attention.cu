@@ -58,8 +58,11 @@ static int check_attention_shape(const pitch_cache_desc* d, int n_queries) {
         return fail(PITCH_ERR_INVALID_INPUT, "cache attention needs dim 64 and two planes (keys, values)");
     const pitch_plane& k = d->planes[0];
     const pitch_plane& v = d->planes[1];
-    if (k.kind != PITCH_PLANE_CHANNEL || k.bits != 4 || k.group_size < 32 || k.group_size % 32 != 0 || k.group_size > PITCH_MAX_GROUP)
-        return fail(PITCH_ERR_INVALID_INPUT, "cache attention needs per-channel 4-bit keys with a group size that is a multiple of 32");
+    if (k.kind == PITCH_PLANE_TURBO) {
+        if (k.bits != 4) return fail(PITCH_ERR_INVALID_INPUT, "cache attention needs 4-bit keys");
+    } else if (k.kind != PITCH_PLANE_CHANNEL || k.bits != 4 || k.group_size < 32 || k.group_size % 32 != 0 || k.group_size > PITCH_MAX_GROUP) {
+        return fail(PITCH_ERR_INVALID_INPUT, "cache attention needs TurboQuant 4-bit keys, or per-channel 4-bit keys with a group size that is a multiple of 32");
+    }
     if (v.kind != PITCH_PLANE_TURBO || v.bits != 4)
         return fail(PITCH_ERR_INVALID_INPUT, "cache attention needs TurboQuant 4-bit values");
     return PITCH_OK;
@@ -114,7 +117,10 @@ int pitch_enqueue_cache_attention(const pitch_cache_desc* d, const pitch_attenti
     attention_slices(sm_count(), d->segments, d->tokens, &p.splits, &p.tokens_per_split);
     if ((int64_t)p.segments * p.splits > 0x7FFFFFFF) return fail(PITCH_ERR_INVALID_INPUT, "segments x runs exceeds 2^31 - 1");
     p.n_queries = a->n_queries;
-    p.group_size = d->planes[0].group_size;
+    const bool turbo_keys = d->planes[0].kind == PITCH_PLANE_TURBO;
+    p.group_size = turbo_keys ? 32 : d->planes[0].group_size;
+    p.kneg_lo = negate_mask32(d->planes[0].seed, 0);
+    p.kneg_hi = negate_mask32(d->planes[0].seed, 32);
     p.scale_log2 = (float)((double)a->scale * 1.4426950408889634);
     p.neg_lo = negate_mask32(d->planes[1].seed, 0);
     p.neg_hi = negate_mask32(d->planes[1].seed, 32);
@@ -134,8 +140,10 @@ int pitch_enqueue_cache_attention(const pitch_cache_desc* d, const pitch_attenti
     {
         static std::atomic<bool> configured[64];
         if (dev >= 0 && dev < 64 && !configured[dev].load(std::memory_order_acquire)) {
-            if (cudaFuncSetAttribute(attention_partial_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES) != cudaSuccess ||
-                cudaFuncSetAttribute(attention_partial_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES) != cudaSuccess)
+            if (cudaFuncSetAttribute(attention_partial_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES) != cudaSuccess ||
+                cudaFuncSetAttribute(attention_partial_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES) != cudaSuccess ||
+                cudaFuncSetAttribute(attention_partial_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES) != cudaSuccess ||
+                cudaFuncSetAttribute(attention_partial_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES) != cudaSuccess)
                 return launch_status(false, "cache_attention (shared memory opt-in)");
             configured[dev].store(true, std::memory_order_release);
         }
@@ -155,8 +163,14 @@ int pitch_enqueue_cache_attention(const pitch_cache_desc* d, const pitch_attenti
         cfg.stream = s;
         cfg.attrs = pdl;
         cfg.numAttrs = 1;
-        if (a->precision == PITCH_ATTENTION_BF16) cudaLaunchKernelEx(&cfg, attention_partial_kernel<true>, p);
-        else cudaLaunchKernelEx(&cfg, attention_partial_kernel<false>, p);
+        const bool fast = a->precision == PITCH_ATTENTION_BF16;
+        if (turbo_keys) {
+            if (fast) cudaLaunchKernelEx(&cfg, attention_partial_kernel<true, true>, p);
+            else cudaLaunchKernelEx(&cfg, attention_partial_kernel<false, true>, p);
+        } else {
+            if (fast) cudaLaunchKernelEx(&cfg, attention_partial_kernel<true, false>, p);
+            else cudaLaunchKernelEx(&cfg, attention_partial_kernel<false, false>, p);
+        }
         if ((st = launch_status(false, "cache_attention"))) return st;
         cfg.gridDim = dim3((unsigned)p.n_queries, (unsigned)p.segments);
         cfg.blockDim = dim3(32 * AT_COMBINE_WARPS);

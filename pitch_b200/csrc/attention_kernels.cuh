@@ -1,5 +1,5 @@
-// Single-token attention straight from the compressed cache (head dimension 64, per-channel 4-bit
-// keys, TurboQuant 4-bit values): the decoded cache is never written to memory.  This is the step
+// Single-token attention straight from the compressed cache (head dimension 64; per-channel 4-bit
+// or TurboQuant 4-bit keys; TurboQuant 4-bit values): the decoded cache is never written to memory.  This is the step
 // the reference names as what has to come next for long contexts (README.md:96, "decoding needs
 // to move inside the attention kernel").
 //
@@ -34,6 +34,12 @@
 // output coordinates in the second is chosen to match how codes sit in their words.
 // Thread (g, t) = (lane / 4, lane % 4).  Rows >= n_queries repeat query 0 and are discarded.
 //
+// TurboQuant keys (K_t = norm_t / 8 * D H cb[codes_t]) take the route of the values instead: the
+// query is rotated once per run, q' = scale * H D q / 8, so that s_t = norm_t * <q', cb[codes_t]>;
+// the centroids of a token's code bytes come from the same lane-replicated table as the values'
+// (both planes use the codebook of (64, 4)), already in A-fragment form, and the key's norm scales
+// the score row after the product.  No grouping, no folding.
+//
 // Kernel 1 (attention_partial_kernel): one CTA of 16 warps per SM, every warp on its own.  The
 // tokens of a segment are cut into runs of whole tiles, about one run per resident warp of the
 // GPU; a warp walks its run with online softmax (running maximum and sum per query, base-2
@@ -54,7 +60,7 @@ constexpr int AT_MAX_QUERIES = 8;
 constexpr int AT_PART_FLOATS = 66;                     // per (segment, slice, query): max, sum, 64 accumulators
 constexpr int AT_STAGE_K = 32 * 32;                    // a tile's key codes, 32 bytes per token
 constexpr int AT_STAGE_V = 32 * 48;                    // a tile's value codes, rows padded to 48 bytes (bank spread)
-constexpr int AT_STAGE_BYTES = AT_STAGE_K + AT_STAGE_V + 128;       // + 32 norms
+constexpr int AT_STAGE_BYTES = AT_STAGE_K + AT_STAGE_V + 256;       // + 32 value norms + 32 key norms (TurboQuant keys)
 // per warp: per-group steps and offsets of the keys; folded query; two tile buffers (one in flight)
 constexpr int AT_WARP_SMEM = 512 + 12 * 32 * 8 + 2 * AT_STAGE_BYTES;
 constexpr int AT_SMEM_BYTES = CD_TABLE_BYTES + AT_WARPS * AT_WARP_SMEM;
@@ -65,6 +71,7 @@ struct AttentionParams {
     int n_queries, group_size;
     float scale_log2;                                  // softmax scale * log2(e)
     uint32_t neg_lo, neg_hi;                           // sign diagonal of the values' rotation
+    uint32_t kneg_lo, kneg_hi;                         // sign diagonal of the keys' rotation (TurboQuant keys)
     const unsigned char* k_codes; int64_t k_codes_seg;
     const unsigned char* k_ranges; int64_t k_ranges_seg;
     const unsigned char* v_codes; int64_t v_codes_seg;
@@ -116,9 +123,11 @@ __device__ __forceinline__ uint32_t key_pair(uint32_t w) {
 // Starts the asynchronous copy of a tile (32 tokens from `tok`, `nvalid` of them existing) into a
 // warp's tile buffer: key codes, value codes, norms.  Bytes of tokens that do not exist are
 // zero-filled without touching memory.
+// k_norms: the keys' norms (TurboQuant keys) or null.
 __device__ __forceinline__ void issue_attn_tile(unsigned char* stage, const unsigned char* __restrict__ k_codes,
                                                 const unsigned char* __restrict__ v_codes,
-                                                const float* __restrict__ v_norms, int tok, int nvalid, int lane) {
+                                                const float* __restrict__ v_norms, const float* __restrict__ k_norms,
+                                                int tok, int nvalid, int lane) {
     const uint32_t base = (uint32_t)__cvta_generic_to_shared(stage);
     const unsigned char* ksrc = k_codes + (int64_t)tok * 32;
     const unsigned char* vsrc = v_codes + (int64_t)tok * 32;
@@ -131,12 +140,13 @@ __device__ __forceinline__ void issue_attn_tile(unsigned char* stage, const unsi
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
                      :: "r"(base + AT_STAGE_K + token * 48 + (c & 1) * 16), "l"(live ? vsrc + c * 16 : vsrc), "r"(live) : "memory");
     }
-    if (lane < 8) {
-        int live = nvalid * 4 - 16 * lane;
+    if (lane < 8 || (k_norms != nullptr && lane < 16)) {
+        const int l8 = lane & 7;
+        int live = nvalid * 4 - 16 * l8;
         live = live < 0 ? 0 : (live > 16 ? 16 : live);
-        const float* nsrc = v_norms + tok;
+        const float* nsrc = (lane < 8 ? v_norms : k_norms) + tok;
         asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;"
-                     :: "r"(base + AT_STAGE_K + AT_STAGE_V + lane * 16), "l"(live ? nsrc + 4 * lane : nsrc), "r"(live) : "memory");
+                     :: "r"(base + AT_STAGE_K + AT_STAGE_V + lane * 16), "l"(live ? nsrc + 4 * l8 : nsrc), "r"(live) : "memory");
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
 }
@@ -152,7 +162,9 @@ struct AttnState {
 // FAST: operands as a bf16 pipeline would have them - the folded query in two bf16 parts instead of
 // three, weights and centroids in one instead of two - which halves the tensor-core products and the
 // table look-ups; the result is then as accurate as attention over the cache decoded to bf16.
-template <bool FAST>
+// TK: TurboQuant keys - the A operand of the score product is looked up in the centroid table and the
+// key norms (128 bytes after the value norms) scale the score rows.
+template <bool FAST, bool TK>
 __device__ __forceinline__ void attn_tile(const unsigned char* kb, const unsigned char* vb, const unsigned char* nb,
                                           AttnState& st, const uint2* qf,
                                           float bias0, float bias1, int nvalid, const unsigned char* table,
@@ -178,11 +190,30 @@ __device__ __forceinline__ void attn_tile(const unsigned char* kb, const unsigne
         if (!FAST) ql = qf[(2 * 4 + KB) * 32];                                                       \
         _Pragma("unroll")                                                                            \
         for (int m = 0; m < 2; ++m) {                                                                \
-            const uint32_t a0 = key_pair<KB>(kc[m][0].x), a1 = key_pair<KB>(kc[m][1].x);             \
-            const uint32_t a2 = key_pair<KB>(kc[m][0].y), a3 = key_pair<KB>(kc[m][1].y);             \
-            mma_bf16(sc[m], a0, a1, a2, a3, qh.x, qh.y);                                             \
-            mma_bf16(sm[m], a0, a1, a2, a3, qm.x, qm.y);                                             \
-            if (!FAST) mma_bf16(sl[m], a0, a1, a2, a3, ql.x, ql.y);                                  \
+            if (TK) {                                                                                \
+                /* byte KB of words 2t and 2t+1 of rows g and g+8: two adjacent codes each */        \
+                const unsigned char* e0 = table + __byte_perm(kc[m][0].x, slot, 0x5504 | (KB << 4)); \
+                const unsigned char* e1 = table + __byte_perm(kc[m][1].x, slot, 0x5504 | (KB << 4)); \
+                const unsigned char* e2 = table + __byte_perm(kc[m][0].y, slot, 0x5504 | (KB << 4)); \
+                const unsigned char* e3 = table + __byte_perm(kc[m][1].y, slot, 0x5504 | (KB << 4)); \
+                const uint32_t a0 = *reinterpret_cast<const uint32_t*>(e0), a1 = *reinterpret_cast<const uint32_t*>(e1); \
+                const uint32_t a2 = *reinterpret_cast<const uint32_t*>(e2), a3 = *reinterpret_cast<const uint32_t*>(e3); \
+                mma_bf16(sc[m], a0, a1, a2, a3, qh.x, qh.y);                                         \
+                mma_bf16(sm[m], a0, a1, a2, a3, qm.x, qm.y);                                         \
+                if (!FAST) {                                                                         \
+                    const uint32_t l0 = *reinterpret_cast<const uint32_t*>(e0 + 128), l1 = *reinterpret_cast<const uint32_t*>(e1 + 128); \
+                    const uint32_t l2 = *reinterpret_cast<const uint32_t*>(e2 + 128), l3 = *reinterpret_cast<const uint32_t*>(e3 + 128); \
+                    mma_bf16(sl[m], a0, a1, a2, a3, ql.x, ql.y);                                     \
+                    mma_bf16(sl[m], l0, l1, l2, l3, qh.x, qh.y);                                     \
+                    mma_bf16(sl[m], l0, l1, l2, l3, qm.x, qm.y);                                     \
+                }                                                                                    \
+            } else {                                                                                 \
+                const uint32_t a0 = key_pair<KB>(kc[m][0].x), a1 = key_pair<KB>(kc[m][1].x);         \
+                const uint32_t a2 = key_pair<KB>(kc[m][0].y), a3 = key_pair<KB>(kc[m][1].y);         \
+                mma_bf16(sc[m], a0, a1, a2, a3, qh.x, qh.y);                                         \
+                mma_bf16(sm[m], a0, a1, a2, a3, qm.x, qm.y);                                         \
+                if (!FAST) mma_bf16(sl[m], a0, a1, a2, a3, ql.x, ql.y);                              \
+            }                                                                                        \
         }                                                                                            \
     }
     PITCH_QK(0) PITCH_QK(1) PITCH_QK(2) PITCH_QK(3)
@@ -191,6 +222,15 @@ __device__ __forceinline__ void attn_tile(const unsigned char* kb, const unsigne
     for (int m = 0; m < 2; ++m)
 #pragma unroll
         for (int i = 0; i < 4; ++i) sc[m][i] += FAST ? sm[m][i] : sm[m][i] + sl[m][i];
+    if (TK) {
+        // s_t = norm_t * <q', centroids>: rows g and g + 8 of each block of 16 tokens
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+            const float n0 = *reinterpret_cast<const float*>(nb + 128 + (16 * m) * 4);
+            const float n1 = *reinterpret_cast<const float*>(nb + 128 + (16 * m + 8) * 4);
+            sc[m][0] *= n0; sc[m][1] *= n0; sc[m][2] *= n1; sc[m][3] *= n1;
+        }
+    }
     if (nvalid < 32) {
 #pragma unroll
         for (int m = 0; m < 2; ++m) {
@@ -319,7 +359,54 @@ __device__ __forceinline__ void fold_group(uint32_t lo2, uint32_t hi2, const flo
     bias1 = __shfl_sync(0xFFFFFFFFu, b, 8 * t + 4);       // of query 2t + 1
 }
 
-template <bool FAST>
+// TurboQuant keys: the rotated query q' = qscale / 8 * H D q of query g as B fragments (three bf16 parts,
+// same places as fold_group's).  Lane (g, t) owns channels 16t ... 16t + 15: the Walsh-Hadamard stages of
+// channel bits 0...3 run in registers, those of bits 4 and 5 between the four lanes of a query.  Fragment
+// slots follow the A side of the TurboQuant-key product: slots (2t, 2t+1) of block KB are channels
+// 16t + 2KB, + 1 (byte KB of the row's word 2t), slots (2t+8, 2t+9) channels 16t + 8 + 2KB, + 1.
+__device__ __forceinline__ void rotate_query(const float* __restrict__ qrow, float qscale, uint32_t neg_lo, uint32_t neg_hi,
+                                             uint2* qf, int lane, int t) {
+    float x[16];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float4 qv = __ldg(reinterpret_cast<const float4*>(qrow + 16 * t + 4 * i));
+        x[4 * i] = qv.x; x[4 * i + 1] = qv.y; x[4 * i + 2] = qv.z; x[4 * i + 3] = qv.w;
+    }
+    const uint32_t neg = t < 2 ? neg_lo : neg_hi;
+    const int shift = (16 * t) & 31;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) x[i] = flip_if(x[i], neg, shift + i);
+#pragma unroll
+    for (int h = 1; h < 16; h <<= 1)
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            if (!(i & h)) {
+                const float a = x[i], b = x[i | h];
+                x[i] = a + b;
+                x[i | h] = a - b;
+            }
+#pragma unroll
+    for (int m = 1; m < 4; m <<= 1)
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float o = __shfl_xor_sync(0xFFFFFFFFu, x[i], m);
+            x[i] = (lane & m) ? o - x[i] : x[i] + o;
+        }
+    const float sc = qscale * 0.125f;
+    __syncwarp();
+#pragma unroll
+    for (int kb = 0; kb < 4; ++kb) {
+        uint2 h, m, l;
+        split_pair3(x[2 * kb] * sc, x[2 * kb + 1] * sc, h.x, m.x, l.x);
+        split_pair3(x[8 + 2 * kb] * sc, x[9 + 2 * kb] * sc, h.y, m.y, l.y);
+        qf[(0 * 4 + kb) * 32 + lane] = h;
+        qf[(1 * 4 + kb) * 32 + lane] = m;
+        qf[(2 * 4 + kb) * 32 + lane] = l;
+    }
+    __syncwarp();
+}
+
+template <bool FAST, bool TK>
 __global__ void __launch_bounds__(AT_THREADS, 1)
 attention_partial_kernel(const __grid_constant__ AttentionParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -364,6 +451,7 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
         if (w_end > p.tokens) w_end = p.tokens;
 
         const __half* k_ranges = reinterpret_cast<const __half*>(p.k_ranges + seg * p.k_ranges_seg) + 2 * lane;
+        const float* k_norms = TK ? reinterpret_cast<const float*>(p.k_ranges + seg * p.k_ranges_seg) : nullptr;
         const unsigned char* k_codes = p.k_codes + seg * p.k_codes_seg;
         const unsigned char* v_codes = p.v_codes + seg * p.v_codes_seg;
         const float* v_norms = reinterpret_cast<const float*>(p.v_norms + seg * p.v_norms_seg);
@@ -382,15 +470,21 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
 
         // the first tile is on its way before anything else of the run is fetched
         __syncwarp();
-        issue_attn_tile(stage0, k_codes, v_codes, v_norms, w_begin, w_end - w_begin, lane);
+        issue_attn_tile(stage0, k_codes, v_codes, v_norms, k_norms, w_begin, w_end - w_begin, lane);
 
-        // the ranges of the first group; those of the following group are fetched a group ahead
-        int group = w_begin / p.group_size;
-        const int last_group = (w_end - 1) / p.group_size;
-        int group_end = (group + 1) * p.group_size;                   // first token of the next group
-        uint32_t lo2 = ldg_stream32(reinterpret_cast<const uint32_t*>(k_ranges + (int64_t)group * 128));
-        uint32_t hi2 = ldg_stream32(reinterpret_cast<const uint32_t*>(k_ranges + (int64_t)group * 128 + 64));
-        bool fold = true;
+        // per-channel keys: the ranges of the first group; those of the following group are fetched a
+        // group ahead.  TurboQuant keys: the query is rotated once, here.
+        int group = TK ? 0 : w_begin / p.group_size;
+        const int last_group = TK ? 0 : (w_end - 1) / p.group_size;
+        int group_end = TK ? 0x7FFFFFFF : (group + 1) * p.group_size;   // first token of the next group
+        uint32_t lo2 = 0, hi2 = 0;
+        bool fold = !TK;
+        if (TK) {
+            rotate_query(qrow, qscale, p.kneg_lo, p.kneg_hi, qf, lane, t);
+        } else {
+            lo2 = ldg_stream32(reinterpret_cast<const uint32_t*>(k_ranges + (int64_t)group * 128));
+            hi2 = ldg_stream32(reinterpret_cast<const uint32_t*>(k_ranges + (int64_t)group * 128 + 64));
+        }
 
         // this lane's places in tile buffer 0; buffer 1 is AT_STAGE_BYTES further
         const unsigned char* kb = stage0 + g * 32 + t * 8;
@@ -400,14 +494,14 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
         {                                                                                               \
             const int nvalid = w_end - t0;                            /* >= 32 for a whole tile */      \
             if (nvalid > 32) {                                                                          \
-                issue_attn_tile(stage0 + (1 - BUF) * AT_STAGE_BYTES, k_codes, v_codes, v_norms, t0 + 32, nvalid - 32, lane); \
+                issue_attn_tile(stage0 + (1 - BUF) * AT_STAGE_BYTES, k_codes, v_codes, v_norms, k_norms, t0 + 32, nvalid - 32, lane); \
                 cp_async_wait<1>();                                                                     \
             } else {                                                                                    \
                 cp_async_wait<0>();                                                                     \
             }                                                                                           \
             __syncwarp();                                                                               \
-            if (t0 >= group_end) { ++group; group_end += p.group_size; fold = true; }                  \
-            if (fold) {                                                                                 \
+            if (!TK && t0 >= group_end) { ++group; group_end += p.group_size; fold = true; }           \
+            if (!TK && fold) {                                                                          \
                 fold = false;                                                                           \
                 fold_group(lo2, hi2, qrow, qscale, gstep, goff, qf, bias0, bias1, lane, g, t);          \
                 if (group < last_group) {                                                               \
@@ -415,7 +509,7 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
                     hi2 = ldg_stream32(reinterpret_cast<const uint32_t*>(k_ranges + (int64_t)(group + 1) * 128 + 64)); \
                 }                                                                                       \
             }                                                                                           \
-            attn_tile<FAST>(kb + BUF * AT_STAGE_BYTES, vb + BUF * AT_STAGE_BYTES, nb + BUF * AT_STAGE_BYTES, st, qf + lane,  \
+            attn_tile<FAST, TK>(kb + BUF * AT_STAGE_BYTES, vb + BUF * AT_STAGE_BYTES, nb + BUF * AT_STAGE_BYTES, st, qf + lane,  \
                       bias0, bias1, nvalid, table, slot, g);                                            \
             __syncwarp();                                             /* this buffer is refilled two tiles on */ \
         }
