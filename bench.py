@@ -313,7 +313,7 @@ class StepTimer:
         # thread-local capture: other threads of the process (the process group's watchdog) stay free to query events
         with torch.cuda.graph(graph, capture_error_mode="thread_local"):
             for i in range(steps):
-                c.step(self.new_k[warmup + i], self.new_v[warmup + i])
+                c.step(self.new_k[warmup + i], self.new_v[warmup + i], views=False)
                 nbytes += sum(step_bytes(c.segments, c.tokens))
         graph.replay()
         for t, keep in zip(state, saved):
@@ -339,7 +339,7 @@ class StepTimer:
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
         ev[0].record()
         for i in range(steps):
-            c.step(self.new_k[warmup + i], self.new_v[warmup + i])
+            c.step(self.new_k[warmup + i], self.new_v[warmup + i], views=False)
             ev[i + 1].record()
         self.barrier()
         per = [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)]

@@ -161,6 +161,7 @@ class KVCache:
                     src[i].residual_seg_stride = pl.residual.stride(0) * 4
                     src[i].residual_bytes = pl.residual.numel() * 4
             self._src_cache = src
+            self._src_geometry = None
             self._lib = _native.lib()
             # twin descriptor with the key-bias tables
             b = _native.CacheDesc.from_buffer_copy(d)
@@ -172,14 +173,20 @@ class KVCache:
         return d
 
     def _fill_src(self, keys, values, first: int, n: int):
-        """Points the cached ``pitch_append_src`` array at tokens ``[first, first + n)`` of the inputs."""
+        """Points the cached ``pitch_append_src`` array at tokens ``[first, first + n)`` of the inputs.
+        Strides and extents are rewritten only when the inputs' geometry changed since the last call
+        (this runs once per generated token)."""
         src = self._src_cache
         esz = keys.element_size()
         off = first * self.dim * esz
-        for i, x in enumerate((keys, values)):
-            src[i].input = x.data_ptr() + off
-            src[i].input_seg_stride = x.stride(0) * esz
-            src[i].input_bytes = x.numel() * esz - off
+        geometry = (keys.stride(0), values.stride(0), keys.numel(), values.numel(), esz, off)
+        src[0].input = keys.data_ptr() + off
+        src[1].input = values.data_ptr() + off
+        if geometry != self._src_geometry:
+            for i, x in enumerate((keys, values)):
+                src[i].input_seg_stride = x.stride(0) * esz
+                src[i].input_bytes = x.numel() * esz - off
+            self._src_geometry = geometry
         return src
 
     def _stream_context(self, stream):
@@ -238,11 +245,13 @@ class KVCache:
             _native.check(st)
 
     # ------------------------------------------------------------------ the per-token path
-    def step(self, keys, values, stream=None):
+    def step(self, keys, values, stream=None, views: bool = True):
         """One generation step: appends ONE new token per segment (tensors ``[segments, 1, dim]``)
         and decodes the whole cache, new token included, in a single launch; returns the decoded
-        views like ``decode``.  Results are exactly those of ``append`` followed by ``decode``.
-        Cache shapes the one-launch kernel does not cover run as those two calls."""
+        views like ``decode`` (``views=False``: returns None and leaves it to the caller to slice
+        ``planes[i].out[:, :tokens]``, which saves a few microseconds per token).  Results are exactly
+        those of ``append`` followed by ``decode``.  Cache shapes the one-launch kernel does not cover
+        run as those two calls."""
         if not self._fused or (self.key_bias is not None and not self._fuse_bias):
             self.append(keys, values, stream)
             return self.decode(stream)
@@ -259,7 +268,7 @@ class KVCache:
         if st:
             _native.check(st)
         self.tokens += 1
-        return tuple(pl.out[:, :self.tokens] for pl in self.planes)
+        return tuple(pl.out[:, :self.tokens] for pl in self.planes) if views else None
 
     def _fused_ok(self) -> bool:
         """Whether the one-launch step kernel covers this cache (dim 64 or 128; TurboQuant planes of
