@@ -321,6 +321,36 @@ def bench_attention(q, reps, segments=48, tokens=32768, n_queries=7):
     yield row("cfg4 attention", "decode, then torch SDPA over the decoded cache", t2, segments * tokens, "kv_tokens",
               stored + 2 * cache.decoded_bytes(), {**extra, "speedup_of_fused": round(t2 / t, 2)})
 
+    # the same shape with TurboQuant keys (the query is rotated once instead of un-rotating every key)
+    tcfg = QuantConfig("turboQuant", d, 4)
+    tcache = KVCache(segments, d, tokens, QuantConfig("turboQuant", d, 4, seed=777), tcfg, out_dtype="bfloat16", pitch=q)
+    for s0 in range(0, segments, 8):
+        x = lognormal_vectors(8 * tokens, d, 40 + s0, q.device).reshape(8, tokens, d)
+        for pl in tcache.planes:
+            for j in range(8):
+                q.enqueue_encode(x[j], pl.codes[s0 + j], pl.side[s0 + j], tokens, pl.config)
+        torch.cuda.synchronize()
+        del x
+    tcache.tokens = tokens
+    got = tcache.attend(qs[0])
+    rk = torch.empty((tokens, d), dtype=torch.float32, device=q.device)
+    rv = torch.empty((tokens, d), dtype=torch.float32, device=q.device)
+    worst_t = 0.0
+    for s in (0, segments - 1):
+        q.enqueue_decode(tcache.planes[0].codes[s], tcache.planes[0].side[s], rk, tokens, tcache.planes[0].config)
+        q.enqueue_decode(tcache.planes[1].codes[s], tcache.planes[1].side[s], rv, tokens, tcache.planes[1].config)
+        ref = torch.softmax((qs[0][s].double() @ rk.double().T) * d ** -0.5, dim=1) @ rv.double()
+        worst_t = max(worst_t, float(((got[s].double() - ref).norm(dim=1) / ref.norm(dim=1)).max()))
+    if worst_t > 5e-5:
+        raise SystemExit(f"parity gate failed: cache attention with TurboQuant keys differs from attention over the decoded cache by {worst_t}")
+    del rk, rv
+    for prec in ("float32", "bfloat16"):
+        tt = timed(lambda i: tcache.attend(qs[i % 4], out=out, precision=prec))
+        yield row("cfg4-shape TurboQuant keys", f"attention from the compressed cache, {prec} operands", tt, segments * tokens, "kv_tokens",
+                  tcache.stored_bytes(), {**extra, "precision": prec, "tokens_per_s": round(segments * tokens / tt, 1),
+                                          "parity": {"max_rel_l2_vs_float64_attention_over_decoded_cache": worst_t}})
+    del tcache
+
     # end to end with host buffers: queries from pinned host memory, result back to pinned host memory, waited for
     hq = torch.randn((8, segments, n_queries, d)).pin_memory()
     ho = torch.empty((segments, n_queries, d)).pin_memory()

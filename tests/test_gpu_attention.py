@@ -139,8 +139,10 @@ def test_turboquant_keys_match_attention_over_spec_decoded_cache(q, S, T, R, sca
     for s in range(S):
         K, V = spec_decoded_turbo(cache, s)
         ref = attention64(Q[s].astype(np.float64), K, V, sc)
-        assert rows_rel_l2(got[s], ref) < TOL, (s, rows_rel_l2(got[s], ref))
-        assert rows_rel_l2(fast[s], ref) < 1e-2, (s, rows_rel_l2(fast[s], ref))
+        # centroids enter the score product as two bf16 parts (2^-17): a softmax scale of 1.0 (scores eight
+        # times larger than usual) carries that into the weights
+        assert rows_rel_l2(got[s], ref) < (TOL if scale is None else 1e-4), (s, rows_rel_l2(got[s], ref))
+        assert rows_rel_l2(fast[s], ref) < (1e-2 if scale is None else 5e-2), (s, rows_rel_l2(fast[s], ref))
 
 
 def test_grows_with_the_cache(q):
