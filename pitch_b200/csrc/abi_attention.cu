@@ -34,10 +34,10 @@ extern "C" {
 // -------------------------------------------------------------------------------- attention
 // How a segment's tokens are cut into runs (one warp each).  Depends on the shape and on the GPU's
 // multiprocessor count only, so that the workspace size can be computed ahead of the call: runs of
-// whole 32-token tiles, about one run per warp that the GPU keeps resident (16 per multiprocessor),
-// at least 4 tiles long.
-static void attention_slices(int sms, int64_t segments, int64_t tokens, int* splits, int* tokens_per_split) {
-    const int64_t tiles = ceil_div(tokens, 32), slots = (int64_t)sms * AT_WARPS;
+// whole 32-token tiles, about one run per warp that the GPU keeps resident (16 per multiprocessor at
+// head dimension 64, 8 at 128), at least 4 tiles long.
+static void attention_slices(int sms, int dim, int64_t segments, int64_t tokens, int* splits, int* tokens_per_split) {
+    const int64_t tiles = ceil_div(tokens, 32), slots = (int64_t)sms * (dim == 64 ? AttnGeom<64>::WARPS : AttnGeom<128>::WARPS);
     int64_t run = ceil_div(segments * tiles, slots);
     if (run < 4) run = 4;
     // rounding the runs per segment up must not push the total past the resident warps: a few
@@ -54,12 +54,14 @@ static int check_attention_shape(const pitch_cache_desc* d, int n_queries) {
         return fail(PITCH_ERR_INVALID_INPUT, "n_queries %d must be in 1...%d", n_queries, AT_MAX_QUERIES);
     if (d->segments < 1 || d->segments > 65535 || d->tokens < 1 || d->tokens > 0x7FFFFFFF - 1024)
         return fail(PITCH_ERR_INVALID_INPUT, "segments must be in 1...65535 and tokens in 1...2^31-1025");
-    if (d->dim != 64 || d->n_planes != 2)
-        return fail(PITCH_ERR_INVALID_INPUT, "cache attention needs dim 64 and two planes (keys, values)");
+    if ((d->dim != 64 && d->dim != 128) || d->n_planes != 2)
+        return fail(PITCH_ERR_INVALID_INPUT, "cache attention needs dim 64 or 128 and two planes (keys, values)");
     const pitch_plane& k = d->planes[0];
     const pitch_plane& v = d->planes[1];
     if (k.kind == PITCH_PLANE_TURBO) {
         if (k.bits != 4) return fail(PITCH_ERR_INVALID_INPUT, "cache attention needs 4-bit keys");
+    } else if (d->dim != 64) {
+        return fail(PITCH_ERR_INVALID_INPUT, "cache attention at dim 128 needs TurboQuant 4-bit keys");
     } else if (k.kind != PITCH_PLANE_CHANNEL || k.bits != 4 || k.group_size < 32 || k.group_size % 32 != 0 || k.group_size > PITCH_MAX_GROUP) {
         return fail(PITCH_ERR_INVALID_INPUT, "cache attention needs TurboQuant 4-bit keys, or per-channel 4-bit keys with a group size that is a multiple of 32");
     }
@@ -71,8 +73,8 @@ static int check_attention_shape(const pitch_cache_desc* d, int n_queries) {
 int64_t pitch_cache_attention_workspace(const pitch_cache_desc* d, int n_queries) {
     if (check_attention_shape(d, n_queries)) return -1;
     int splits, tps;
-    attention_slices(desc_sm_count(d), d->segments, d->tokens, &splits, &tps);
-    return d->segments * splits * n_queries * AT_PART_FLOATS * (int64_t)sizeof(float);
+    attention_slices(desc_sm_count(d), d->dim, d->segments, d->tokens, &splits, &tps);
+    return d->segments * splits * n_queries * (2 + d->dim) * (int64_t)sizeof(float);
 }
 
 int pitch_enqueue_cache_attention(const pitch_cache_desc* d, const pitch_attention_args* a, void* stream) {
@@ -93,15 +95,15 @@ int pitch_enqueue_cache_attention(const pitch_cache_desc* d, const pitch_attenti
         if (!pl.codes || !pl.side) return fail(PITCH_ERR_INVALID_INPUT, "plane %d: null pointer", i);
         if (!aligned16(pl.codes) || !aligned16(pl.side) || (pl.codes_seg_stride & 15) || (pl.side_seg_stride & 15))
             return fail(PITCH_ERR_INVALID_INPUT, "plane %d: pointers and segment strides must be multiples of 16", i);
-        if (d->segments > 1 && (pl.codes_seg_stride < d->tokens * 32 || pl.side_seg_stride < plane_side_bytes(pl, 64, d->tokens)))
+        if (d->segments > 1 && (pl.codes_seg_stride < d->tokens * (d->dim / 2) || pl.side_seg_stride < plane_side_bytes(pl, d->dim, d->tokens)))
             return fail(PITCH_ERR_INVALID_INPUT, "plane %d: a segment stride is smaller than one segment", i);
         // Codec.check (Sources/PITCH/Core/Codec.swift:42-46): the buffers must hold what the call reads
-        if (pl.codes_bytes < (d->segments - 1) * pl.codes_seg_stride + d->tokens * 32)
+        if (pl.codes_bytes < (d->segments - 1) * pl.codes_seg_stride + d->tokens * (d->dim / 2))
             return fail(PITCH_ERR_INVALID_INPUT, "plane %d: codes buffer has %lld bytes; needs %lld", i, (long long)pl.codes_bytes,
-                        (long long)((d->segments - 1) * pl.codes_seg_stride + d->tokens * 32));
-        if (pl.side_bytes < (d->segments - 1) * pl.side_seg_stride + plane_side_bytes(pl, 64, d->tokens))
+                        (long long)((d->segments - 1) * pl.codes_seg_stride + d->tokens * (d->dim / 2)));
+        if (pl.side_bytes < (d->segments - 1) * pl.side_seg_stride + plane_side_bytes(pl, d->dim, d->tokens))
             return fail(PITCH_ERR_INVALID_INPUT, "plane %d: side-information buffer has %lld bytes; needs %lld", i,
-                        (long long)pl.side_bytes, (long long)((d->segments - 1) * pl.side_seg_stride + plane_side_bytes(pl, 64, d->tokens)));
+                        (long long)pl.side_bytes, (long long)((d->segments - 1) * pl.side_seg_stride + plane_side_bytes(pl, d->dim, d->tokens)));
     }
     const pitch_buffer bufs[5] = {{const_cast<void*>(a->queries), 0, 0}, {a->out, 0, 0}, {a->workspace, 0, 0},
                                   {d->planes[0].codes, 0, 0}, {d->planes[1].codes, 0, 0}};
@@ -114,16 +116,17 @@ int pitch_enqueue_cache_attention(const pitch_cache_desc* d, const pitch_attenti
     memset(&p, 0, sizeof p);
     p.segments = (int)d->segments;
     p.tokens = (int)d->tokens;
-    attention_slices(sm_count(), d->segments, d->tokens, &p.splits, &p.tokens_per_split);
+    attention_slices(sm_count(), d->dim, d->segments, d->tokens, &p.splits, &p.tokens_per_split);
     if ((int64_t)p.segments * p.splits > 0x7FFFFFFF) return fail(PITCH_ERR_INVALID_INPUT, "segments x runs exceeds 2^31 - 1");
     p.n_queries = a->n_queries;
     const bool turbo_keys = d->planes[0].kind == PITCH_PLANE_TURBO;
     p.group_size = turbo_keys ? 32 : d->planes[0].group_size;
-    p.kneg_lo = negate_mask32(d->planes[0].seed, 0);
-    p.kneg_hi = negate_mask32(d->planes[0].seed, 32);
+    for (int j = 0; j < 4; ++j) {
+        p.kneg[j] = negate_mask32(d->planes[0].seed, 32u * j);
+        p.neg[j] = negate_mask32(d->planes[1].seed, 32u * j);
+    }
+    p.rs = rsqrt_dim(d->dim);
     p.scale_log2 = (float)((double)a->scale * 1.4426950408889634);
-    p.neg_lo = negate_mask32(d->planes[1].seed, 0);
-    p.neg_hi = negate_mask32(d->planes[1].seed, 32);
     p.k_codes = static_cast<const unsigned char*>(d->planes[0].codes);
     p.k_codes_seg = d->planes[0].codes_seg_stride;
     p.k_ranges = static_cast<const unsigned char*>(d->planes[0].side);
@@ -135,20 +138,26 @@ int pitch_enqueue_cache_attention(const pitch_cache_desc* d, const pitch_attenti
     p.q = static_cast<const float*>(a->queries);
     p.work = static_cast<float*>(a->workspace);
     p.out = static_cast<float*>(a->out);
-    if (!book_get(64, 4, p.book.c)) return fail(PITCH_ERR_INVALID_INPUT, "no TurboQuant codebook for dim 64, bits 4");
+    if (!book_get(d->dim, 4, p.book.c)) return fail(PITCH_ERR_INVALID_INPUT, "no TurboQuant codebook for dim %d, bits 4", d->dim);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     {
+        const bool wide = d->dim == 128;
+        const int smem = wide ? AttnGeom<128>::SMEM_BYTES : AttnGeom<64>::SMEM_BYTES;
+        const int warps = wide ? AttnGeom<128>::WARPS : AttnGeom<64>::WARPS;
         static std::atomic<bool> configured[64];
         if (dev >= 0 && dev < 64 && !configured[dev].load(std::memory_order_acquire)) {
-            if (cudaFuncSetAttribute(attention_partial_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES) != cudaSuccess ||
-                cudaFuncSetAttribute(attention_partial_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES) != cudaSuccess ||
-                cudaFuncSetAttribute(attention_partial_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES) != cudaSuccess ||
-                cudaFuncSetAttribute(attention_partial_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES) != cudaSuccess)
+            const cudaFuncAttribute at = cudaFuncAttributeMaxDynamicSharedMemorySize;
+            if (cudaFuncSetAttribute(attention_partial_kernel<64, false, false>, at, AttnGeom<64>::SMEM_BYTES) != cudaSuccess ||
+                cudaFuncSetAttribute(attention_partial_kernel<64, true, false>, at, AttnGeom<64>::SMEM_BYTES) != cudaSuccess ||
+                cudaFuncSetAttribute(attention_partial_kernel<64, false, true>, at, AttnGeom<64>::SMEM_BYTES) != cudaSuccess ||
+                cudaFuncSetAttribute(attention_partial_kernel<64, true, true>, at, AttnGeom<64>::SMEM_BYTES) != cudaSuccess ||
+                cudaFuncSetAttribute(attention_partial_kernel<128, false, true>, at, AttnGeom<128>::SMEM_BYTES) != cudaSuccess ||
+                cudaFuncSetAttribute(attention_partial_kernel<128, true, true>, at, AttnGeom<128>::SMEM_BYTES) != cudaSuccess)
                 return launch_status(false, "cache_attention (shared memory opt-in)");
             configured[dev].store(true, std::memory_order_release);
         }
-        // one CTA of sixteen warps per SM; a warp takes runs warp, warp + all warps, ...
-        int64_t ctas = ceil_div((int64_t)p.segments * p.splits, AT_WARPS);
+        // one CTA per SM (16 warps at dim 64, 8 at dim 128); a warp takes runs warp, warp + all warps, ...
+        int64_t ctas = ceil_div((int64_t)p.segments * p.splits, warps);
         if (ctas > sm_count()) ctas = sm_count();
         // Both launches are programmatic dependent launches: each grid may be scheduled while the
         // kernel before it in the stream is still running, sets itself up, then waits for that
@@ -158,24 +167,28 @@ int pitch_enqueue_cache_attention(const pitch_cache_desc* d, const pitch_attenti
         pdl[0].val.programmaticStreamSerializationAllowed = 1;
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)ctas);
-        cfg.blockDim = dim3(AT_THREADS);
-        cfg.dynamicSmemBytes = AT_SMEM_BYTES;
+        cfg.blockDim = dim3(32 * warps);
+        cfg.dynamicSmemBytes = smem;
         cfg.stream = s;
         cfg.attrs = pdl;
         cfg.numAttrs = 1;
         const bool fast = a->precision == PITCH_ATTENTION_BF16;
-        if (turbo_keys) {
-            if (fast) cudaLaunchKernelEx(&cfg, attention_partial_kernel<true, true>, p);
-            else cudaLaunchKernelEx(&cfg, attention_partial_kernel<false, true>, p);
+        if (wide) {
+            if (fast) cudaLaunchKernelEx(&cfg, attention_partial_kernel<128, true, true>, p);
+            else cudaLaunchKernelEx(&cfg, attention_partial_kernel<128, false, true>, p);
+        } else if (turbo_keys) {
+            if (fast) cudaLaunchKernelEx(&cfg, attention_partial_kernel<64, true, true>, p);
+            else cudaLaunchKernelEx(&cfg, attention_partial_kernel<64, false, true>, p);
         } else {
-            if (fast) cudaLaunchKernelEx(&cfg, attention_partial_kernel<true, false>, p);
-            else cudaLaunchKernelEx(&cfg, attention_partial_kernel<false, false>, p);
+            if (fast) cudaLaunchKernelEx(&cfg, attention_partial_kernel<64, true, false>, p);
+            else cudaLaunchKernelEx(&cfg, attention_partial_kernel<64, false, false>, p);
         }
         if ((st = launch_status(false, "cache_attention"))) return st;
         cfg.gridDim = dim3((unsigned)p.n_queries, (unsigned)p.segments);
         cfg.blockDim = dim3(32 * AT_COMBINE_WARPS);
         cfg.dynamicSmemBytes = 0;
-        cudaLaunchKernelEx(&cfg, attention_combine_kernel, p);
+        if (wide) cudaLaunchKernelEx(&cfg, attention_combine_kernel<128>, p);
+        else cudaLaunchKernelEx(&cfg, attention_combine_kernel<64>, p);
     }
     return launch_status(false, "cache_attention (combine)");
 }

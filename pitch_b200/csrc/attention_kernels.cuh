@@ -1,5 +1,8 @@
-// Single-token attention straight from the compressed cache (head dimension 64; per-channel 4-bit
-// or TurboQuant 4-bit keys; TurboQuant 4-bit values): the decoded cache is never written to memory.  This is the step
+// Single-token attention straight from the compressed cache (head dimension 64 with per-channel 4-bit
+// or TurboQuant 4-bit keys, head dimension 128 with TurboQuant 4-bit keys; TurboQuant 4-bit values):
+// the decoded cache is never written to memory.  The text below describes dimension 64; at 128 every
+// row is twice as long (eight blocks of 16 channels / coordinates instead of four, four code words
+// per lane instead of two) and a CTA has 8 warps instead of 16, because the accumulators double.  This is the step
 // the reference names as what has to come next for long contexts (README.md:96, "decoding needs
 // to move inside the attention kernel").
 //
@@ -54,32 +57,40 @@
 
 namespace pitch {
 
-constexpr int AT_THREADS = 512;
-constexpr int AT_WARPS = AT_THREADS / 32;
 constexpr int AT_MAX_QUERIES = 8;
-constexpr int AT_PART_FLOATS = 66;                     // per (segment, slice, query): max, sum, 64 accumulators
-constexpr int AT_STAGE_K = 32 * 32;                    // a tile's key codes, 32 bytes per token
-constexpr int AT_STAGE_V = 32 * 48;                    // a tile's value codes, rows padded to 48 bytes (bank spread)
-constexpr int AT_STAGE_BYTES = AT_STAGE_K + AT_STAGE_V + 256;       // + 32 value norms + 32 key norms (TurboQuant keys)
-// per warp: per-group steps and offsets of the keys; folded query; two tile buffers (one in flight)
-constexpr int AT_WARP_SMEM = 512 + 12 * 32 * 8 + 2 * AT_STAGE_BYTES;
-constexpr int AT_SMEM_BYTES = CD_TABLE_BYTES + AT_WARPS * AT_WARP_SMEM;
 constexpr int AT_COMBINE_WARPS = 8;
+
+// Sizes for head dimension D (64 or 128), 4-bit codes.
+template <int D> struct AttnGeom {
+    static constexpr int WARPS = D == 64 ? 16 : 8;             // warps per CTA (one CTA per multiprocessor)
+    static constexpr int THREADS = WARPS * 32;
+    static constexpr int NKB = D / 16;                         // blocks of 16 channels / coordinates
+    static constexpr int ROWB = D / 2;                         // bytes of codes per token
+    static constexpr int VPITCH = ROWB + 16;                   // value rows padded by 16 bytes (bank spread)
+    static constexpr int PART_FLOATS = 2 + D;                  // per (segment, run, query): max, sum, D accumulators
+    static constexpr int STAGE_K = 32 * ROWB;                  // a tile's key codes
+    static constexpr int STAGE_V = 32 * VPITCH;                // a tile's value codes
+    static constexpr int STAGE_BYTES = STAGE_K + STAGE_V + 256;          // + 32 value norms + 32 key norms (TurboQuant keys)
+    // per warp: per-group steps and offsets of the keys; query fragments (3 parts); two tile buffers (one in flight)
+    static constexpr int WARP_SMEM = 512 + 3 * NKB * 32 * 8 + 2 * STAGE_BYTES;
+    static constexpr int SMEM_BYTES = CD_TABLE_BYTES + WARPS * WARP_SMEM;
+};
 
 struct AttentionParams {
     int segments, tokens, splits, tokens_per_split;    // a run: tokens_per_split tokens, a multiple of 32
     int n_queries, group_size;
     float scale_log2;                                  // softmax scale * log2(e)
-    uint32_t neg_lo, neg_hi;                           // sign diagonal of the values' rotation
-    uint32_t kneg_lo, kneg_hi;                         // sign diagonal of the keys' rotation (TurboQuant keys)
+    uint32_t neg[4];                                   // sign diagonal of the values' rotation (bit i of word j: coordinate 32j + i)
+    uint32_t kneg[4];                                  // sign diagonal of the keys' rotation (TurboQuant keys)
+    float rs;                                          // 1 / sqrt(dim)
     const unsigned char* k_codes; int64_t k_codes_seg;
     const unsigned char* k_ranges; int64_t k_ranges_seg;
     const unsigned char* v_codes; int64_t v_codes_seg;
     const unsigned char* v_norms; int64_t v_norms_seg;
-    const float* q;                                    // [segments][n_queries][64]
-    float* work;                                       // [segments][splits][n_queries][66]
-    float* out;                                        // [segments][n_queries][64]
-    Book16 book;                                       // TurboQuant centroids (64, 4)
+    const float* q;                                    // [segments][n_queries][dim]
+    float* work;                                       // [segments][splits][n_queries][2 + dim]
+    float* out;                                        // [segments][n_queries][dim]
+    Book16 book;                                       // TurboQuant centroids (dim, 4)
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -122,23 +133,25 @@ __device__ __forceinline__ uint32_t key_pair(uint32_t w) {
 
 // Starts the asynchronous copy of a tile (32 tokens from `tok`, `nvalid` of them existing) into a
 // warp's tile buffer: key codes, value codes, norms.  Bytes of tokens that do not exist are
-// zero-filled without touching memory.
-// k_norms: the keys' norms (TurboQuant keys) or null.
+// zero-filled without touching memory.  k_norms: the keys' norms (TurboQuant keys) or null.
+template <int D>
 __device__ __forceinline__ void issue_attn_tile(unsigned char* stage, const unsigned char* __restrict__ k_codes,
                                                 const unsigned char* __restrict__ v_codes,
                                                 const float* __restrict__ v_norms, const float* __restrict__ k_norms,
                                                 int tok, int nvalid, int lane) {
+    typedef AttnGeom<D> G;
+    constexpr int CPR = G::ROWB / 16;                               // 16-byte chunks per token row
     const uint32_t base = (uint32_t)__cvta_generic_to_shared(stage);
-    const unsigned char* ksrc = k_codes + (int64_t)tok * 32;
-    const unsigned char* vsrc = v_codes + (int64_t)tok * 32;
+    const unsigned char* ksrc = k_codes + (int64_t)tok * G::ROWB;
+    const unsigned char* vsrc = v_codes + (int64_t)tok * G::ROWB;
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const int c = lane + 32 * i, token = c >> 1;                 // 16-byte chunk c of the tile's 1024 code bytes
+    for (int i = 0; i < CPR; ++i) {
+        const int c = lane + 32 * i, token = c / CPR;                // chunk c of the tile's code bytes
         const int live = token < nvalid ? 16 : 0;
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
                      :: "r"(base + c * 16), "l"(live ? ksrc + c * 16 : ksrc), "r"(live) : "memory");
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
-                     :: "r"(base + AT_STAGE_K + token * 48 + (c & 1) * 16), "l"(live ? vsrc + c * 16 : vsrc), "r"(live) : "memory");
+                     :: "r"(base + G::STAGE_K + token * G::VPITCH + (c % CPR) * 16), "l"(live ? vsrc + c * 16 : vsrc), "r"(live) : "memory");
     }
     if (lane < 8 || (k_norms != nullptr && lane < 16)) {
         const int l8 = lane & 7;
@@ -146,14 +159,14 @@ __device__ __forceinline__ void issue_attn_tile(unsigned char* stage, const unsi
         live = live < 0 ? 0 : (live > 16 ? 16 : live);
         const float* nsrc = (lane < 8 ? v_norms : k_norms) + tok;
         asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;"
-                     :: "r"(base + AT_STAGE_K + AT_STAGE_V + lane * 16), "l"(live ? nsrc + 4 * l8 : nsrc), "r"(live) : "memory");
+                     :: "r"(base + G::STAGE_K + G::STAGE_V + lane * 16), "l"(live ? nsrc + 4 * l8 : nsrc), "r"(live) : "memory");
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
-struct AttnState {
+template <int D> struct AttnState {
     float m0, m1, l0, l1;         // running maximum and (per-thread partial) sum of queries 2t and 2t + 1
-    float acc[4][4];              // out^T fragments: [block of 16 coordinates][fragment register]
+    float acc[D / 16][4];         // out^T fragments: [block of 16 coordinates][fragment register]
 };
 
 // One tile: scores, online softmax, value accumulation.  kb / vb / nb: this lane's places in the
@@ -164,18 +177,28 @@ struct AttnState {
 // table look-ups; the result is then as accurate as attention over the cache decoded to bf16.
 // TK: TurboQuant keys - the A operand of the score product is looked up in the centroid table and the
 // key norms (128 bytes after the value norms) scale the score rows.
-template <bool FAST, bool TK>
+template <int D, bool FAST, bool TK>
 __device__ __forceinline__ void attn_tile(const unsigned char* kb, const unsigned char* vb, const unsigned char* nb,
-                                          AttnState& st, const uint2* qf,
+                                          AttnState<D>& st, const uint2* qf,
                                           float bias0, float bias1, int nvalid, const unsigned char* table,
                                           uint32_t slot, int g) {
     // ---- scores^T: two blocks of 16 tokens x 8 queries; one accumulator per part of the query, so
     //      that six short chains of products are in flight instead of two long ones
-    uint2 kc[2][2];                                               // words 2t, 2t+1 of tokens 16m + g and 16m + g + 8
+    typedef AttnGeom<D> G;
+    constexpr int NKB = G::NKB, WPL = D / 32;                     // code words per lane and row: 2 or 4
+    uint32_t kc[2][2][WPL];                                       // this lane's words of tokens 16m + g and 16m + g + 8
 #pragma unroll
     for (int m = 0; m < 2; ++m)
 #pragma unroll
-        for (int h = 0; h < 2; ++h) kc[m][h] = *reinterpret_cast<const uint2*>(kb + (16 * m + 8 * h) * 32);
+        for (int h = 0; h < 2; ++h) {
+            if (WPL == 2) {
+                const uint2 v = *reinterpret_cast<const uint2*>(kb + (16 * m + 8 * h) * G::ROWB);
+                kc[m][h][0] = v.x; kc[m][h][1] = v.y;
+            } else {
+                const uint4 v = *reinterpret_cast<const uint4*>(kb + (16 * m + 8 * h) * G::ROWB);
+                kc[m][h][0] = v.x; kc[m][h][1] = v.y; kc[m][h][WPL - 2] = v.z; kc[m][h][WPL - 1] = v.w;
+            }
+        }
     float sc[2][4], sm[2][4], sl[2][4];
 #pragma unroll
     for (int m = 0; m < 2; ++m) {
@@ -183,19 +206,21 @@ __device__ __forceinline__ void attn_tile(const unsigned char* kb, const unsigne
 #pragma unroll
         for (int i = 0; i < 4; ++i) { sm[m][i] = 0.0f; sl[m][i] = 0.0f; }
     }
+    // block KB of 16 channels: words 2*(KB/4), 2*(KB/4) + 1 of the lane's words, byte / nibble pair KB % 4
 #define PITCH_QK(KB)                                                                                 \
-    {                                                                                                \
-        const uint2 qh = qf[(0 * 4 + KB) * 32], qm = qf[(1 * 4 + KB) * 32];                          \
+    if (KB < NKB) {                                                                                  \
+        constexpr int W = 2 * ((KB) >> 2) < WPL ? 2 * ((KB) >> 2) : 0, B = (KB) & 3;                 \
+        const uint2 qh = qf[(0 * NKB + KB) * 32], qm = qf[(1 * NKB + KB) * 32];                      \
         uint2 ql = make_uint2(0, 0);                                                                 \
-        if (!FAST) ql = qf[(2 * 4 + KB) * 32];                                                       \
+        if (!FAST) ql = qf[(2 * NKB + KB) * 32];                                                     \
         _Pragma("unroll")                                                                            \
         for (int m = 0; m < 2; ++m) {                                                                \
             if (TK) {                                                                                \
-                /* byte KB of words 2t and 2t+1 of rows g and g+8: two adjacent codes each */        \
-                const unsigned char* e0 = table + __byte_perm(kc[m][0].x, slot, 0x5504 | (KB << 4)); \
-                const unsigned char* e1 = table + __byte_perm(kc[m][1].x, slot, 0x5504 | (KB << 4)); \
-                const unsigned char* e2 = table + __byte_perm(kc[m][0].y, slot, 0x5504 | (KB << 4)); \
-                const unsigned char* e3 = table + __byte_perm(kc[m][1].y, slot, 0x5504 | (KB << 4)); \
+                /* byte B of the word pair of rows g and g+8: two adjacent codes each */             \
+                const unsigned char* e0 = table + __byte_perm(kc[m][0][W], slot, 0x5504 | (B << 4)); \
+                const unsigned char* e1 = table + __byte_perm(kc[m][1][W], slot, 0x5504 | (B << 4)); \
+                const unsigned char* e2 = table + __byte_perm(kc[m][0][W + 1], slot, 0x5504 | (B << 4)); \
+                const unsigned char* e3 = table + __byte_perm(kc[m][1][W + 1], slot, 0x5504 | (B << 4)); \
                 const uint32_t a0 = *reinterpret_cast<const uint32_t*>(e0), a1 = *reinterpret_cast<const uint32_t*>(e1); \
                 const uint32_t a2 = *reinterpret_cast<const uint32_t*>(e2), a3 = *reinterpret_cast<const uint32_t*>(e3); \
                 mma_bf16(sc[m], a0, a1, a2, a3, qh.x, qh.y);                                         \
@@ -208,15 +233,15 @@ __device__ __forceinline__ void attn_tile(const unsigned char* kb, const unsigne
                     mma_bf16(sl[m], l0, l1, l2, l3, qm.x, qm.y);                                     \
                 }                                                                                    \
             } else {                                                                                 \
-                const uint32_t a0 = key_pair<KB>(kc[m][0].x), a1 = key_pair<KB>(kc[m][1].x);         \
-                const uint32_t a2 = key_pair<KB>(kc[m][0].y), a3 = key_pair<KB>(kc[m][1].y);         \
+                const uint32_t a0 = key_pair<B>(kc[m][0][W]), a1 = key_pair<B>(kc[m][1][W]);         \
+                const uint32_t a2 = key_pair<B>(kc[m][0][W + 1]), a3 = key_pair<B>(kc[m][1][W + 1]); \
                 mma_bf16(sc[m], a0, a1, a2, a3, qh.x, qh.y);                                         \
                 mma_bf16(sm[m], a0, a1, a2, a3, qm.x, qm.y);                                         \
                 if (!FAST) mma_bf16(sl[m], a0, a1, a2, a3, ql.x, ql.y);                              \
             }                                                                                        \
         }                                                                                            \
     }
-    PITCH_QK(0) PITCH_QK(1) PITCH_QK(2) PITCH_QK(3)
+    PITCH_QK(0) PITCH_QK(1) PITCH_QK(2) PITCH_QK(3) PITCH_QK(4) PITCH_QK(5) PITCH_QK(6) PITCH_QK(7)
 #undef PITCH_QK
 #pragma unroll
     for (int m = 0; m < 2; ++m)
@@ -251,7 +276,7 @@ __device__ __forceinline__ void attn_tile(const unsigned char* kb, const unsigne
         const float c0 = fast_exp2(st.m0 - n0), c1 = fast_exp2(st.m1 - n1);     // 0 on the first tile
         st.l0 *= c0; st.l1 *= c1;
 #pragma unroll
-        for (int mb = 0; mb < 4; ++mb) { st.acc[mb][0] *= c0; st.acc[mb][1] *= c1; st.acc[mb][2] *= c0; st.acc[mb][3] *= c1; }
+        for (int mb = 0; mb < NKB; ++mb) { st.acc[mb][0] *= c0; st.acc[mb][1] *= c1; st.acc[mb][2] *= c0; st.acc[mb][3] *= c1; }
         st.m0 = n0; st.m1 = n1;
     }
     uint32_t wh[2][2], wl[2][2];                                  // weights^T, B fragments per 16 tokens
@@ -276,40 +301,43 @@ __device__ __forceinline__ void attn_tile(const unsigned char* kb, const unsigne
     // ---- out^T += centroids^T . weights^T
 #pragma unroll
     for (int m = 0; m < 2; ++m) {
-        // coordinate-wise interleave of the token pairs (2t, 2t+1) and (2t+8, 2t+9)
-        // word g of tokens 16m + {2t, 2t+1, 2t+8, 2t+9}
-        const unsigned char* vrow = vb + 16 * m * 48;
-        const uint32_t v0 = *reinterpret_cast<const uint32_t*>(vrow), v1 = *reinterpret_cast<const uint32_t*>(vrow + 48);
-        const uint32_t v2 = *reinterpret_cast<const uint32_t*>(vrow + 8 * 48), v3 = *reinterpret_cast<const uint32_t*>(vrow + 9 * 48);
-        const uint32_t ea = (v0 & 0x0F0F0F0Fu) | ((v1 << 4) & 0xF0F0F0F0u);   // even coordinates
-        const uint32_t oa = ((v0 >> 4) & 0x0F0F0F0Fu) | (v1 & 0xF0F0F0F0u);   // odd coordinates
-        const uint32_t eb = (v2 & 0x0F0F0F0Fu) | ((v3 << 4) & 0xF0F0F0F0u);
-        const uint32_t ob = ((v2 >> 4) & 0x0F0F0F0Fu) | (v3 & 0xF0F0F0F0u);
-        uint32_t ch[4][4], cl[4][4];                               // [coordinate block][fragment register]
 #pragma unroll
-        for (int mb = 0; mb < 4; ++mb) {
-            const unsigned char* e0 = table + __byte_perm(ea, slot, 0x5504 | (mb << 4));
-            const unsigned char* e1 = table + __byte_perm(oa, slot, 0x5504 | (mb << 4));
-            const unsigned char* e2 = table + __byte_perm(eb, slot, 0x5504 | (mb << 4));
-            const unsigned char* e3 = table + __byte_perm(ob, slot, 0x5504 | (mb << 4));
-            ch[mb][0] = *reinterpret_cast<const uint32_t*>(e0);
-            ch[mb][1] = *reinterpret_cast<const uint32_t*>(e1);
-            ch[mb][2] = *reinterpret_cast<const uint32_t*>(e2);
-            ch[mb][3] = *reinterpret_cast<const uint32_t*>(e3);
-            if (!FAST) {
-                cl[mb][0] = *reinterpret_cast<const uint32_t*>(e0 + 128);
-                cl[mb][1] = *reinterpret_cast<const uint32_t*>(e1 + 128);
-                cl[mb][2] = *reinterpret_cast<const uint32_t*>(e2 + 128);
-                cl[mb][3] = *reinterpret_cast<const uint32_t*>(e3 + 128);
+        for (int half = 0; half < D / 64; ++half) {
+            // coordinate-wise interleave of the token pairs (2t, 2t+1) and (2t+8, 2t+9)
+            // word g (+ 8 per half) of tokens 16m + {2t, 2t+1, 2t+8, 2t+9}: coordinates 64 * half + 8g ...
+            const unsigned char* vrow = vb + 16 * m * G::VPITCH + half * 32;
+            const uint32_t v0 = *reinterpret_cast<const uint32_t*>(vrow), v1 = *reinterpret_cast<const uint32_t*>(vrow + G::VPITCH);
+            const uint32_t v2 = *reinterpret_cast<const uint32_t*>(vrow + 8 * G::VPITCH), v3 = *reinterpret_cast<const uint32_t*>(vrow + 9 * G::VPITCH);
+            const uint32_t ea = (v0 & 0x0F0F0F0Fu) | ((v1 << 4) & 0xF0F0F0F0u);   // even coordinates
+            const uint32_t oa = ((v0 >> 4) & 0x0F0F0F0Fu) | (v1 & 0xF0F0F0F0u);   // odd coordinates
+            const uint32_t eb = (v2 & 0x0F0F0F0Fu) | ((v3 << 4) & 0xF0F0F0F0u);
+            const uint32_t ob = ((v2 >> 4) & 0x0F0F0F0Fu) | (v3 & 0xF0F0F0F0u);
+            uint32_t ch[4][4], cl[4][4];                               // [coordinate block][fragment register]
+#pragma unroll
+            for (int mb = 0; mb < 4; ++mb) {
+                const unsigned char* e0 = table + __byte_perm(ea, slot, 0x5504 | (mb << 4));
+                const unsigned char* e1 = table + __byte_perm(oa, slot, 0x5504 | (mb << 4));
+                const unsigned char* e2 = table + __byte_perm(eb, slot, 0x5504 | (mb << 4));
+                const unsigned char* e3 = table + __byte_perm(ob, slot, 0x5504 | (mb << 4));
+                ch[mb][0] = *reinterpret_cast<const uint32_t*>(e0);
+                ch[mb][1] = *reinterpret_cast<const uint32_t*>(e1);
+                ch[mb][2] = *reinterpret_cast<const uint32_t*>(e2);
+                ch[mb][3] = *reinterpret_cast<const uint32_t*>(e3);
+                if (!FAST) {
+                    cl[mb][0] = *reinterpret_cast<const uint32_t*>(e0 + 128);
+                    cl[mb][1] = *reinterpret_cast<const uint32_t*>(e1 + 128);
+                    cl[mb][2] = *reinterpret_cast<const uint32_t*>(e2 + 128);
+                    cl[mb][3] = *reinterpret_cast<const uint32_t*>(e3 + 128);
+                }
             }
-        }
 #pragma unroll
-        for (int mb = 0; mb < 4; ++mb) mma_bf16(st.acc[mb], ch[mb][0], ch[mb][1], ch[mb][2], ch[mb][3], wh[m][0], wh[m][1]);
-        if (!FAST) {
+            for (int mb = 0; mb < 4; ++mb) mma_bf16(st.acc[4 * half + mb], ch[mb][0], ch[mb][1], ch[mb][2], ch[mb][3], wh[m][0], wh[m][1]);
+            if (!FAST) {
 #pragma unroll
-            for (int mb = 0; mb < 4; ++mb) mma_bf16(st.acc[mb], ch[mb][0], ch[mb][1], ch[mb][2], ch[mb][3], wl[m][0], wl[m][1]);
+                for (int mb = 0; mb < 4; ++mb) mma_bf16(st.acc[4 * half + mb], ch[mb][0], ch[mb][1], ch[mb][2], ch[mb][3], wl[m][0], wl[m][1]);
 #pragma unroll
-            for (int mb = 0; mb < 4; ++mb) mma_bf16(st.acc[mb], cl[mb][0], cl[mb][1], cl[mb][2], cl[mb][3], wh[m][0], wh[m][1]);
+                for (int mb = 0; mb < 4; ++mb) mma_bf16(st.acc[4 * half + mb], cl[mb][0], cl[mb][1], cl[mb][2], cl[mb][3], wh[m][0], wh[m][1]);
+            }
         }
     }
 }
@@ -359,27 +387,30 @@ __device__ __forceinline__ void fold_group(uint32_t lo2, uint32_t hi2, const flo
     bias1 = __shfl_sync(0xFFFFFFFFu, b, 8 * t + 4);       // of query 2t + 1
 }
 
-// TurboQuant keys: the rotated query q' = qscale / 8 * H D q of query g as B fragments (three bf16 parts,
-// same places as fold_group's).  Lane (g, t) owns channels 16t ... 16t + 15: the Walsh-Hadamard stages of
-// channel bits 0...3 run in registers, those of bits 4 and 5 between the four lanes of a query.  Fragment
-// slots follow the A side of the TurboQuant-key product: slots (2t, 2t+1) of block KB are channels
-// 16t + 2KB, + 1 (byte KB of the row's word 2t), slots (2t+8, 2t+9) channels 16t + 8 + 2KB, + 1.
-__device__ __forceinline__ void rotate_query(const float* __restrict__ qrow, float qscale, uint32_t neg_lo, uint32_t neg_hi,
+// TurboQuant keys: the rotated query q' = qscale / sqrt(D) * H D q of query g as B fragments (three bf16
+// parts, same places as fold_group's).  Lane (g, t) owns the D/4 channels from t * D/4 on: the
+// Walsh-Hadamard stages of the low channel bits run in registers, those of the two top bits between the
+// four lanes of a query.  Fragment slots follow the A side of the TurboQuant-key product: in block KB,
+// slots (2t, 2t+1) are the lane's channels 16 (KB / 4) + 2 (KB % 4), + 1 (byte KB % 4 of its word
+// 2 (KB / 4)), slots (2t+8, 2t+9) the same 8 channels further on (the next word).
+template <int D>
+__device__ __forceinline__ void rotate_query(const float* __restrict__ qrow, float qscale, float rs, const uint32_t (&kneg)[4],
                                              uint2* qf, int lane, int t) {
-    float x[16];
+    constexpr int N = D / 4, NKB = D / 16;
+    float x[N];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float4 qv = __ldg(reinterpret_cast<const float4*>(qrow + 16 * t + 4 * i));
+    for (int i = 0; i < N / 4; ++i) {
+        const float4 qv = __ldg(reinterpret_cast<const float4*>(qrow + N * t + 4 * i));
         x[4 * i] = qv.x; x[4 * i + 1] = qv.y; x[4 * i + 2] = qv.z; x[4 * i + 3] = qv.w;
     }
-    const uint32_t neg = t < 2 ? neg_lo : neg_hi;
-    const int shift = (16 * t) & 31;
+    const uint32_t neg = kneg[(N * t) >> 5];
+    const int shift = (N * t) & 31;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) x[i] = flip_if(x[i], neg, shift + i);
+    for (int i = 0; i < N; ++i) x[i] = flip_if(x[i], neg, shift + i);
 #pragma unroll
-    for (int h = 1; h < 16; h <<= 1)
+    for (int h = 1; h < N; h <<= 1)
 #pragma unroll
-        for (int i = 0; i < 16; ++i)
+        for (int i = 0; i < N; ++i)
             if (!(i & h)) {
                 const float a = x[i], b = x[i | h];
                 x[i] = a + b;
@@ -388,43 +419,46 @@ __device__ __forceinline__ void rotate_query(const float* __restrict__ qrow, flo
 #pragma unroll
     for (int m = 1; m < 4; m <<= 1)
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
+        for (int i = 0; i < N; ++i) {
             const float o = __shfl_xor_sync(0xFFFFFFFFu, x[i], m);
             x[i] = (lane & m) ? o - x[i] : x[i] + o;
         }
-    const float sc = qscale * 0.125f;
+    const float sc = qscale * rs;
     __syncwarp();
 #pragma unroll
-    for (int kb = 0; kb < 4; ++kb) {
+    for (int kb = 0; kb < NKB; ++kb) {
+        const int i0 = 16 * (kb >> 2) + 2 * (kb & 3);
         uint2 h, m, l;
-        split_pair3(x[2 * kb] * sc, x[2 * kb + 1] * sc, h.x, m.x, l.x);
-        split_pair3(x[8 + 2 * kb] * sc, x[9 + 2 * kb] * sc, h.y, m.y, l.y);
-        qf[(0 * 4 + kb) * 32 + lane] = h;
-        qf[(1 * 4 + kb) * 32 + lane] = m;
-        qf[(2 * 4 + kb) * 32 + lane] = l;
+        split_pair3(x[i0] * sc, x[i0 + 1] * sc, h.x, m.x, l.x);
+        split_pair3(x[i0 + 8] * sc, x[i0 + 9] * sc, h.y, m.y, l.y);
+        qf[(0 * NKB + kb) * 32 + lane] = h;
+        qf[(1 * NKB + kb) * 32 + lane] = m;
+        qf[(2 * NKB + kb) * 32 + lane] = l;
     }
     __syncwarp();
 }
 
-template <bool FAST, bool TK>
-__global__ void __launch_bounds__(AT_THREADS, 1)
+template <int D, bool FAST, bool TK>
+__global__ void __launch_bounds__(AttnGeom<D>::THREADS, 1)
 attention_partial_kernel(const __grid_constant__ AttentionParams p) {
+    static_assert(D == 64 || TK, "per-channel keys are handled at head dimension 64 only");
+    typedef AttnGeom<D> G;
+    constexpr int AT_WARPS = G::WARPS, AT_STAGE_BYTES = G::STAGE_BYTES, AT_PART_FLOATS = G::PART_FLOATS;
     extern __shared__ __align__(1024) unsigned char smem[];
     // byte (na | nb << 4) of two tokens' codes, lane slot l: the bf16 pair (c[na], c[nb]) as hi parts at
     // byte * 256 + l * 4 and lo parts 128 bytes further (every lane reads its own bank)
     unsigned char* table = smem;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    float* gstep = reinterpret_cast<float*>(smem + CD_TABLE_BYTES + warp * AT_WARP_SMEM);   // [64]
+    float* gstep = reinterpret_cast<float*>(smem + CD_TABLE_BYTES + warp * G::WARP_SMEM);   // [64]
     float* goff = gstep + 64;                                                               // [64] lo - 16 * step
-    uint2* qf = reinterpret_cast<uint2*>(goff + 64);                                        // [3 parts][4 blocks][32 lanes]
-    unsigned char* stage0 = reinterpret_cast<unsigned char*>(qf + 12 * 32);                 // two tile buffers
+    uint2* qf = reinterpret_cast<uint2*>(goff + 64);                                        // [3 parts][blocks][32 lanes]
+    unsigned char* stage0 = reinterpret_cast<unsigned char*>(qf + 3 * G::NKB * 32);         // two tile buffers
     const int R = p.n_queries;
     const uint32_t slot = (uint32_t)lane * 4u;
 
-    if (threadIdx.x < 256) {
+    for (int e = threadIdx.x; e < 256; e += G::THREADS) {
         // one table entry per thread (256 code pairs), written to its 32 lane slots
-        const int e = threadIdx.x;
         uint32_t hi, lo;
         split_pair(p.book.c[e & 15], p.book.c[e >> 4], hi, lo);
         uint4* row = reinterpret_cast<uint4*>(table + e * 256);
@@ -456,21 +490,21 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
         const unsigned char* v_codes = p.v_codes + seg * p.v_codes_seg;
         const float* v_norms = reinterpret_cast<const float*>(p.v_norms + seg * p.v_norms_seg);
         // this lane's query row (query g); rows beyond n_queries repeat query 0 and are never written out
-        const float* qrow = p.q + (seg * R + (g < R ? g : 0)) * 64;
+        const float* qrow = p.q + (seg * R + (g < R ? g : 0)) * D;
         const float qscale = p.scale_log2;
 
-        AttnState st;
+        AttnState<D> st;
         st.m0 = st.m1 = -INFINITY;
         st.l0 = st.l1 = 0.0f;
 #pragma unroll
-        for (int mb = 0; mb < 4; ++mb)
+        for (int mb = 0; mb < G::NKB; ++mb)
 #pragma unroll
             for (int i = 0; i < 4; ++i) st.acc[mb][i] = 0.0f;
         float bias0 = 0.0f, bias1 = 0.0f;
 
         // the first tile is on its way before anything else of the run is fetched
         __syncwarp();
-        issue_attn_tile(stage0, k_codes, v_codes, v_norms, k_norms, w_begin, w_end - w_begin, lane);
+        issue_attn_tile<D>(stage0, k_codes, v_codes, v_norms, k_norms, w_begin, w_end - w_begin, lane);
 
         // per-channel keys: the ranges of the first group; those of the following group are fetched a
         // group ahead.  TurboQuant keys: the query is rotated once, here.
@@ -480,21 +514,21 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
         uint32_t lo2 = 0, hi2 = 0;
         bool fold = !TK;
         if (TK) {
-            rotate_query(qrow, qscale, p.kneg_lo, p.kneg_hi, qf, lane, t);
+            rotate_query<D>(qrow, qscale, p.rs, p.kneg, qf, lane, t);
         } else {
             lo2 = ldg_stream32(reinterpret_cast<const uint32_t*>(k_ranges + (int64_t)group * 128));
             hi2 = ldg_stream32(reinterpret_cast<const uint32_t*>(k_ranges + (int64_t)group * 128 + 64));
         }
 
         // this lane's places in tile buffer 0; buffer 1 is AT_STAGE_BYTES further
-        const unsigned char* kb = stage0 + g * 32 + t * 8;
-        const unsigned char* vb = stage0 + AT_STAGE_K + 2 * t * 48 + g * 4;
-        const unsigned char* nb = stage0 + AT_STAGE_K + AT_STAGE_V + g * 4;
+        const unsigned char* kb = stage0 + g * G::ROWB + t * (G::ROWB / 4);
+        const unsigned char* vb = stage0 + G::STAGE_K + 2 * t * G::VPITCH + g * 4;
+        const unsigned char* nb = stage0 + G::STAGE_K + G::STAGE_V + g * 4;
 #define PITCH_TILE(BUF)                                                                                  \
         {                                                                                               \
             const int nvalid = w_end - t0;                            /* >= 32 for a whole tile */      \
             if (nvalid > 32) {                                                                          \
-                issue_attn_tile(stage0 + (1 - BUF) * AT_STAGE_BYTES, k_codes, v_codes, v_norms, k_norms, t0 + 32, nvalid - 32, lane); \
+                issue_attn_tile<D>(stage0 + (1 - BUF) * AT_STAGE_BYTES, k_codes, v_codes, v_norms, k_norms, t0 + 32, nvalid - 32, lane); \
                 cp_async_wait<1>();                                                                     \
             } else {                                                                                    \
                 cp_async_wait<0>();                                                                     \
@@ -509,7 +543,7 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
                     hi2 = ldg_stream32(reinterpret_cast<const uint32_t*>(k_ranges + (int64_t)(group + 1) * 128 + 64)); \
                 }                                                                                       \
             }                                                                                           \
-            attn_tile<FAST, TK>(kb + BUF * AT_STAGE_BYTES, vb + BUF * AT_STAGE_BYTES, nb + BUF * AT_STAGE_BYTES, st, qf + lane,  \
+            attn_tile<D, FAST, TK>(kb + BUF * AT_STAGE_BYTES, vb + BUF * AT_STAGE_BYTES, nb + BUF * AT_STAGE_BYTES, st, qf + lane,  \
                       bias0, bias1, nvalid, table, slot, g);                                            \
             __syncwarp();                                             /* this buffer is refilled two tiles on */ \
         }
@@ -532,45 +566,55 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
         if (2 * t < R) {
             if (g == 0) { d0[0] = st.m0; d0[1] = st.l0; }
 #pragma unroll
-            for (int mb = 0; mb < 4; ++mb)                            // coordinates 8g + 2mb and 8g + 2mb + 1
-                *reinterpret_cast<float2*>(d0 + 2 + 8 * g + 2 * mb) = make_float2(st.acc[mb][0], st.acc[mb][2]);
+            for (int mb = 0; mb < G::NKB; ++mb)                       // coordinates 64 (mb / 4) + 8g + 2 (mb % 4) and the next
+                *reinterpret_cast<float2*>(d0 + 2 + 64 * (mb >> 2) + 8 * g + 2 * (mb & 3)) = make_float2(st.acc[mb][0], st.acc[mb][2]);
         }
         if (2 * t + 1 < R) {
             if (g == 0) { d1[0] = st.m1; d1[1] = st.l1; }
 #pragma unroll
-            for (int mb = 0; mb < 4; ++mb)
-                *reinterpret_cast<float2*>(d1 + 2 + 8 * g + 2 * mb) = make_float2(st.acc[mb][1], st.acc[mb][3]);
+            for (int mb = 0; mb < G::NKB; ++mb)
+                *reinterpret_cast<float2*>(d1 + 2 + 64 * (mb >> 2) + 8 * g + 2 * (mb & 3)) = make_float2(st.acc[mb][1], st.acc[mb][3]);
         }
     }
 }
 
 // grid = (n_queries, segments), 8 warps: warp w merges runs w, w + 8, ... of its (segment, query),
-// lane l owning coordinates 2l and 2l + 1; warp 0 merges the eight, normalises and un-rotates.
+// lane l owning coordinates l * D/32 ... ; warp 0 merges the eight, normalises and un-rotates.
+template <int D>
 __global__ void __launch_bounds__(32 * AT_COMBINE_WARPS)
 attention_combine_kernel(const __grid_constant__ AttentionParams p) {
-    __shared__ float part[AT_COMBINE_WARPS][AT_PART_FLOATS];
+    constexpr int PF = AttnGeom<D>::PART_FLOATS, E = D / 32;       // coordinates per lane: 2 or 4
+    __shared__ float part[AT_COMBINE_WARPS][PF];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int r = blockIdx.x;
     const int64_t seg = blockIdx.y;
     const int R = p.n_queries;
     asm volatile("griddepcontrol.wait;" ::: "memory");       // the partial results of the kernel before this one
-    const float* base = p.work + (seg * p.splits * R + r) * AT_PART_FLOATS;
-    const int64_t stride = (int64_t)R * AT_PART_FLOATS;
+    const float* base = p.work + (seg * p.splits * R + r) * PF;
+    const int64_t stride = (int64_t)R * PF;
     float mm = -INFINITY;
-    float2 a = make_float2(0.0f, 0.0f);
+    float a[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e) a[e] = 0.0f;
     float ll = 0.0f;
     for (int s0 = warp; s0 < p.splits; s0 += 4 * AT_COMBINE_WARPS) {
         // four runs in flight per warp
         float ms[4], ls[4];
-        float2 v[4];
+        float v[4][E];
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const int s = s0 + k * AT_COMBINE_WARPS;
-            ms[k] = -INFINITY; ls[k] = 0.0f; v[k] = make_float2(0.0f, 0.0f);
+            ms[k] = -INFINITY; ls[k] = 0.0f;
+#pragma unroll
+            for (int e = 0; e < E; ++e) v[k][e] = 0.0f;
             if (s < p.splits) {
                 const float* src = base + s * stride;
                 ms[k] = src[0]; ls[k] = src[1];
-                v[k] = *reinterpret_cast<const float2*>(src + 2 + 2 * lane);
+#pragma unroll
+                for (int e = 0; e < E; e += 2) {
+                    const float2 f = *reinterpret_cast<const float2*>(src + 2 + E * lane + e);
+                    v[k][e] = f.x; v[k][e + 1] = f.y;
+                }
             }
         }
 #pragma unroll
@@ -578,44 +622,57 @@ attention_combine_kernel(const __grid_constant__ AttentionParams p) {
             if (ms[k] == -INFINITY) continue;                             // beyond the last run
             const float mn = fmaxf(mm, ms[k]);
             const float fo = fast_exp2(mm - mn), fn = fast_exp2(ms[k] - mn);
-            a.x = fmaf(v[k].x, fn, a.x * fo);
-            a.y = fmaf(v[k].y, fn, a.y * fo);
+#pragma unroll
+            for (int e = 0; e < E; ++e) a[e] = fmaf(v[k][e], fn, a[e] * fo);
             ll = fmaf(ls[k], fn, ll * fo);
             mm = mn;
         }
     }
     if (lane == 0) { part[warp][0] = mm; part[warp][1] = ll; }
-    *reinterpret_cast<float2*>(&part[warp][2 + 2 * lane]) = a;
+#pragma unroll
+    for (int e = 0; e < E; ++e) part[warp][2 + E * lane + e] = a[e];
     __syncthreads();
     if (warp != 0) return;
     mm = -INFINITY;
 #pragma unroll
     for (int w = 0; w < AT_COMBINE_WARPS; ++w) mm = fmaxf(mm, part[w][0]);
-    a = make_float2(0.0f, 0.0f);
+#pragma unroll
+    for (int e = 0; e < E; ++e) a[e] = 0.0f;
     ll = 0.0f;
 #pragma unroll
     for (int w = 0; w < AT_COMBINE_WARPS; ++w) {
         const float f = part[w][0] == -INFINITY ? 0.0f : fast_exp2(part[w][0] - mm);   // a warp without a run
-        const float2 v = *reinterpret_cast<const float2*>(&part[w][2 + 2 * lane]);
-        a.x = fmaf(v.x, f, a.x);
-        a.y = fmaf(v.y, f, a.y);
+#pragma unroll
+        for (int e = 0; e < E; ++e) a[e] = fmaf(part[w][2 + E * lane + e], f, a[e]);
         ll = fmaf(part[w][1], f, ll);
     }
-    // normalise, then rotate back once: H over 64 coordinates (two per lane), 1/8, sign diagonal
-    const float inv = 0.125f / ll;
-    float x0 = a.x + a.y, x1 = a.x - a.y;                    // stage 1 inside the lane
+    // normalise, then rotate back once: H over D coordinates (E per lane), 1/sqrt(D), sign diagonal
+    const float inv = p.rs / ll;
 #pragma unroll
-    for (int mbit = 1; mbit < 32; mbit <<= 1) {              // stages 2 ... 32 across lanes
-        const float o0 = __shfl_xor_sync(0xFFFFFFFFu, x0, mbit), o1 = __shfl_xor_sync(0xFFFFFFFFu, x1, mbit);
+    for (int h = 1; h < E; h <<= 1)                          // stages inside the lane
+#pragma unroll
+        for (int i = 0; i < E; ++i)
+            if (!(i & h)) {
+                const float x = a[i], y = a[i | h];
+                a[i] = x + y;
+                a[i | h] = x - y;
+            }
+#pragma unroll
+    for (int mbit = 1; mbit < 32; mbit <<= 1) {              // stages across lanes
         const bool upper = (lane & mbit) != 0;
-        x0 = upper ? o0 - x0 : x0 + o0;
-        x1 = upper ? o1 - x1 : x1 + o1;
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            const float o = __shfl_xor_sync(0xFFFFFFFFu, a[e], mbit);
+            a[e] = upper ? o - a[e] : a[e] + o;
+        }
     }
-    const uint32_t neg = lane < 16 ? p.neg_lo : p.neg_hi;
-    const int bit = (2 * lane) & 31;
-    x0 = flip_if(x0 * inv, neg, bit);
-    x1 = flip_if(x1 * inv, neg, bit + 1);
-    *reinterpret_cast<float2*>(p.out + (seg * R + r) * 64 + 2 * lane) = make_float2(x0, x1);
+    const uint32_t neg = p.neg[(E * lane) >> 5];
+    const int bit = (E * lane) & 31;
+#pragma unroll
+    for (int e = 0; e < E; ++e) a[e] = flip_if(a[e] * inv, neg, bit + e);
+#pragma unroll
+    for (int e = 0; e < E; e += 2)
+        *reinterpret_cast<float2*>(p.out + (seg * R + r) * D + E * lane + e) = make_float2(a[e], a[e + 1]);
 }
 
 }  // namespace pitch

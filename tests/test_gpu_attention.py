@@ -102,12 +102,11 @@ def test_bf16_operand_mode_is_as_accurate_as_attention_over_the_bf16_cache(q, S,
         cache.attend(Qd, precision="float8")
 
 
-def build_turbo_cache(q, S, T, seed):
-    """Keys and values both TurboQuant 4-bit, d=64 (with different rotation seeds)."""
+def build_turbo_cache(q, S, T, seed, d=64):
+    """Keys and values both TurboQuant 4-bit (with different rotation seeds)."""
     import torch
     from pitch_b200 import KVCache, QuantConfig
     rng = np.random.default_rng(seed)
-    d = 64
     K = (rng.standard_normal((S, T, d)) * np.exp(0.4 * rng.standard_normal((S, T, 1)))).astype(np.float32)
     V = (rng.standard_normal((S, T, d)) * np.exp(0.5 * rng.standard_normal((S, T, 1)))).astype(np.float32)
     cache = KVCache(S, d, T, QuantConfig("turboQuant", d, 4, seed=777), QuantConfig("turboQuant", d, 4), out_dtype="float32", pitch=q)
@@ -119,23 +118,25 @@ def spec_decoded_turbo(cache, s):
     T, d = cache.tokens, cache.dim
     out = []
     for pl in cache.planes:
-        c = pl.codes[s, :T * 32].cpu().numpy()
+        c = pl.codes[s, :T * (d // 2)].cpu().numpy()
         n = pl.side[s, :T].cpu().numpy().astype(np.float64)
         out.append(np.asarray(spec_np.turbo_decode(spec_np.unpack_codes(c.tobytes(), T, d, 4), n, 4, pl.config.seed), dtype=np.float64))
     return out
 
 
+@pytest.mark.parametrize("d", [64, 128])
 @pytest.mark.parametrize("S,T,R,scale", [(3, 333, 7, None), (2, 5000, 1, None), (1, 31, 8, None), (2, 9000, 5, 1.0), (1, 1, 3, None)])
-def test_turboquant_keys_match_attention_over_spec_decoded_cache(q, S, T, R, scale):
-    """A cache whose keys are TurboQuant too: the query is rotated once instead of un-rotating every key."""
+def test_turboquant_keys_match_attention_over_spec_decoded_cache(q, S, T, R, scale, d):
+    """A cache whose keys are TurboQuant too (dimension 64, and 128 as in a Llama-3-70B-shaped cache):
+    the query is rotated once instead of un-rotating every key."""
     import torch
-    cache, rng = build_turbo_cache(q, S, T, seed=400 + T)
-    Q = rng.standard_normal((S, R, 64)).astype(np.float32)
+    cache, rng = build_turbo_cache(q, S, T, seed=400 + T, d=d)
+    Q = rng.standard_normal((S, R, d)).astype(np.float32)
     Qd = torch.from_numpy(Q).to(q.device)
     got = cache.attend(Qd, scale=scale).cpu().numpy().astype(np.float64)
     fast = cache.attend(Qd, scale=scale, precision="bfloat16").cpu().numpy().astype(np.float64)
     assert np.isfinite(got).all() and np.isfinite(fast).all()
-    sc = 64 ** -0.5 if scale is None else scale
+    sc = d ** -0.5 if scale is None else scale
     for s in range(S):
         K, V = spec_decoded_turbo(cache, s)
         ref = attention64(Q[s].astype(np.float64), K, V, sc)
