@@ -423,18 +423,19 @@ def run_ours(args) -> None:
     if not args.kernel_only:
         e2e_steps = max(3, min(20, K))
         cache.truncate(TOKENS - GROUP)                      # make room again (a group boundary)
-        hk = torch.randn((e2e_steps + 1, segments, 1, DIM)).pin_memory()
-        hv = torch.randn((e2e_steps + 1, segments, 1, DIM)).pin_memory()
+        hkv = torch.randn((e2e_steps + 1, 2, segments, 1, DIM)).pin_memory()       # new keys and values of every step
+        dkv = torch.empty((2, segments, 1, DIM), device=dev)                        # where a step's new token lands on the device
+        dnew = torch.empty((2, segments, DIM), dtype=torch.bfloat16, device=dev)
         host_new = torch.empty((2, segments, DIM), dtype=torch.bfloat16).pin_memory()
         stream = torch.cuda.current_stream(dev)
 
         def e2e_step(i):
-            dk = hk[i].to(dev, non_blocking=True)
-            dv = hv[i].to(dev, non_blocking=True)
-            ko, vo = cache.step(dk, dv)
-            host_new[0].copy_(ko[:, -1], non_blocking=True)
-            host_new[1].copy_(vo[:, -1], non_blocking=True)
-            stream.synchronize()                            # the host holds the step's result
+            dkv.copy_(hkv[i], non_blocking=True)                # host -> device: this step's inputs
+            ko, vo = cache.step(dkv[0], dkv[1])
+            dnew[0].copy_(ko[:, -1])                            # the newly decoded token of every segment ...
+            dnew[1].copy_(vo[:, -1])
+            host_new.copy_(dnew, non_blocking=True)             # ... device -> host
+            stream.synchronize()                                # the host holds the step's result
             return cache.tokens
 
         e2e_step(0)
@@ -456,7 +457,8 @@ def run_ours(args) -> None:
             t0 = time.perf_counter()
             fb = 0
             for i in range(n_full):
-                cache.step(hk[i].to(dev, non_blocking=True), hv[i].to(dev, non_blocking=True))
+                dkv.copy_(hkv[i], non_blocking=True)
+                cache.step(dkv[0], dkv[1])
                 host_k.copy_(cache.planes[0].out, non_blocking=True)
                 host_v.copy_(cache.planes[1].out, non_blocking=True)
                 stream.synchronize()
