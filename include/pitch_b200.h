@@ -263,6 +263,9 @@ int pitch_enqueue_cache_step(const pitch_cache_desc* desc, const pitch_append_sr
  *   - One array serves every call.  It keeps the newest group of ONE cache per GPU: feed every
  *     token of that group through this entry point, and switch to another cache only when
  *     tokens is a multiple of the group size (otherwise PITCH_ERR_CONFIGURATION_MISMATCH).
+ *     The cache is recognised by plane 0's `codes` pointer and its token count, nothing more: a
+ *     cache that was freed and another one allocated at the same address and filled to the same
+ *     count would be taken for it, so start a new cache on a group boundary (tokens = 0 is one).
  *     Nothing in it needs to start at zero: a group's running range and rows are written before
  *     they are read.  Two calls that overlap on the GPU (different streams, or two host threads)
  *     race on the array; keep calls on one GPU stream-ordered. */

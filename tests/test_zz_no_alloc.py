@@ -98,3 +98,35 @@ def test_noalloc_append_python_helper_and_limits():
     Y = torch.zeros((segs, 1, d), device=q.device)
     with pytest.raises(PITCHError, match="built-in buffer holds"):
         append_noalloc(big, Y, Y)
+
+
+def test_noalloc_append_removes_the_key_bias_like_append():
+    """A cache built with ``key_bias`` takes the rotated bias off the new keys before encoding them;
+    the allocation-free helper must do the same, or ``decode`` would add back a bias that was never
+    removed.  Codes, norms and ranges must equal those of ``KVCache.append``, and so must the decoded keys."""
+    import torch
+    from pitch_b200 import ChannelQuantConfig, KVCache, PITCH, QuantConfig
+    from pitch_b200.noalloc import append_noalloc
+    q = PITCH()
+    rng = np.random.default_rng(101)
+    S, d, T = 4, 64, 150
+    inv = 10000.0 ** (-np.arange(0, d, 2, dtype=np.float64) / d)
+    ang = np.arange(256, dtype=np.float64)[:, None] * inv[None, :]
+    ang = np.concatenate([ang, ang], axis=1)
+    kb = tuple(torch.from_numpy(a).to(q.device) for a in ((5.0 * rng.standard_normal((S, d))).astype(np.float32),
+                                                          np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)))
+    K = torch.from_numpy((rng.standard_normal((S, T, d)) + 3).astype(np.float32)).to(q.device)
+    V = torch.from_numpy(rng.standard_normal((S, T, d)).astype(np.float32)).to(q.device)
+    for kcfg in (ChannelQuantConfig(d, 4, 64), QuantConfig("turboQuant", d, 4)):
+        ref = KVCache(S, d, 256, kcfg, QuantConfig("turboQuant", d, 4), pitch=q, key_bias=kb)
+        new = KVCache(S, d, 256, kcfg, QuantConfig("turboQuant", d, 4), pitch=q, key_bias=kb)
+        t = 0
+        for n_new in (64, 1, 30, 1, 33, 21):
+            k, v = K[:, t:t + n_new].contiguous(), V[:, t:t + n_new].contiguous()
+            ref.append(k, v)
+            append_noalloc(new, k, v)
+            t += n_new
+        torch.cuda.synchronize()
+        assert ref.tokens == new.tokens == T and _same(ref, new)
+        ra, rb = ref.decode(), new.decode()
+        assert torch.equal(ra[0], rb[0]) and torch.equal(ra[1], rb[1])
