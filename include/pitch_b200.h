@@ -282,8 +282,9 @@ int pitch_enqueue_cache_append_noalloc(const pitch_cache_desc* desc, const pitch
  * names this fusion ("decoding needs to move inside the attention kernel") as the work that has
  * to follow the whole-cache decode.
  *   Supported cache shapes: dim 64 with plane 0 (keys) per-channel, 4 bits, group size a multiple
- *   of 32, or TurboQuant, 4 bits; dim 128 with TurboQuant 4-bit keys (a Llama-3-70B-shaped cache);
- *   plane 1 (values) TurboQuant, 4 bits.  Anything else returns PITCH_ERR_INVALID_INPUT.  The
+ *   of 32, or TurboQuant, 4 bits; dim 128 with TurboQuant keys of 4 or 3 bits (a Llama-3-70B-shaped
+ *   cache); plane 1 (values) TurboQuant, 4 bits (3 bits where the keys have 3).  Anything else
+ *   returns PITCH_ERR_INVALID_INPUT.  The
  *   planes' `out` pointers are not used and may be null.
  *   queries, out: float32 [segments][n_queries][dim], 16-byte aligned, device memory.
  *   workspace: device scratch of at least pitch_cache_attention_workspace(desc, n_queries)

@@ -249,29 +249,28 @@ def bench_cfg5(q, bits, reps, segments=80, tokens=131072, gate=None):
     yield row("cfg5-shard", "whole-cache decode", t, 2 * segments * tokens, "vectors", nbytes,
               {"method": "turboQuant", "dim": d, "bits": bits, "segments": segments, "tokens": tokens, "out_dtype": "float16",
                "decode_output_GB_per_s": round(cache.decoded_bytes() / t / 1e9, 1), "parity": parity})
-    if bits == 4:
-        # attention straight from this shard (8 query heads per KV head, as Llama-3-70B has), gated against
-        # float64 attention over one segment decoded by the stand-alone decoder
-        g = torch.Generator(device=q.device)
-        g.manual_seed(55)
-        qs = torch.randn((segments, 8, d), generator=g, device=q.device)
-        got = cache.attend(qs)
-        rk = torch.empty((tokens, d), dtype=torch.float32, device=q.device)
-        rv = torch.empty((tokens, d), dtype=torch.float32, device=q.device)
-        s = segments // 2
-        q.enqueue_decode(cache.planes[0].codes[s], cache.planes[0].side[s], rk, tokens, cfg)
-        q.enqueue_decode(cache.planes[1].codes[s], cache.planes[1].side[s], rv, tokens, cfg)
-        ref = torch.softmax((qs[s].double() @ rk.double().T) * d ** -0.5, dim=1) @ rv.double()
-        worst = float(((got[s].double() - ref).norm(dim=1) / ref.norm(dim=1)).max())
-        if worst > 1e-4:
-            raise SystemExit(f"parity gate failed: cache attention at dim 128 differs from attention over the decoded cache by {worst}")
-        del rk, rv, ref
-        out = torch.empty_like(qs)
-        for prec in ("float32", "bfloat16"):
-            ta = time_launches(lambda i: cache.attend(qs, out=out, precision=prec), 1, reps)
-            yield row("cfg5-shard", f"attention from the compressed cache, {prec} operands", ta, segments * tokens, "kv_tokens",
-                      cache.stored_bytes(), {"dim": d, "bits": bits, "segments": segments, "tokens": tokens, "n_queries": 8, "precision": prec,
-                                             "parity": {"max_rel_l2_vs_float64_attention_over_decoded_cache": worst}})
+    # attention straight from this shard (8 query heads per KV head, as Llama-3-70B has), gated against
+    # float64 attention over one segment decoded by the stand-alone decoder
+    g = torch.Generator(device=q.device)
+    g.manual_seed(55)
+    qs = torch.randn((segments, 8, d), generator=g, device=q.device)
+    got = cache.attend(qs)
+    rk = torch.empty((tokens, d), dtype=torch.float32, device=q.device)
+    rv = torch.empty((tokens, d), dtype=torch.float32, device=q.device)
+    s = segments // 2
+    q.enqueue_decode(cache.planes[0].codes[s], cache.planes[0].side[s], rk, tokens, cfg)
+    q.enqueue_decode(cache.planes[1].codes[s], cache.planes[1].side[s], rv, tokens, cfg)
+    ref = torch.softmax((qs[s].double() @ rk.double().T) * d ** -0.5, dim=1) @ rv.double()
+    worst = float(((got[s].double() - ref).norm(dim=1) / ref.norm(dim=1)).max())
+    if worst > 1e-4:
+        raise SystemExit(f"parity gate failed: cache attention at dim 128 differs from attention over the decoded cache by {worst}")
+    del rk, rv, ref
+    out = torch.empty_like(qs)
+    for prec in ("float32", "bfloat16"):
+        ta = time_launches(lambda i: cache.attend(qs, out=out, precision=prec), 1, reps)
+        yield row("cfg5-shard", f"attention from the compressed cache, {prec} operands", ta, segments * tokens, "kv_tokens",
+                  cache.stored_bytes(), {"dim": d, "bits": bits, "segments": segments, "tokens": tokens, "n_queries": 8, "precision": prec,
+                                         "parity": {"max_rel_l2_vs_float64_attention_over_decoded_cache": worst}})
 
 
 def bench_attention(q, reps, segments=48, tokens=32768, n_queries=7):

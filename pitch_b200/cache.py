@@ -410,7 +410,8 @@ class KVCache:
         heads that share a KV head); returns float32 ``[segments, n_queries, dim]`` with
         ``softmax_t(scale * q . K_t) . V_t`` over the ``tokens`` tokens held.  ``scale`` defaults
         to ``1/sqrt(dim)``.  Supported: dim 64 with per-channel 4-bit keys (group size a multiple of
-        32) or TurboQuant 4-bit keys, dim 128 with TurboQuant 4-bit keys; TurboQuant 4-bit values.  ``precision="float32"`` keeps products float32-accurate
+        32) or TurboQuant 4-bit keys, dim 128 with TurboQuant keys and values of 4 or of 3 bits;
+        TurboQuant 4-bit values otherwise.  ``precision="float32"`` keeps products float32-accurate
         (about 1e-5 against attention over the float32-decoded cache); ``"bfloat16"`` uses operands
         as a bf16 pipeline has them (as accurate as attention over the cache decoded to bf16: a few
         bf16 roundings, up to about 5e-3) at half the tensor-core work.  Stream-ordered; the scratch buffer is kept by the

@@ -59,14 +59,17 @@ static int check_attention_shape(const pitch_cache_desc* d, int n_queries) {
     const pitch_plane& k = d->planes[0];
     const pitch_plane& v = d->planes[1];
     if (k.kind == PITCH_PLANE_TURBO) {
-        if (k.bits != 4) return fail(PITCH_ERR_INVALID_INPUT, "cache attention needs 4-bit keys");
+        if (k.bits != 4 && !(k.bits == 3 && d->dim == 128))
+            return fail(PITCH_ERR_INVALID_INPUT, "cache attention needs 4-bit keys (3-bit TurboQuant keys at dim 128 only)");
     } else if (d->dim != 64) {
         return fail(PITCH_ERR_INVALID_INPUT, "cache attention at dim 128 needs TurboQuant 4-bit keys");
     } else if (k.kind != PITCH_PLANE_CHANNEL || k.bits != 4 || k.group_size < 32 || k.group_size % 32 != 0 || k.group_size > PITCH_MAX_GROUP) {
         return fail(PITCH_ERR_INVALID_INPUT, "cache attention needs TurboQuant 4-bit keys, or per-channel 4-bit keys with a group size that is a multiple of 32");
     }
-    if (v.kind != PITCH_PLANE_TURBO || v.bits != 4)
-        return fail(PITCH_ERR_INVALID_INPUT, "cache attention needs TurboQuant 4-bit values");
+    if (v.kind != PITCH_PLANE_TURBO || (v.bits != 4 && !(v.bits == 3 && d->dim == 128 && k.kind == PITCH_PLANE_TURBO)))
+        return fail(PITCH_ERR_INVALID_INPUT, "cache attention needs TurboQuant 4-bit values (3-bit at dim 128 with TurboQuant keys)");
+    if (k.kind == PITCH_PLANE_TURBO && k.bits != v.bits)
+        return fail(PITCH_ERR_INVALID_INPUT, "cache attention needs keys and values of one width");
     return PITCH_OK;
 }
 
@@ -95,12 +98,12 @@ int pitch_enqueue_cache_attention(const pitch_cache_desc* d, const pitch_attenti
         if (!pl.codes || !pl.side) return fail(PITCH_ERR_INVALID_INPUT, "plane %d: null pointer", i);
         if (!aligned16(pl.codes) || !aligned16(pl.side) || (pl.codes_seg_stride & 15) || (pl.side_seg_stride & 15))
             return fail(PITCH_ERR_INVALID_INPUT, "plane %d: pointers and segment strides must be multiples of 16", i);
-        if (d->segments > 1 && (pl.codes_seg_stride < d->tokens * (d->dim / 2) || pl.side_seg_stride < plane_side_bytes(pl, d->dim, d->tokens)))
+        if (d->segments > 1 && (pl.codes_seg_stride < d->tokens * pitch_code_stride(d->dim, pl.bits) || pl.side_seg_stride < plane_side_bytes(pl, d->dim, d->tokens)))
             return fail(PITCH_ERR_INVALID_INPUT, "plane %d: a segment stride is smaller than one segment", i);
         // Codec.check (Sources/PITCH/Core/Codec.swift:42-46): the buffers must hold what the call reads
-        if (pl.codes_bytes < (d->segments - 1) * pl.codes_seg_stride + d->tokens * (d->dim / 2))
+        if (pl.codes_bytes < (d->segments - 1) * pl.codes_seg_stride + d->tokens * pitch_code_stride(d->dim, pl.bits))
             return fail(PITCH_ERR_INVALID_INPUT, "plane %d: codes buffer has %lld bytes; needs %lld", i, (long long)pl.codes_bytes,
-                        (long long)((d->segments - 1) * pl.codes_seg_stride + d->tokens * (d->dim / 2)));
+                        (long long)((d->segments - 1) * pl.codes_seg_stride + d->tokens * pitch_code_stride(d->dim, pl.bits)));
         if (pl.side_bytes < (d->segments - 1) * pl.side_seg_stride + plane_side_bytes(pl, d->dim, d->tokens))
             return fail(PITCH_ERR_INVALID_INPUT, "plane %d: side-information buffer has %lld bytes; needs %lld", i,
                         (long long)pl.side_bytes, (long long)((d->segments - 1) * pl.side_seg_stride + plane_side_bytes(pl, d->dim, d->tokens)));
@@ -138,21 +141,24 @@ int pitch_enqueue_cache_attention(const pitch_cache_desc* d, const pitch_attenti
     p.q = static_cast<const float*>(a->queries);
     p.work = static_cast<float*>(a->workspace);
     p.out = static_cast<float*>(a->out);
-    if (!book_get(d->dim, 4, p.book.c)) return fail(PITCH_ERR_INVALID_INPUT, "no TurboQuant codebook for dim %d, bits 4", d->dim);
+    const int vbits = d->planes[1].bits;
+    if (!book_get(d->dim, vbits, p.book.c)) return fail(PITCH_ERR_INVALID_INPUT, "no TurboQuant codebook for dim %d, bits %d", d->dim, vbits);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     {
         const bool wide = d->dim == 128;
-        const int smem = wide ? AttnGeom<128>::SMEM_BYTES : AttnGeom<64>::SMEM_BYTES;
+        const int smem = wide ? (vbits == 3 ? AttnGeom<128, 3>::SMEM_BYTES : AttnGeom<128>::SMEM_BYTES) : AttnGeom<64>::SMEM_BYTES;
         const int warps = wide ? AttnGeom<128>::WARPS : AttnGeom<64>::WARPS;
         static std::atomic<bool> configured[64];
         if (dev >= 0 && dev < 64 && !configured[dev].load(std::memory_order_acquire)) {
             const cudaFuncAttribute at = cudaFuncAttributeMaxDynamicSharedMemorySize;
-            if (cudaFuncSetAttribute(attention_partial_kernel<64, false, false>, at, AttnGeom<64>::SMEM_BYTES) != cudaSuccess ||
-                cudaFuncSetAttribute(attention_partial_kernel<64, true, false>, at, AttnGeom<64>::SMEM_BYTES) != cudaSuccess ||
-                cudaFuncSetAttribute(attention_partial_kernel<64, false, true>, at, AttnGeom<64>::SMEM_BYTES) != cudaSuccess ||
-                cudaFuncSetAttribute(attention_partial_kernel<64, true, true>, at, AttnGeom<64>::SMEM_BYTES) != cudaSuccess ||
-                cudaFuncSetAttribute(attention_partial_kernel<128, false, true>, at, AttnGeom<128>::SMEM_BYTES) != cudaSuccess ||
-                cudaFuncSetAttribute(attention_partial_kernel<128, true, true>, at, AttnGeom<128>::SMEM_BYTES) != cudaSuccess)
+            if (cudaFuncSetAttribute(attention_partial_kernel<64, 4, false, false>, at, AttnGeom<64>::SMEM_BYTES) != cudaSuccess ||
+                cudaFuncSetAttribute(attention_partial_kernel<64, 4, true, false>, at, AttnGeom<64>::SMEM_BYTES) != cudaSuccess ||
+                cudaFuncSetAttribute(attention_partial_kernel<64, 4, false, true>, at, AttnGeom<64>::SMEM_BYTES) != cudaSuccess ||
+                cudaFuncSetAttribute(attention_partial_kernel<64, 4, true, true>, at, AttnGeom<64>::SMEM_BYTES) != cudaSuccess ||
+                cudaFuncSetAttribute(attention_partial_kernel<128, 4, false, true>, at, AttnGeom<128>::SMEM_BYTES) != cudaSuccess ||
+                cudaFuncSetAttribute(attention_partial_kernel<128, 4, true, true>, at, AttnGeom<128>::SMEM_BYTES) != cudaSuccess ||
+                cudaFuncSetAttribute(attention_partial_kernel<128, 3, false, true>, at, AttnGeom<128, 3>::SMEM_BYTES) != cudaSuccess ||
+                cudaFuncSetAttribute(attention_partial_kernel<128, 3, true, true>, at, AttnGeom<128, 3>::SMEM_BYTES) != cudaSuccess)
                 return launch_status(false, "cache_attention (shared memory opt-in)");
             configured[dev].store(true, std::memory_order_release);
         }
@@ -173,15 +179,18 @@ int pitch_enqueue_cache_attention(const pitch_cache_desc* d, const pitch_attenti
         cfg.attrs = pdl;
         cfg.numAttrs = 1;
         const bool fast = a->precision == PITCH_ATTENTION_BF16;
-        if (wide) {
-            if (fast) cudaLaunchKernelEx(&cfg, attention_partial_kernel<128, true, true>, p);
-            else cudaLaunchKernelEx(&cfg, attention_partial_kernel<128, false, true>, p);
+        if (wide && vbits == 3) {
+            if (fast) cudaLaunchKernelEx(&cfg, attention_partial_kernel<128, 3, true, true>, p);
+            else cudaLaunchKernelEx(&cfg, attention_partial_kernel<128, 3, false, true>, p);
+        } else if (wide) {
+            if (fast) cudaLaunchKernelEx(&cfg, attention_partial_kernel<128, 4, true, true>, p);
+            else cudaLaunchKernelEx(&cfg, attention_partial_kernel<128, 4, false, true>, p);
         } else if (turbo_keys) {
-            if (fast) cudaLaunchKernelEx(&cfg, attention_partial_kernel<64, true, true>, p);
-            else cudaLaunchKernelEx(&cfg, attention_partial_kernel<64, false, true>, p);
+            if (fast) cudaLaunchKernelEx(&cfg, attention_partial_kernel<64, 4, true, true>, p);
+            else cudaLaunchKernelEx(&cfg, attention_partial_kernel<64, 4, false, true>, p);
         } else {
-            if (fast) cudaLaunchKernelEx(&cfg, attention_partial_kernel<64, true, false>, p);
-            else cudaLaunchKernelEx(&cfg, attention_partial_kernel<64, false, false>, p);
+            if (fast) cudaLaunchKernelEx(&cfg, attention_partial_kernel<64, 4, true, false>, p);
+            else cudaLaunchKernelEx(&cfg, attention_partial_kernel<64, 4, false, false>, p);
         }
         if ((st = launch_status(false, "cache_attention"))) return st;
         cfg.gridDim = dim3((unsigned)p.n_queries, (unsigned)p.segments);

@@ -60,13 +60,13 @@ namespace pitch {
 constexpr int AT_MAX_QUERIES = 8;
 constexpr int AT_COMBINE_WARPS = 8;
 
-// Sizes for head dimension D (64 or 128), 4-bit codes.
-template <int D> struct AttnGeom {
+// Sizes for head dimension D (64 or 128) and code width BITS (4; 3 at D = 128).
+template <int D, int BITS = 4> struct AttnGeom {
     static constexpr int WARPS = D == 64 ? 16 : 8;             // warps per CTA (one CTA per multiprocessor)
     static constexpr int THREADS = WARPS * 32;
     static constexpr int NKB = D / 16;                         // blocks of 16 channels / coordinates
-    static constexpr int ROWB = D / 2;                         // bytes of codes per token
-    static constexpr int VPITCH = ROWB + 16;                   // value rows padded by 16 bytes (bank spread)
+    static constexpr int ROWB = D * BITS / 8;                  // bytes of codes per token
+    static constexpr int VPITCH = ROWB + (BITS == 4 ? 16 : 8); // value rows padded (bank spread)
     static constexpr int PART_FLOATS = 2 + D;                  // per (segment, run, query): max, sum, D accumulators
     static constexpr int STAGE_K = 32 * ROWB;                  // a tile's key codes
     static constexpr int STAGE_V = 32 * VPITCH;                // a tile's value codes
@@ -134,24 +134,38 @@ __device__ __forceinline__ uint32_t key_pair(uint32_t w) {
 // Starts the asynchronous copy of a tile (32 tokens from `tok`, `nvalid` of them existing) into a
 // warp's tile buffer: key codes, value codes, norms.  Bytes of tokens that do not exist are
 // zero-filled without touching memory.  k_norms: the keys' norms (TurboQuant keys) or null.
-template <int D>
+template <int D, int BITS>
 __device__ __forceinline__ void issue_attn_tile(unsigned char* stage, const unsigned char* __restrict__ k_codes,
                                                 const unsigned char* __restrict__ v_codes,
                                                 const float* __restrict__ v_norms, const float* __restrict__ k_norms,
                                                 int tok, int nvalid, int lane) {
-    typedef AttnGeom<D> G;
-    constexpr int CPR = G::ROWB / 16;                               // 16-byte chunks per token row
+    typedef AttnGeom<D, BITS> G;
     const uint32_t base = (uint32_t)__cvta_generic_to_shared(stage);
     const unsigned char* ksrc = k_codes + (int64_t)tok * G::ROWB;
     const unsigned char* vsrc = v_codes + (int64_t)tok * G::ROWB;
+    if (BITS == 4) {
+        constexpr int CPR = G::ROWB / 16;                           // 16-byte chunks per token row
 #pragma unroll
-    for (int i = 0; i < CPR; ++i) {
-        const int c = lane + 32 * i, token = c / CPR;                // chunk c of the tile's code bytes
-        const int live = token < nvalid ? 16 : 0;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
-                     :: "r"(base + c * 16), "l"(live ? ksrc + c * 16 : ksrc), "r"(live) : "memory");
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
-                     :: "r"(base + G::STAGE_K + token * G::VPITCH + (c % CPR) * 16), "l"(live ? vsrc + c * 16 : vsrc), "r"(live) : "memory");
+        for (int i = 0; i < CPR; ++i) {
+            const int c = lane + 32 * i, token = c / CPR;            // chunk c of the tile's code bytes
+            const int live = token < nvalid ? 16 : 0;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                         :: "r"(base + c * 16), "l"(live ? ksrc + c * 16 : ksrc), "r"(live) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                         :: "r"(base + G::STAGE_K + token * G::VPITCH + (c % CPR) * 16), "l"(live ? vsrc + c * 16 : vsrc), "r"(live) : "memory");
+        }
+    } else {
+        // rows of 48 bytes: 8-byte pieces, so that a piece never straddles two rows
+        constexpr int PPR = G::ROWB / 8;                            // pieces per token row
+#pragma unroll
+        for (int i = 0; i < PPR; ++i) {
+            const int c = lane + 32 * i, token = c / PPR;
+            const int live = token < nvalid ? 8 : 0;
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;"
+                         :: "r"(base + c * 8), "l"(live ? ksrc + c * 8 : ksrc), "r"(live) : "memory");
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;"
+                         :: "r"(base + G::STAGE_K + token * G::VPITCH + (c % PPR) * 8), "l"(live ? vsrc + c * 8 : vsrc), "r"(live) : "memory");
+        }
     }
     if (lane < 8 || (k_norms != nullptr && lane < 16)) {
         const int l8 = lane & 7;
@@ -162,6 +176,21 @@ __device__ __forceinline__ void issue_attn_tile(unsigned char* stage, const unsi
                      :: "r"(base + G::STAGE_K + G::STAGE_V + lane * 16), "l"(live ? nsrc + 4 * l8 : nsrc), "r"(live) : "memory");
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+// w[i], or w[0] where i lies beyond the array (only ever reached in code that is compiled but never run)
+template <int N>
+__device__ __forceinline__ uint32_t word_at(const uint32_t (&w)[N], int i) { return w[i < N ? i : 0]; }
+
+// Byte offset into the centroid table of the pair of adjacent 3-bit codes number p (bits [6p, 6p + 6))
+// of a run of N code words, lane slot included.
+template <int N>
+__device__ __forceinline__ uint32_t pair3_offset(const uint32_t (&w)[N], int p, uint32_t slot) {
+    const int bit = 6 * p, word = bit >> 5, off = bit & 31;
+    uint32_t x;
+    if (off + 6 <= 32) x = off >= 8 ? (w[word] >> (off - 8)) : (w[word] << (8 - off));
+    else x = __funnelshift_r(w[word], w[word + 1 < N ? word + 1 : word], off - 8);
+    return (x & 0x3F00u) | slot;
 }
 
 template <int D> struct AttnState {
@@ -177,21 +206,24 @@ template <int D> struct AttnState {
 // table look-ups; the result is then as accurate as attention over the cache decoded to bf16.
 // TK: TurboQuant keys - the A operand of the score product is looked up in the centroid table and the
 // key norms (128 bytes after the value norms) scale the score rows.
-template <int D, bool FAST, bool TK>
+template <int D, int BITS, bool FAST, bool TK>
 __device__ __forceinline__ void attn_tile(const unsigned char* kb, const unsigned char* vb, const unsigned char* nb,
                                           AttnState<D>& st, const uint2* qf,
                                           float bias0, float bias1, int nvalid, const unsigned char* table,
                                           uint32_t slot, int g) {
     // ---- scores^T: two blocks of 16 tokens x 8 queries; one accumulator per part of the query, so
     //      that six short chains of products are in flight instead of two long ones
-    typedef AttnGeom<D> G;
-    constexpr int NKB = G::NKB, WPL = D / 32;                     // code words per lane and row: 2 or 4
+    typedef AttnGeom<D, BITS> G;
+    constexpr int NKB = G::NKB, WPL = D * BITS / 128;             // code words per lane and row: 2 or 4 (3 at 3 bits)
     uint32_t kc[2][2][WPL];                                       // this lane's words of tokens 16m + g and 16m + g + 8
 #pragma unroll
     for (int m = 0; m < 2; ++m)
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            if (WPL == 2) {
+            if (BITS == 3) {
+#pragma unroll
+                for (int i = 0; i < WPL; ++i) kc[m][h][i] = *reinterpret_cast<const uint32_t*>(kb + (16 * m + 8 * h) * G::ROWB + 4 * i);
+            } else if (WPL == 2) {
                 const uint2 v = *reinterpret_cast<const uint2*>(kb + (16 * m + 8 * h) * G::ROWB);
                 kc[m][h][0] = v.x; kc[m][h][1] = v.y;
             } else {
@@ -209,18 +241,26 @@ __device__ __forceinline__ void attn_tile(const unsigned char* kb, const unsigne
     // block KB of 16 channels: words 2*(KB/4), 2*(KB/4) + 1 of the lane's words, byte / nibble pair KB % 4
 #define PITCH_QK(KB)                                                                                 \
     if (KB < NKB) {                                                                                  \
-        constexpr int W = 2 * ((KB) >> 2) < WPL ? 2 * ((KB) >> 2) : 0, B = (KB) & 3;                 \
+        constexpr int W = 2 * ((KB) >> 2) < D / 32 ? 2 * ((KB) >> 2) : 0, B = (KB) & 3;              \
         const uint2 qh = qf[(0 * NKB + KB) * 32], qm = qf[(1 * NKB + KB) * 32];                      \
         uint2 ql = make_uint2(0, 0);                                                                 \
         if (!FAST) ql = qf[(2 * NKB + KB) * 32];                                                     \
         _Pragma("unroll")                                                                            \
         for (int m = 0; m < 2; ++m) {                                                                \
             if (TK) {                                                                                \
-                /* byte B of the word pair of rows g and g+8: two adjacent codes each */             \
-                const unsigned char* e0 = table + __byte_perm(kc[m][0][W], slot, 0x5504 | (B << 4)); \
-                const unsigned char* e1 = table + __byte_perm(kc[m][1][W], slot, 0x5504 | (B << 4)); \
-                const unsigned char* e2 = table + __byte_perm(kc[m][0][W + 1], slot, 0x5504 | (B << 4)); \
-                const unsigned char* e3 = table + __byte_perm(kc[m][1][W + 1], slot, 0x5504 | (B << 4)); \
+                /* the pair of adjacent codes number 4W + B (and four pairs on) of rows g and g+8 */ \
+                const unsigned char *e0, *e1, *e2, *e3;                                              \
+                if (BITS == 4) {                                                                     \
+                    e0 = table + __byte_perm(word_at(kc[m][0], W), slot, 0x5504 | (B << 4));                  \
+                    e1 = table + __byte_perm(word_at(kc[m][1], W), slot, 0x5504 | (B << 4));                  \
+                    e2 = table + __byte_perm(word_at(kc[m][0], W + 1), slot, 0x5504 | (B << 4));              \
+                    e3 = table + __byte_perm(word_at(kc[m][1], W + 1), slot, 0x5504 | (B << 4));              \
+                } else {                                                                             \
+                    e0 = table + pair3_offset(kc[m][0], 4 * W + B, slot);                            \
+                    e1 = table + pair3_offset(kc[m][1], 4 * W + B, slot);                            \
+                    e2 = table + pair3_offset(kc[m][0], 4 * W + B + 4, slot);                        \
+                    e3 = table + pair3_offset(kc[m][1], 4 * W + B + 4, slot);                        \
+                }                                                                                    \
                 const uint32_t a0 = *reinterpret_cast<const uint32_t*>(e0), a1 = *reinterpret_cast<const uint32_t*>(e1); \
                 const uint32_t a2 = *reinterpret_cast<const uint32_t*>(e2), a3 = *reinterpret_cast<const uint32_t*>(e3); \
                 mma_bf16(sc[m], a0, a1, a2, a3, qh.x, qh.y);                                         \
@@ -233,8 +273,8 @@ __device__ __forceinline__ void attn_tile(const unsigned char* kb, const unsigne
                     mma_bf16(sl[m], l0, l1, l2, l3, qm.x, qm.y);                                     \
                 }                                                                                    \
             } else {                                                                                 \
-                const uint32_t a0 = key_pair<B>(kc[m][0][W]), a1 = key_pair<B>(kc[m][1][W]);         \
-                const uint32_t a2 = key_pair<B>(kc[m][0][W + 1]), a3 = key_pair<B>(kc[m][1][W + 1]); \
+                const uint32_t a0 = key_pair<B>(word_at(kc[m][0], W)), a1 = key_pair<B>(word_at(kc[m][1], W)); \
+                const uint32_t a2 = key_pair<B>(word_at(kc[m][0], W + 1)), a3 = key_pair<B>(word_at(kc[m][1], W + 1)); \
                 mma_bf16(sc[m], a0, a1, a2, a3, qh.x, qh.y);                                         \
                 mma_bf16(sm[m], a0, a1, a2, a3, qm.x, qm.y);                                         \
                 if (!FAST) mma_bf16(sl[m], a0, a1, a2, a3, ql.x, ql.y);                              \
@@ -303,31 +343,56 @@ __device__ __forceinline__ void attn_tile(const unsigned char* kb, const unsigne
     for (int m = 0; m < 2; ++m) {
 #pragma unroll
         for (int half = 0; half < D / 64; ++half) {
-            // coordinate-wise interleave of the token pairs (2t, 2t+1) and (2t+8, 2t+9)
-            // word g (+ 8 per half) of tokens 16m + {2t, 2t+1, 2t+8, 2t+9}: coordinates 64 * half + 8g ...
-            const unsigned char* vrow = vb + 16 * m * G::VPITCH + half * 32;
-            const uint32_t v0 = *reinterpret_cast<const uint32_t*>(vrow), v1 = *reinterpret_cast<const uint32_t*>(vrow + G::VPITCH);
-            const uint32_t v2 = *reinterpret_cast<const uint32_t*>(vrow + 8 * G::VPITCH), v3 = *reinterpret_cast<const uint32_t*>(vrow + 9 * G::VPITCH);
-            const uint32_t ea = (v0 & 0x0F0F0F0Fu) | ((v1 << 4) & 0xF0F0F0F0u);   // even coordinates
-            const uint32_t oa = ((v0 >> 4) & 0x0F0F0F0Fu) | (v1 & 0xF0F0F0F0u);   // odd coordinates
-            const uint32_t eb = (v2 & 0x0F0F0F0Fu) | ((v3 << 4) & 0xF0F0F0F0u);
-            const uint32_t ob = ((v2 >> 4) & 0x0F0F0F0Fu) | (v3 & 0xF0F0F0F0u);
             uint32_t ch[4][4], cl[4][4];                               // [coordinate block][fragment register]
+            const unsigned char* e[4][4];                              // table entries of the same
+            if (BITS == 4) {
+                // coordinate-wise interleave of the token pairs (2t, 2t+1) and (2t+8, 2t+9)
+                // word g (+ 8 per half) of tokens 16m + {2t, 2t+1, 2t+8, 2t+9}: coordinates 64 * half + 8g ...
+                const unsigned char* vrow = vb + 16 * m * G::VPITCH + half * 32;
+                const uint32_t v0 = *reinterpret_cast<const uint32_t*>(vrow), v1 = *reinterpret_cast<const uint32_t*>(vrow + G::VPITCH);
+                const uint32_t v2 = *reinterpret_cast<const uint32_t*>(vrow + 8 * G::VPITCH), v3 = *reinterpret_cast<const uint32_t*>(vrow + 9 * G::VPITCH);
+                const uint32_t ea = (v0 & 0x0F0F0F0Fu) | ((v1 << 4) & 0xF0F0F0F0u);   // even coordinates
+                const uint32_t oa = ((v0 >> 4) & 0x0F0F0F0Fu) | (v1 & 0xF0F0F0F0u);   // odd coordinates
+                const uint32_t eb = (v2 & 0x0F0F0F0Fu) | ((v3 << 4) & 0xF0F0F0F0u);
+                const uint32_t ob = ((v2 >> 4) & 0x0F0F0F0Fu) | (v3 & 0xF0F0F0F0u);
+#pragma unroll
+                for (int mb = 0; mb < 4; ++mb) {
+                    e[mb][0] = table + __byte_perm(ea, slot, 0x5504 | (mb << 4));
+                    e[mb][1] = table + __byte_perm(oa, slot, 0x5504 | (mb << 4));
+                    e[mb][2] = table + __byte_perm(eb, slot, 0x5504 | (mb << 4));
+                    e[mb][3] = table + __byte_perm(ob, slot, 0x5504 | (mb << 4));
+                }
+            } else {
+                // 3-bit codes: the 8 coordinates 64 * half + 8g ... of a token are 24 bits at byte 3g + 24 * half
+                // of its row (vb points 4g bytes into the row of token 2t, the place of the 4-bit word)
+                const int byte0 = 3 * g + 24 * half;
+                const unsigned char* vrow = vb - 4 * g + 16 * m * G::VPITCH + (byte0 & ~3);
+                const int sh = 8 * (byte0 & 3);
+                uint32_t x[4];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const unsigned char* row = vrow + ((r & 1) + 8 * (r >> 1)) * G::VPITCH;       // tokens 2t, 2t+1, 2t+8, 2t+9
+                    x[r] = __funnelshift_r(*reinterpret_cast<const uint32_t*>(row), *reinterpret_cast<const uint32_t*>(row + 4), sh);
+                }
+#pragma unroll
+                for (int mb = 0; mb < 4; ++mb) {
+                    // coordinate j of tokens (A, B): entry (code_A | code_B << 3) at byte (entry << 8) + slot
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const int j = 2 * mb + (k & 1);                                             // even, odd coordinate
+                        const uint32_t xa = x[2 * (k >> 1)], xb = x[2 * (k >> 1) + 1];
+                        const uint32_t lo3 = 3 * j >= 8 ? (xa >> (3 * j - 8)) : (xa << (8 - 3 * j));
+                        const uint32_t hi3 = 3 * j >= 11 ? (xb >> (3 * j - 11)) : (xb << (11 - 3 * j));
+                        e[mb][k] = table + ((lo3 & 0x0700u) | (hi3 & 0x3800u) | slot);
+                    }
+                }
+            }
 #pragma unroll
             for (int mb = 0; mb < 4; ++mb) {
-                const unsigned char* e0 = table + __byte_perm(ea, slot, 0x5504 | (mb << 4));
-                const unsigned char* e1 = table + __byte_perm(oa, slot, 0x5504 | (mb << 4));
-                const unsigned char* e2 = table + __byte_perm(eb, slot, 0x5504 | (mb << 4));
-                const unsigned char* e3 = table + __byte_perm(ob, slot, 0x5504 | (mb << 4));
-                ch[mb][0] = *reinterpret_cast<const uint32_t*>(e0);
-                ch[mb][1] = *reinterpret_cast<const uint32_t*>(e1);
-                ch[mb][2] = *reinterpret_cast<const uint32_t*>(e2);
-                ch[mb][3] = *reinterpret_cast<const uint32_t*>(e3);
-                if (!FAST) {
-                    cl[mb][0] = *reinterpret_cast<const uint32_t*>(e0 + 128);
-                    cl[mb][1] = *reinterpret_cast<const uint32_t*>(e1 + 128);
-                    cl[mb][2] = *reinterpret_cast<const uint32_t*>(e2 + 128);
-                    cl[mb][3] = *reinterpret_cast<const uint32_t*>(e3 + 128);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    ch[mb][k] = *reinterpret_cast<const uint32_t*>(e[mb][k]);
+                    if (!FAST) cl[mb][k] = *reinterpret_cast<const uint32_t*>(e[mb][k] + 128);
                 }
             }
 #pragma unroll
@@ -438,11 +503,12 @@ __device__ __forceinline__ void rotate_query(const float* __restrict__ qrow, flo
     __syncwarp();
 }
 
-template <int D, bool FAST, bool TK>
-__global__ void __launch_bounds__(AttnGeom<D>::THREADS, 1)
+template <int D, int BITS, bool FAST, bool TK>
+__global__ void __launch_bounds__(AttnGeom<D, BITS>::THREADS, 1)
 attention_partial_kernel(const __grid_constant__ AttentionParams p) {
     static_assert(D == 64 || TK, "per-channel keys are handled at head dimension 64 only");
-    typedef AttnGeom<D> G;
+    static_assert(BITS == 4 || (BITS == 3 && D == 128 && TK), "3-bit codes are handled at head dimension 128 with TurboQuant keys");
+    typedef AttnGeom<D, BITS> G;
     constexpr int AT_WARPS = G::WARPS, AT_STAGE_BYTES = G::STAGE_BYTES, AT_PART_FLOATS = G::PART_FLOATS;
     extern __shared__ __align__(1024) unsigned char smem[];
     // byte (na | nb << 4) of two tokens' codes, lane slot l: the bf16 pair (c[na], c[nb]) as hi parts at
@@ -457,10 +523,10 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
     const int R = p.n_queries;
     const uint32_t slot = (uint32_t)lane * 4u;
 
-    for (int e = threadIdx.x; e < 256; e += G::THREADS) {
-        // one table entry per thread (256 code pairs), written to its 32 lane slots
+    for (int e = threadIdx.x; e < (1 << (2 * BITS)); e += G::THREADS) {
+        // one table entry per thread (all pairs of codes), written to its 32 lane slots
         uint32_t hi, lo;
-        split_pair(p.book.c[e & 15], p.book.c[e >> 4], hi, lo);
+        split_pair(p.book.c[e & ((1 << BITS) - 1)], p.book.c[e >> BITS], hi, lo);
         uint4* row = reinterpret_cast<uint4*>(table + e * 256);
 #pragma unroll
         for (int i = 0; i < 16; ++i) {                   // rows are 256 bytes apart: rotate the chunk order per lane
@@ -504,7 +570,7 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
 
         // the first tile is on its way before anything else of the run is fetched
         __syncwarp();
-        issue_attn_tile<D>(stage0, k_codes, v_codes, v_norms, k_norms, w_begin, w_end - w_begin, lane);
+        issue_attn_tile<D, BITS>(stage0, k_codes, v_codes, v_norms, k_norms, w_begin, w_end - w_begin, lane);
 
         // per-channel keys: the ranges of the first group; those of the following group are fetched a
         // group ahead.  TurboQuant keys: the query is rotated once, here.
@@ -528,7 +594,7 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
         {                                                                                               \
             const int nvalid = w_end - t0;                            /* >= 32 for a whole tile */      \
             if (nvalid > 32) {                                                                          \
-                issue_attn_tile<D>(stage0 + (1 - BUF) * AT_STAGE_BYTES, k_codes, v_codes, v_norms, k_norms, t0 + 32, nvalid - 32, lane); \
+                issue_attn_tile<D, BITS>(stage0 + (1 - BUF) * AT_STAGE_BYTES, k_codes, v_codes, v_norms, k_norms, t0 + 32, nvalid - 32, lane); \
                 cp_async_wait<1>();                                                                     \
             } else {                                                                                    \
                 cp_async_wait<0>();                                                                     \
@@ -543,7 +609,7 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
                     hi2 = ldg_stream32(reinterpret_cast<const uint32_t*>(k_ranges + (int64_t)(group + 1) * 128 + 64)); \
                 }                                                                                       \
             }                                                                                           \
-            attn_tile<D, FAST, TK>(kb + BUF * AT_STAGE_BYTES, vb + BUF * AT_STAGE_BYTES, nb + BUF * AT_STAGE_BYTES, st, qf + lane,  \
+            attn_tile<D, BITS, FAST, TK>(kb + BUF * AT_STAGE_BYTES, vb + BUF * AT_STAGE_BYTES, nb + BUF * AT_STAGE_BYTES, st, qf + lane,  \
                       bias0, bias1, nvalid, table, slot, g);                                            \
             __syncwarp();                                             /* this buffer is refilled two tiles on */ \
         }

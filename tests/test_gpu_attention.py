@@ -102,14 +102,14 @@ def test_bf16_operand_mode_is_as_accurate_as_attention_over_the_bf16_cache(q, S,
         cache.attend(Qd, precision="float8")
 
 
-def build_turbo_cache(q, S, T, seed, d=64):
-    """Keys and values both TurboQuant 4-bit (with different rotation seeds)."""
+def build_turbo_cache(q, S, T, seed, d=64, bits=4):
+    """Keys and values both TurboQuant (with different rotation seeds)."""
     import torch
     from pitch_b200 import KVCache, QuantConfig
     rng = np.random.default_rng(seed)
     K = (rng.standard_normal((S, T, d)) * np.exp(0.4 * rng.standard_normal((S, T, 1)))).astype(np.float32)
     V = (rng.standard_normal((S, T, d)) * np.exp(0.5 * rng.standard_normal((S, T, 1)))).astype(np.float32)
-    cache = KVCache(S, d, T, QuantConfig("turboQuant", d, 4, seed=777), QuantConfig("turboQuant", d, 4), out_dtype="float32", pitch=q)
+    cache = KVCache(S, d, T, QuantConfig("turboQuant", d, bits, seed=777), QuantConfig("turboQuant", d, bits), out_dtype="float32", pitch=q)
     cache.prefill(torch.from_numpy(K).to(q.device), torch.from_numpy(V).to(q.device))
     return cache, rng
 
@@ -118,9 +118,10 @@ def spec_decoded_turbo(cache, s):
     T, d = cache.tokens, cache.dim
     out = []
     for pl in cache.planes:
-        c = pl.codes[s, :T * (d // 2)].cpu().numpy()
+        b = pl.config.bits
+        c = pl.codes[s, :T * (d * b // 8)].cpu().numpy()
         n = pl.side[s, :T].cpu().numpy().astype(np.float64)
-        out.append(np.asarray(spec_np.turbo_decode(spec_np.unpack_codes(c.tobytes(), T, d, 4), n, 4, pl.config.seed), dtype=np.float64))
+        out.append(np.asarray(spec_np.turbo_decode(spec_np.unpack_codes(c.tobytes(), T, d, b), n, b, pl.config.seed), dtype=np.float64))
     return out
 
 
@@ -144,6 +145,28 @@ def test_turboquant_keys_match_attention_over_spec_decoded_cache(q, S, T, R, sca
         # times larger than usual) carries that into the weights
         assert rows_rel_l2(got[s], ref) < (TOL if scale is None else 1e-4), (s, rows_rel_l2(got[s], ref))
         assert rows_rel_l2(fast[s], ref) < (1e-2 if scale is None else 5e-2), (s, rows_rel_l2(fast[s], ref))
+
+
+@pytest.mark.parametrize("S,T,R,scale", [(3, 333, 7, None), (2, 5000, 1, None), (1, 31, 8, None), (2, 9000, 5, 1.0), (1, 1, 3, None),
+                                          (1, 32768, 8, None)])
+def test_three_bit_cache_at_dimension_128(q, S, T, R, scale):
+    """The 3-bit Llama-3-70B-shaped cache: codes of a vector are 48 bytes, a pair of codes straddles bytes."""
+    import torch
+    cache, rng = build_turbo_cache(q, S, T, seed=500 + T, d=128, bits=3)
+    Q = rng.standard_normal((S, R, 128)).astype(np.float32)
+    Qd = torch.from_numpy(Q).to(q.device)
+    got = cache.attend(Qd, scale=scale).cpu().numpy().astype(np.float64)
+    fast = cache.attend(Qd, scale=scale, precision="bfloat16").cpu().numpy().astype(np.float64)
+    assert np.isfinite(got).all() and np.isfinite(fast).all()
+    sc = 128 ** -0.5 if scale is None else scale
+    for s in range(S):
+        K, V = spec_decoded_turbo(cache, s)
+        ref = attention64(Q[s].astype(np.float64), K, V, sc)
+        assert rows_rel_l2(got[s], ref) < (TOL if scale is None else 1e-4), (s, rows_rel_l2(got[s], ref))
+        # over 32,768 random tokens the output is a mean whose norm shrinks as 1/sqrt(T); bf16 operand
+        # rounding does not shrink with it
+        fast_tol = 5e-2 if scale is not None else (2e-2 if T > 10000 else 1e-2)
+        assert rows_rel_l2(fast[s], ref) < fast_tol, (s, rows_rel_l2(fast[s], ref))
 
 
 def test_grows_with_the_cache(q):
@@ -207,7 +230,9 @@ def test_unsupported_shapes_are_refused(q):
     cases = [(64, ChannelQuantConfig(64, 4, 48), QuantConfig("turboQuant", 64, 4)),      # group not a multiple of 32
              (64, ChannelQuantConfig(64, 2, 64), QuantConfig("turboQuant", 64, 4)),      # 2-bit keys
              (64, ChannelQuantConfig(64, 4, 64), QuantConfig("polarQuant", 64, 4)),      # PolarQuant values
-             (128, ChannelQuantConfig(128, 4, 64), QuantConfig("turboQuant", 128, 4))]   # dim 128
+             (128, ChannelQuantConfig(128, 4, 64), QuantConfig("turboQuant", 128, 4)),   # per-channel keys at dim 128
+             (64, QuantConfig("turboQuant", 64, 3), QuantConfig("turboQuant", 64, 3)),   # 3 bits at dim 64
+             (128, QuantConfig("turboQuant", 128, 4), QuantConfig("turboQuant", 128, 3))]  # keys and values of different widths
     for d, kc, vc in cases:
         cache = KVCache(2, d, 128, kc, vc, pitch=q)
         x = torch.randn((2, 128, d), device=dev)
