@@ -146,19 +146,23 @@ int pitch_enqueue_cache_attention(const pitch_cache_desc* d, const pitch_attenti
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     {
         const bool wide = d->dim == 128;
-        const int smem = wide ? (vbits == 3 ? AttnGeom<128, 3>::SMEM_BYTES : AttnGeom<128>::SMEM_BYTES) : AttnGeom<64>::SMEM_BYTES;
+        // all the shared memory a block may have: the kernel's table must sit at a fixed shared-memory address
+        const int smem = AT_SMEM_BYTES;
         const int warps = wide ? AttnGeom<128>::WARPS : AttnGeom<64>::WARPS;
         static std::atomic<bool> configured[64];
         if (dev >= 0 && dev < 64 && !configured[dev].load(std::memory_order_acquire)) {
+            int optin = 0;
+            if (cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess || optin != AT_SMEM_BYTES)
+                return fail(PITCH_ERR_KERNEL_UNAVAILABLE, "cache attention needs a device with %d bytes of shared memory per block (this one: %d)", AT_SMEM_BYTES, optin);
             const cudaFuncAttribute at = cudaFuncAttributeMaxDynamicSharedMemorySize;
-            if (cudaFuncSetAttribute(attention_partial_kernel<64, 4, false, false>, at, AttnGeom<64>::SMEM_BYTES) != cudaSuccess ||
-                cudaFuncSetAttribute(attention_partial_kernel<64, 4, true, false>, at, AttnGeom<64>::SMEM_BYTES) != cudaSuccess ||
-                cudaFuncSetAttribute(attention_partial_kernel<64, 4, false, true>, at, AttnGeom<64>::SMEM_BYTES) != cudaSuccess ||
-                cudaFuncSetAttribute(attention_partial_kernel<64, 4, true, true>, at, AttnGeom<64>::SMEM_BYTES) != cudaSuccess ||
-                cudaFuncSetAttribute(attention_partial_kernel<128, 4, false, true>, at, AttnGeom<128>::SMEM_BYTES) != cudaSuccess ||
-                cudaFuncSetAttribute(attention_partial_kernel<128, 4, true, true>, at, AttnGeom<128>::SMEM_BYTES) != cudaSuccess ||
-                cudaFuncSetAttribute(attention_partial_kernel<128, 3, false, true>, at, AttnGeom<128, 3>::SMEM_BYTES) != cudaSuccess ||
-                cudaFuncSetAttribute(attention_partial_kernel<128, 3, true, true>, at, AttnGeom<128, 3>::SMEM_BYTES) != cudaSuccess)
+            if (cudaFuncSetAttribute(attention_partial_kernel<64, 4, false, false>, at, smem) != cudaSuccess ||
+                cudaFuncSetAttribute(attention_partial_kernel<64, 4, true, false>, at, smem) != cudaSuccess ||
+                cudaFuncSetAttribute(attention_partial_kernel<64, 4, false, true>, at, smem) != cudaSuccess ||
+                cudaFuncSetAttribute(attention_partial_kernel<64, 4, true, true>, at, smem) != cudaSuccess ||
+                cudaFuncSetAttribute(attention_partial_kernel<128, 4, false, true>, at, smem) != cudaSuccess ||
+                cudaFuncSetAttribute(attention_partial_kernel<128, 4, true, true>, at, smem) != cudaSuccess ||
+                cudaFuncSetAttribute(attention_partial_kernel<128, 3, false, true>, at, smem) != cudaSuccess ||
+                cudaFuncSetAttribute(attention_partial_kernel<128, 3, true, true>, at, smem) != cudaSuccess)
                 return launch_status(false, "cache_attention (shared memory opt-in)");
             configured[dev].store(true, std::memory_order_release);
         }

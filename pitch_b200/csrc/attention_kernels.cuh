@@ -59,6 +59,9 @@ namespace pitch {
 
 constexpr int AT_MAX_QUERIES = 8;
 constexpr int AT_COMBINE_WARPS = 8;
+constexpr int AT_TABLE_ADDR = 0x10000;      // shared-memory address of the centroid table: byte 2 of every entry's address is 1
+constexpr int AT_SMEM_RESERVED = 1024;      // start of a block's dynamic shared memory when it takes all there is
+constexpr int AT_SMEM_BYTES = 232448;       // dynamic shared memory of a launch: the most a block may have (227 KB)
 
 // Sizes for head dimension D (64 or 128) and code width BITS (4; 3 at D = 128).
 template <int D, int BITS = 4> struct AttnGeom {
@@ -73,7 +76,13 @@ template <int D, int BITS = 4> struct AttnGeom {
     static constexpr int STAGE_BYTES = STAGE_K + STAGE_V + 256;          // + 32 value norms + 32 key norms (TurboQuant keys)
     // per warp: per-group steps and offsets of the keys; query fragments (3 parts); two tile buffers (one in flight)
     static constexpr int WARP_SMEM = 512 + 3 * NKB * 32 * 8 + 2 * STAGE_BYTES;
-    static constexpr int SMEM_BYTES = CD_TABLE_BYTES + WARPS * WARP_SMEM;
+    // The centroid table sits at shared-memory address AT_TABLE_ADDR exactly (see table_word), the warps'
+    // areas below and above it.  The kernel is launched with all the shared memory a block may have
+    // (AT_SMEM_BYTES of dynamic memory), which pins the start of its dynamic memory to an address of
+    // 0 ... AT_SMEM_RESERVED: a later start would not fit the multiprocessor and the launch would fail.
+    static constexpr int LOW_WARPS = (AT_TABLE_ADDR - AT_SMEM_RESERVED) / WARP_SMEM;    // areas below the table
+    static_assert(LOW_WARPS >= 1 && LOW_WARPS < WARPS, "warps' areas on both sides of the table");
+    static_assert(AT_TABLE_ADDR + CD_TABLE_BYTES + (WARPS - LOW_WARPS) * WARP_SMEM <= AT_SMEM_BYTES, "the areas above the table must fit");
 };
 
 struct AttentionParams {
@@ -131,6 +140,24 @@ __device__ __forceinline__ uint32_t key_pair(uint32_t w) {
     return (s & 0x00780078u) | 0x41804180u;
 }
 
+// The centroid table: entry e (a byte of two 4-bit codes, or 6 bits of two 3-bit codes) holds the bf16 pair
+// of its two centroids' heads in 32 lane slots of 4 bytes (every lane reads its own bank), the pair of
+// remainders 128 bytes further.  Because the table starts at shared-memory address 0x10000, the address of
+// (entry, lane) is the bytes (4 * lane, entry, 1, 0): one byte permutation of a code word and the lane's
+// constant `slot` = AT_TABLE_ADDR | 4 * lane, with no addition.
+__device__ __forceinline__ uint32_t table_word(uint32_t addr) {
+    uint32_t v;
+    asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t table_word_lo(uint32_t addr) {
+    uint32_t v;
+    asm("ld.shared.u32 %0, [%1+128];" : "=r"(v) : "r"(addr));
+    return v;
+}
+template <int B>
+__device__ __forceinline__ uint32_t entry_of_byte(uint32_t w, uint32_t slot) { return __byte_perm(w, slot, 0x7604 | (B << 4)); }
+
 // Starts the asynchronous copy of a tile (32 tokens from `tok`, `nvalid` of them existing) into a
 // warp's tile buffer: key codes, value codes, norms.  Bytes of tokens that do not exist are
 // zero-filled without touching memory.  k_norms: the keys' norms (TurboQuant keys) or null.
@@ -182,8 +209,8 @@ __device__ __forceinline__ void issue_attn_tile(unsigned char* stage, const unsi
 template <int N>
 __device__ __forceinline__ uint32_t word_at(const uint32_t (&w)[N], int i) { return w[i < N ? i : 0]; }
 
-// Byte offset into the centroid table of the pair of adjacent 3-bit codes number p (bits [6p, 6p + 6))
-// of a run of N code words, lane slot included.
+// Table address of the pair of adjacent 3-bit codes number p (bits [6p, 6p + 6)) of a run of N code
+// words, for the lane of `slot`.
 template <int N>
 __device__ __forceinline__ uint32_t pair3_offset(const uint32_t (&w)[N], int p, uint32_t slot) {
     const int bit = 6 * p, word = bit >> 5, off = bit & 31;
@@ -202,15 +229,16 @@ template <int D> struct AttnState {
 // tile buffer (key row g words 2t, 2t+1; value row 2t word g; norm g); qf: its folded-query fragments
 // in shared memory (stride 32 entries); bias0/1: score offsets of queries 2t and 2t + 1.
 // FAST: operands as a bf16 pipeline would have them - the folded query in two bf16 parts instead of
-// three, weights and centroids in one instead of two - which halves the tensor-core products and the
-// table look-ups; the result is then as accurate as attention over the cache decoded to bf16.
+// three (one part alone doubles the error of attention over a bf16 cache: the folded query multiplies
+// 16 + code, the rotated query of TurboQuant keys has all its coordinates of one magnitude), weights and
+// centroids in one instead of two - which halves the tensor-core products and the table look-ups; the
+// result is then as accurate as attention over the cache decoded to bf16.
 // TK: TurboQuant keys - the A operand of the score product is looked up in the centroid table and the
 // key norms (128 bytes after the value norms) scale the score rows.
 template <int D, int BITS, bool FAST, bool TK>
 __device__ __forceinline__ void attn_tile(const unsigned char* kb, const unsigned char* vb, const unsigned char* nb,
                                           AttnState<D>& st, const uint2* qf,
-                                          float bias0, float bias1, int nvalid, const unsigned char* table,
-                                          uint32_t slot, int g) {
+                                          float bias0, float bias1, int nvalid, uint32_t slot, int g) {
     // ---- scores^T: two blocks of 16 tokens x 8 queries; one accumulator per part of the query, so
     //      that six short chains of products are in flight instead of two long ones
     typedef AttnGeom<D, BITS> G;
@@ -249,25 +277,23 @@ __device__ __forceinline__ void attn_tile(const unsigned char* kb, const unsigne
         for (int m = 0; m < 2; ++m) {                                                                \
             if (TK) {                                                                                \
                 /* the pair of adjacent codes number 4W + B (and four pairs on) of rows g and g+8 */ \
-                const unsigned char *e0, *e1, *e2, *e3;                                              \
+                uint32_t e0, e1, e2, e3;                                                             \
                 if (BITS == 4) {                                                                     \
-                    e0 = table + __byte_perm(word_at(kc[m][0], W), slot, 0x5504 | (B << 4));                  \
-                    e1 = table + __byte_perm(word_at(kc[m][1], W), slot, 0x5504 | (B << 4));                  \
-                    e2 = table + __byte_perm(word_at(kc[m][0], W + 1), slot, 0x5504 | (B << 4));              \
-                    e3 = table + __byte_perm(word_at(kc[m][1], W + 1), slot, 0x5504 | (B << 4));              \
+                    e0 = entry_of_byte<B>(word_at(kc[m][0], W), slot);                               \
+                    e1 = entry_of_byte<B>(word_at(kc[m][1], W), slot);                               \
+                    e2 = entry_of_byte<B>(word_at(kc[m][0], W + 1), slot);                           \
+                    e3 = entry_of_byte<B>(word_at(kc[m][1], W + 1), slot);                           \
                 } else {                                                                             \
-                    e0 = table + pair3_offset(kc[m][0], 4 * W + B, slot);                            \
-                    e1 = table + pair3_offset(kc[m][1], 4 * W + B, slot);                            \
-                    e2 = table + pair3_offset(kc[m][0], 4 * W + B + 4, slot);                        \
-                    e3 = table + pair3_offset(kc[m][1], 4 * W + B + 4, slot);                        \
+                    e0 = pair3_offset(kc[m][0], 4 * W + B, slot);                                    \
+                    e1 = pair3_offset(kc[m][1], 4 * W + B, slot);                                    \
+                    e2 = pair3_offset(kc[m][0], 4 * W + B + 4, slot);                                \
+                    e3 = pair3_offset(kc[m][1], 4 * W + B + 4, slot);                                \
                 }                                                                                    \
-                const uint32_t a0 = *reinterpret_cast<const uint32_t*>(e0), a1 = *reinterpret_cast<const uint32_t*>(e1); \
-                const uint32_t a2 = *reinterpret_cast<const uint32_t*>(e2), a3 = *reinterpret_cast<const uint32_t*>(e3); \
+                const uint32_t a0 = table_word(e0), a1 = table_word(e1), a2 = table_word(e2), a3 = table_word(e3); \
                 mma_bf16(sc[m], a0, a1, a2, a3, qh.x, qh.y);                                         \
                 mma_bf16(sm[m], a0, a1, a2, a3, qm.x, qm.y);                                         \
                 if (!FAST) {                                                                         \
-                    const uint32_t l0 = *reinterpret_cast<const uint32_t*>(e0 + 128), l1 = *reinterpret_cast<const uint32_t*>(e1 + 128); \
-                    const uint32_t l2 = *reinterpret_cast<const uint32_t*>(e2 + 128), l3 = *reinterpret_cast<const uint32_t*>(e3 + 128); \
+                    const uint32_t l0 = table_word_lo(e0), l1 = table_word_lo(e1), l2 = table_word_lo(e2), l3 = table_word_lo(e3); \
                     mma_bf16(sl[m], a0, a1, a2, a3, ql.x, ql.y);                                     \
                     mma_bf16(sl[m], l0, l1, l2, l3, qh.x, qh.y);                                     \
                     mma_bf16(sl[m], l0, l1, l2, l3, qm.x, qm.y);                                     \
@@ -344,7 +370,7 @@ __device__ __forceinline__ void attn_tile(const unsigned char* kb, const unsigne
 #pragma unroll
         for (int half = 0; half < D / 64; ++half) {
             uint32_t ch[4][4], cl[4][4];                               // [coordinate block][fragment register]
-            const unsigned char* e[4][4];                              // table entries of the same
+            uint32_t e[4][4];                                          // table addresses of the same
             if (BITS == 4) {
                 // coordinate-wise interleave of the token pairs (2t, 2t+1) and (2t+8, 2t+9)
                 // word g (+ 8 per half) of tokens 16m + {2t, 2t+1, 2t+8, 2t+9}: coordinates 64 * half + 8g ...
@@ -357,10 +383,10 @@ __device__ __forceinline__ void attn_tile(const unsigned char* kb, const unsigne
                 const uint32_t ob = ((v2 >> 4) & 0x0F0F0F0Fu) | (v3 & 0xF0F0F0F0u);
 #pragma unroll
                 for (int mb = 0; mb < 4; ++mb) {
-                    e[mb][0] = table + __byte_perm(ea, slot, 0x5504 | (mb << 4));
-                    e[mb][1] = table + __byte_perm(oa, slot, 0x5504 | (mb << 4));
-                    e[mb][2] = table + __byte_perm(eb, slot, 0x5504 | (mb << 4));
-                    e[mb][3] = table + __byte_perm(ob, slot, 0x5504 | (mb << 4));
+                    e[mb][0] = __byte_perm(ea, slot, 0x7604 | (mb << 4));
+                    e[mb][1] = __byte_perm(oa, slot, 0x7604 | (mb << 4));
+                    e[mb][2] = __byte_perm(eb, slot, 0x7604 | (mb << 4));
+                    e[mb][3] = __byte_perm(ob, slot, 0x7604 | (mb << 4));
                 }
             } else {
                 // 3-bit codes: the 8 coordinates 64 * half + 8g ... of a token are 24 bits at byte 3g + 24 * half
@@ -383,7 +409,7 @@ __device__ __forceinline__ void attn_tile(const unsigned char* kb, const unsigne
                         const uint32_t xa = x[2 * (k >> 1)], xb = x[2 * (k >> 1) + 1];
                         const uint32_t lo3 = 3 * j >= 8 ? (xa >> (3 * j - 8)) : (xa << (8 - 3 * j));
                         const uint32_t hi3 = 3 * j >= 11 ? (xb >> (3 * j - 11)) : (xb << (11 - 3 * j));
-                        e[mb][k] = table + ((lo3 & 0x0700u) | (hi3 & 0x3800u) | slot);
+                        e[mb][k] = (lo3 & 0x0700u) | (hi3 & 0x3800u) | slot;
                     }
                 }
             }
@@ -391,8 +417,8 @@ __device__ __forceinline__ void attn_tile(const unsigned char* kb, const unsigne
             for (int mb = 0; mb < 4; ++mb) {
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    ch[mb][k] = *reinterpret_cast<const uint32_t*>(e[mb][k]);
-                    if (!FAST) cl[mb][k] = *reinterpret_cast<const uint32_t*>(e[mb][k] + 128);
+                    ch[mb][k] = table_word(e[mb][k]);
+                    if (!FAST) cl[mb][k] = table_word_lo(e[mb][k]);
                 }
             }
 #pragma unroll
@@ -411,6 +437,7 @@ __device__ __forceinline__ void attn_tile(const unsigned char* kb, const unsigne
 // (three bf16 parts, left in shared memory: qf[(part * 4 + block of 16 channels) * 32 + lane])
 // and the score bias of queries 2t and 2t + 1.  lo2 / hi2: this lane's two
 // channels of the group's fp16 minima and maxima.
+template <bool FAST>
 __device__ __forceinline__ void fold_group(uint32_t lo2, uint32_t hi2, const float* __restrict__ qrow, float qscale, float* gstep, float* goff,
                                            uint2* qf, float& bias0, float& bias1, int lane, int g, int t) {
     const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&lo2));
@@ -439,11 +466,16 @@ __device__ __forceinline__ void fold_group(uint32_t lo2, uint32_t hi2, const flo
 #pragma unroll
     for (int kb = 0; kb < 4; ++kb) {
         uint2 h, m, l;
-        split_pair3(x[kb], x[kb + 4], h.x, m.x, l.x);
-        split_pair3(x[8 + kb], x[12 + kb], h.y, m.y, l.y);
+        if (FAST) {                                       // the third part is not used
+            split_pair(x[kb], x[kb + 4], h.x, m.x);
+            split_pair(x[8 + kb], x[12 + kb], h.y, m.y);
+        } else {
+            split_pair3(x[kb], x[kb + 4], h.x, m.x, l.x);
+            split_pair3(x[8 + kb], x[12 + kb], h.y, m.y, l.y);
+            qf[(2 * 4 + kb) * 32 + lane] = l;
+        }
         qf[(0 * 4 + kb) * 32 + lane] = h;
         qf[(1 * 4 + kb) * 32 + lane] = m;
-        qf[(2 * 4 + kb) * 32 + lane] = l;
     }
     __syncwarp();
     b += __shfl_xor_sync(0xFFFFFFFFu, b, 1);
@@ -458,7 +490,7 @@ __device__ __forceinline__ void fold_group(uint32_t lo2, uint32_t hi2, const flo
 // four lanes of a query.  Fragment slots follow the A side of the TurboQuant-key product: in block KB,
 // slots (2t, 2t+1) are the lane's channels 16 (KB / 4) + 2 (KB % 4), + 1 (byte KB % 4 of its word
 // 2 (KB / 4)), slots (2t+8, 2t+9) the same 8 channels further on (the next word).
-template <int D>
+template <int D, bool FAST>
 __device__ __forceinline__ void rotate_query(const float* __restrict__ qrow, float qscale, float rs, const uint32_t (&kneg)[4],
                                              uint2* qf, int lane, int t) {
     constexpr int N = D / 4, NKB = D / 16;
@@ -494,11 +526,16 @@ __device__ __forceinline__ void rotate_query(const float* __restrict__ qrow, flo
     for (int kb = 0; kb < NKB; ++kb) {
         const int i0 = 16 * (kb >> 2) + 2 * (kb & 3);
         uint2 h, m, l;
-        split_pair3(x[i0] * sc, x[i0 + 1] * sc, h.x, m.x, l.x);
-        split_pair3(x[i0 + 8] * sc, x[i0 + 9] * sc, h.y, m.y, l.y);
+        if (FAST) {                                       // the third part is not used
+            split_pair(x[i0] * sc, x[i0 + 1] * sc, h.x, m.x);
+            split_pair(x[i0 + 8] * sc, x[i0 + 9] * sc, h.y, m.y);
+        } else {
+            split_pair3(x[i0] * sc, x[i0 + 1] * sc, h.x, m.x, l.x);
+            split_pair3(x[i0 + 8] * sc, x[i0 + 9] * sc, h.y, m.y, l.y);
+            qf[(2 * NKB + kb) * 32 + lane] = l;
+        }
         qf[(0 * NKB + kb) * 32 + lane] = h;
         qf[(1 * NKB + kb) * 32 + lane] = m;
-        qf[(2 * NKB + kb) * 32 + lane] = l;
     }
     __syncwarp();
 }
@@ -511,17 +548,19 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
     typedef AttnGeom<D, BITS> G;
     constexpr int AT_WARPS = G::WARPS, AT_STAGE_BYTES = G::STAGE_BYTES, AT_PART_FLOATS = G::PART_FLOATS;
     extern __shared__ __align__(1024) unsigned char smem[];
-    // byte (na | nb << 4) of two tokens' codes, lane slot l: the bf16 pair (c[na], c[nb]) as hi parts at
-    // byte * 256 + l * 4 and lo parts 128 bytes further (every lane reads its own bank)
-    unsigned char* table = smem;
+    // the table at shared address AT_TABLE_ADDR; warps 0 ... LOW_WARPS - 1 below it, the others above
+    const uint32_t smem_addr = (uint32_t)__cvta_generic_to_shared(smem);            // <= AT_SMEM_RESERVED
+    unsigned char* table = smem + (AT_TABLE_ADDR - smem_addr);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    float* gstep = reinterpret_cast<float*>(smem + CD_TABLE_BYTES + warp * G::WARP_SMEM);   // [64]
+    unsigned char* area = warp < G::LOW_WARPS ? smem + warp * G::WARP_SMEM
+                                              : table + CD_TABLE_BYTES + (warp - G::LOW_WARPS) * G::WARP_SMEM;
+    float* gstep = reinterpret_cast<float*>(area);                                          // [64]
     float* goff = gstep + 64;                                                               // [64] lo - 16 * step
     uint2* qf = reinterpret_cast<uint2*>(goff + 64);                                        // [3 parts][blocks][32 lanes]
     unsigned char* stage0 = reinterpret_cast<unsigned char*>(qf + 3 * G::NKB * 32);         // two tile buffers
     const int R = p.n_queries;
-    const uint32_t slot = (uint32_t)lane * 4u;
+    const uint32_t slot = (uint32_t)AT_TABLE_ADDR | (uint32_t)lane * 4u;
 
     for (int e = threadIdx.x; e < (1 << (2 * BITS)); e += G::THREADS) {
         // one table entry per thread (all pairs of codes), written to its 32 lane slots
@@ -580,7 +619,7 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
         uint32_t lo2 = 0, hi2 = 0;
         bool fold = !TK;
         if (TK) {
-            rotate_query<D>(qrow, qscale, p.rs, p.kneg, qf, lane, t);
+            rotate_query<D, FAST>(qrow, qscale, p.rs, p.kneg, qf, lane, t);
         } else {
             lo2 = ldg_stream32(reinterpret_cast<const uint32_t*>(k_ranges + (int64_t)group * 128));
             hi2 = ldg_stream32(reinterpret_cast<const uint32_t*>(k_ranges + (int64_t)group * 128 + 64));
@@ -603,14 +642,14 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
             if (!TK && t0 >= group_end) { ++group; group_end += p.group_size; fold = true; }           \
             if (!TK && fold) {                                                                          \
                 fold = false;                                                                           \
-                fold_group(lo2, hi2, qrow, qscale, gstep, goff, qf, bias0, bias1, lane, g, t);          \
+                fold_group<FAST>(lo2, hi2, qrow, qscale, gstep, goff, qf, bias0, bias1, lane, g, t);          \
                 if (group < last_group) {                                                               \
                     lo2 = ldg_stream32(reinterpret_cast<const uint32_t*>(k_ranges + (int64_t)(group + 1) * 128));      \
                     hi2 = ldg_stream32(reinterpret_cast<const uint32_t*>(k_ranges + (int64_t)(group + 1) * 128 + 64)); \
                 }                                                                                       \
             }                                                                                           \
             attn_tile<D, BITS, FAST, TK>(kb + BUF * AT_STAGE_BYTES, vb + BUF * AT_STAGE_BYTES, nb + BUF * AT_STAGE_BYTES, st, qf + lane,  \
-                      bias0, bias1, nvalid, table, slot, g);                                            \
+                      bias0, bias1, nvalid, slot, g);                                                   \
             __syncwarp();                                             /* this buffer is refilled two tiles on */ \
         }
         for (int t0 = w_begin; t0 < w_end; t0 += 32) {

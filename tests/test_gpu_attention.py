@@ -125,6 +125,15 @@ def spec_decoded_turbo(cache, s):
     return out
 
 
+def bf16_pipeline(cache, Qd, scale):
+    """What ``precision="bfloat16"`` stands in for: torch attention in bf16 over the cache decoded to bf16."""
+    import torch
+    ko, vo = cache.decode()
+    out = torch.nn.functional.scaled_dot_product_attention(Qd.bfloat16().unsqueeze(0), ko.bfloat16().unsqueeze(0),
+                                                           vo.bfloat16().unsqueeze(0), scale=scale)
+    return out[0].float().cpu().numpy().astype(np.float64)
+
+
 @pytest.mark.parametrize("d", [64, 128])
 @pytest.mark.parametrize("S,T,R,scale", [(3, 333, 7, None), (2, 5000, 1, None), (1, 31, 8, None), (2, 9000, 5, 1.0), (1, 1, 3, None)])
 def test_turboquant_keys_match_attention_over_spec_decoded_cache(q, S, T, R, scale, d):
@@ -138,13 +147,17 @@ def test_turboquant_keys_match_attention_over_spec_decoded_cache(q, S, T, R, sca
     fast = cache.attend(Qd, scale=scale, precision="bfloat16").cpu().numpy().astype(np.float64)
     assert np.isfinite(got).all() and np.isfinite(fast).all()
     sc = d ** -0.5 if scale is None else scale
+    sdpa = bf16_pipeline(cache, Qd, sc)
     for s in range(S):
         K, V = spec_decoded_turbo(cache, s)
         ref = attention64(Q[s].astype(np.float64), K, V, sc)
         # centroids enter the score product as two bf16 parts (2^-17): a softmax scale of 1.0 (scores eight
         # times larger than usual) carries that into the weights
         assert rows_rel_l2(got[s], ref) < (TOL if scale is None else 1e-4), (s, rows_rel_l2(got[s], ref))
-        assert rows_rel_l2(fast[s], ref) < (1e-2 if scale is None else 5e-2), (s, rows_rel_l2(fast[s], ref))
+        # bf16 operands (centroids and weights each in one bf16): the error class of torch attention over the
+        # cache decoded to bf16 (a few bf16 roundings; observed up to twice its error on short contexts)
+        e_fast, e_sdpa = rows_rel_l2(fast[s], ref), rows_rel_l2(sdpa[s], ref)
+        assert e_fast < 2.5 * e_sdpa + 2e-3, (s, e_fast, e_sdpa)
 
 
 @pytest.mark.parametrize("S,T,R,scale", [(3, 333, 7, None), (2, 5000, 1, None), (1, 31, 8, None), (2, 9000, 5, 1.0), (1, 1, 3, None),
@@ -159,14 +172,13 @@ def test_three_bit_cache_at_dimension_128(q, S, T, R, scale):
     fast = cache.attend(Qd, scale=scale, precision="bfloat16").cpu().numpy().astype(np.float64)
     assert np.isfinite(got).all() and np.isfinite(fast).all()
     sc = 128 ** -0.5 if scale is None else scale
+    sdpa = bf16_pipeline(cache, Qd, sc)
     for s in range(S):
         K, V = spec_decoded_turbo(cache, s)
         ref = attention64(Q[s].astype(np.float64), K, V, sc)
         assert rows_rel_l2(got[s], ref) < (TOL if scale is None else 1e-4), (s, rows_rel_l2(got[s], ref))
-        # over 32,768 random tokens the output is a mean whose norm shrinks as 1/sqrt(T); bf16 operand
-        # rounding does not shrink with it
-        fast_tol = 5e-2 if scale is not None else (2e-2 if T > 10000 else 1e-2)
-        assert rows_rel_l2(fast[s], ref) < fast_tol, (s, rows_rel_l2(fast[s], ref))
+        e_fast, e_sdpa = rows_rel_l2(fast[s], ref), rows_rel_l2(sdpa[s], ref)
+        assert e_fast < 2.5 * e_sdpa + 2e-3, (s, e_fast, e_sdpa)
 
 
 def test_grows_with_the_cache(q):
