@@ -1,8 +1,9 @@
 // Single-token attention straight from the compressed cache (head dimension 64 with per-channel 4-bit
-// or TurboQuant 4-bit keys, head dimension 128 with TurboQuant 4-bit keys; TurboQuant 4-bit values):
-// the decoded cache is never written to memory.  The text below describes dimension 64; at 128 every
-// row is twice as long (eight blocks of 16 channels / coordinates instead of four, four code words
-// per lane instead of two) and a CTA has 8 warps instead of 16, because the accumulators double.  This is the step
+// or TurboQuant 4-bit keys, head dimension 128 with TurboQuant keys of 4 or 3 bits; TurboQuant values of
+// the same width): the decoded cache is never written to memory.  The text below describes dimension
+// 64; at 128 every row is twice as long (eight blocks of 16 channels / coordinates instead of four, four
+// code words per lane instead of two, three with 3-bit codes, whose pairs are 6-bit fields cut out of
+// the words by funnel shifts) and a CTA has 8 warps instead of 16, because the accumulators double.  This is the step
 // the reference names as what has to come next for long contexts (README.md:96, "decoding needs
 // to move inside the attention kernel").
 //
