@@ -244,6 +244,17 @@ typedef struct pitch_cache_state {
 int pitch_enqueue_cache_step(const pitch_cache_desc* desc, const pitch_append_src* src, int in_dtype,
                              pitch_cache_state* state, void* stream);
 
+/* The decoded token at the newest position (tokens - 1) of every plane and segment, gathered into
+ * dst as [n_planes][segments][dim] elements of out_dtype: what a host reads back after a step
+ * (README.md:73-76 reads the decoded buffer on the host) without knowing, on the host, where the
+ * newest token sits.  `state` as for pitch_enqueue_cache_step: NULL -> desc->tokens tokens are held;
+ * non-NULL -> the kernel reads the count from the device-side counter (desc->capacity must be set), so
+ * a captured CUDA graph of (copy the new token in, step, this, copy dst out) can be replayed token
+ * after token.  dst: device memory, 16-byte aligned, dst_bytes >= n_planes * segments * dim *
+ * sizeof(element).  No counterpart in the reference. */
+int pitch_enqueue_cache_newest(const pitch_cache_desc* desc, const pitch_cache_state* state, void* dst,
+                               int64_t dst_bytes, void* stream);
+
 /* Same as pitch_enqueue_cache_append for callers that cannot provide the residual buffer.
  * No counterpart in the reference.  Two kinds of caller are meant: a serving process that hands
  * all device memory to its own arena at start-up and forbids driver allocations afterwards

@@ -84,6 +84,7 @@ PROTOTYPES = {
     "pitch_enqueue_cache_append": (c_int, [POINTER(CacheDesc), POINTER(AppendSrc), c_int, c_int64, c_void_p]),
     "pitch_enqueue_cache_append_noalloc": (c_int, [POINTER(CacheDesc), POINTER(AppendSrc), c_int, c_int64, c_void_p]),
     "pitch_enqueue_cache_step": (c_int, [POINTER(CacheDesc), POINTER(AppendSrc), c_int, c_void_p, c_void_p]),
+    "pitch_enqueue_cache_newest": (c_int, [POINTER(CacheDesc), c_void_p, c_void_p, c_int64, c_void_p]),
     "pitch_cache_attention_workspace": (c_int64, [POINTER(CacheDesc), c_int]),
     "pitch_enqueue_cache_attention": (c_int, [POINTER(CacheDesc), POINTER(AttentionArgs), c_void_p]),
     "pitch_enqueue_rope_bias": (c_int, [c_int, c_int, c_int, c_void_p, c_int64, c_int64, c_int64, c_int64,

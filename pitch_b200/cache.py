@@ -314,6 +314,13 @@ class KVCache:
         """Captures one ``step`` reading the new token from the given tensors (whose storage the
         caller refills before every replay) into a CUDA graph.  Returns the graph; run it with
         ``replay``."""
+        return self.capture(lambda: self.step(keys, values, views=False))
+
+    def capture(self, enqueue):
+        """Captures what ``enqueue()`` puts on the current stream into a CUDA graph: exactly one
+        ``step``, and around it whatever belongs to a generation step - the copy of the new token from
+        pinned host memory, ``newest``, the copy of its result back to the host.  All tensors it touches
+        must stay alive and in place.  Returns the graph; run it with ``replay``."""
         torch = _torch()
         self.use_device_counter()
         if self.tokens >= 1:
@@ -322,9 +329,35 @@ class KVCache:
         graph = torch.cuda.CUDAGraph()
         held = self.tokens
         with torch.cuda.graph(graph, capture_error_mode="thread_local"):
-            self.step(keys, values)
+            enqueue()
+        if self.tokens != held + 1:
+            self.tokens = held
+            raise InvalidInput("the captured function must make exactly one step")
         self.tokens = held                       # capturing queues nothing
         return graph
+
+    def newest(self, out=None, stream=None):
+        """The decoded token at the newest position of every plane and segment, gathered into one
+        contiguous tensor ``[planes, segments, dim]`` of the output dtype (``pitch_enqueue_cache_newest``).
+        With the device-side counter in use the position is read on the device, so the call can be part
+        of a captured step."""
+        torch = _torch()
+        if self.tokens < 1:
+            raise InvalidInput("the cache is empty")
+        dt = self.planes[0].out.dtype
+        shape = (len(self.planes), self.segments, self.dim)
+        if out is None:
+            with self._stream_context(stream):
+                out = torch.empty(shape, dtype=dt, device=self.device)
+        elif (tuple(out.shape) != shape or out.dtype != dt or not out.is_contiguous() or not out.is_cuda
+              or out.device != self.planes[0].out.device):
+            raise InvalidInput(f"out must be a contiguous CUDA tensor of shape {shape} and dtype {dt} on the cache's device")
+        self._desc(self.tokens, False)
+        st = self._lib.pitch_enqueue_cache_newest(self._desc_ref, self._state.data_ptr() if self._state is not None else None,
+                                                  out.data_ptr(), out.numel() * out.element_size(), stream_handle(stream, self.device))
+        if st:
+            _native.check(st)
+        return out
 
     def replay(self, graph):
         """Replays a graph made by ``capture_step``: one more token per segment."""

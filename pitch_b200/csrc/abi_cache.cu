@@ -524,6 +524,46 @@ int pitch_enqueue_cache_step(const pitch_cache_desc* d, const pitch_append_src* 
     return launch_status(false, "cache_step");
 }
 
+int pitch_enqueue_cache_newest(const pitch_cache_desc* d, const pitch_cache_state* state, void* dst, int64_t dst_bytes, void* stream) {
+    if (d == nullptr) return fail(PITCH_ERR_INVALID_INPUT, "descriptor is null");
+    if (d->out_dtype < PITCH_F32 || d->out_dtype > PITCH_BF16) return fail(PITCH_ERR_INVALID_INPUT, "unknown dtype %d", d->out_dtype);
+    if (state != nullptr && d->capacity < 1)
+        return fail(PITCH_ERR_INVALID_INPUT, "reading the newest token with a device-side token counter needs desc->capacity");
+    if (state == nullptr && d->tokens < 1) return fail(PITCH_ERR_INVALID_INPUT, "the cache holds no token");
+    const int64_t held = state != nullptr ? d->capacity : d->tokens;
+    int st;
+    if ((st = check_desc_shape(d, DescNeeds{held, true, 16, d->out_dtype}))) return st;
+    if (d->segments > 0x7FFFFF) return fail(PITCH_ERR_INVALID_INPUT, "segments must be below 2^23");
+    const int64_t row_bytes = (int64_t)d->dim * elem_size(d->out_dtype);
+    if (row_bytes & 15) return fail(PITCH_ERR_INVALID_DIMENSION, "a token row of %lld bytes is not a multiple of 16", (long long)row_bytes);
+    const int64_t need = d->n_planes * d->segments * row_bytes;
+    if (dst == nullptr || !aligned16(dst)) return fail(PITCH_ERR_INVALID_INPUT, "destination must be a 16-byte aligned device pointer");
+    if (dst_bytes < need)
+        return fail(PITCH_ERR_INVALID_INPUT, "destination has %lld bytes; needs %lld", (long long)dst_bytes, (long long)need);
+    if (need > 0x7FFFFFFF) return fail(PITCH_ERR_INVALID_INPUT, "more than 2^31 - 1 bytes of newest tokens");
+    PointerSet extra;
+    extra.add(dst);
+    if (state != nullptr) extra.add(state);
+    int dev;
+    if ((st = check_desc_device(d, true, extra, &dev))) return st;
+    DeviceGuard guard(dev);
+    NewestParams p;
+    p.n_planes = d->n_planes;
+    p.segments = (int)d->segments;
+    p.row_bytes = (int)row_bytes;
+    p.tokens = d->tokens;
+    p.state = reinterpret_cast<const CacheState*>(state);
+    for (int i = 0; i < 4; ++i) {
+        p.out[i] = i < d->n_planes ? static_cast<const unsigned char*>(d->planes[i].out) : nullptr;
+        p.out_seg_stride[i] = i < d->n_planes ? d->planes[i].out_seg_stride : 0;
+    }
+    p.dst = static_cast<unsigned char*>(dst);
+    const int chunks = (int)(need / 16);
+    const int ctas = chunks < 256 * 64 ? (chunks + 255) / 256 : 64;
+    cache_newest_kernel<uint4><<<ctas, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    return launch_status(false, "cache_newest");
+}
+
 // ------------------------------------------------------------------ append without allocations
 // Residual scratch of pitch_enqueue_cache_append_noalloc: lives in the library image, so every
 // GPU that loads the library holds these bytes until the process exits.

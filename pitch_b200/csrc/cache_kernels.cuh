@@ -1093,4 +1093,35 @@ cache_decode_bias_kernel(const __grid_constant__ Cache64Params p) {
     }
 }
 
+// ------------------------------------------------------------------------------------------
+// The decoded token at the newest position of every plane and segment, gathered into one contiguous
+// buffer [plane][segment][dim]: what a host reads back after a step.  The position comes from the
+// device-side token counter when there is one, so a captured graph of (step, this) stays valid
+// from token to token.
+// ------------------------------------------------------------------------------------------
+struct NewestParams {
+    int n_planes, segments;
+    int row_bytes;                     // dim * sizeof(out element), a multiple of 16
+    int64_t tokens;                    // tokens held (read from *state instead when state is set)
+    const CacheState* state;
+    const unsigned char* out[4];
+    int64_t out_seg_stride[4];
+    unsigned char* dst;
+};
+
+template <typename Chunk>                  // uint4: rows are copied in 16-byte chunks
+__global__ void __launch_bounds__(256)
+cache_newest_kernel(const __grid_constant__ NewestParams p) {
+    const int64_t tokens = p.state != nullptr ? p.state->tokens : p.tokens;
+    if (tokens < 1) return;
+    const int cpr = p.row_bytes / (int)sizeof(Chunk);                  // chunks per token row
+    const int total = p.n_planes * p.segments * cpr;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int c = i % cpr, row = i / cpr;
+        const int seg = row % p.segments, pl = row / p.segments;
+        const unsigned char* src = p.out[pl] + (int64_t)seg * p.out_seg_stride[pl] + (tokens - 1) * p.row_bytes + c * (int)sizeof(Chunk);
+        reinterpret_cast<Chunk*>(p.dst)[i] = *reinterpret_cast<const Chunk*>(src);
+    }
+}
+
 }  // namespace pitch

@@ -181,6 +181,61 @@ def test_step_with_device_counter_replays_from_one_cuda_graph(q):
     assert new.counter() == (200, 0)
 
 
+def test_whole_generation_step_from_host_to_host_as_one_graph(q):
+    """What a serving loop does per token, captured once: the new token comes from pinned host memory,
+    the step runs, the newly decoded token of every plane and segment is gathered (its position read from
+    the device-side counter) and goes back to pinned host memory."""
+    import torch
+    from pitch_b200 import ChannelQuantConfig, InvalidInput, KVCache, QuantConfig
+    S, d = 6, 64
+    kcfg, vcfg = ChannelQuantConfig(d, 4, 64), QuantConfig("turboQuant", d, 4)
+    K, V = _data(S, 200, d, 15, torch.float32, q.device)
+    Kh, Vh = K.cpu(), V.cpu()
+    cache = KVCache(S, d, 256, kcfg, vcfg, pitch=q)
+    with pytest.raises(InvalidInput):
+        cache.newest()                                                   # nothing held yet
+    cache.prefill(K[:, :70].contiguous(), V[:, :70].contiguous())
+    # direct call, host-side count
+    cache.decode()
+    got = cache.newest()
+    torch.cuda.synchronize()
+    assert got.shape == (2, S, d) and got.dtype == torch.bfloat16
+    assert torch.equal(got[0], cache.planes[0].out[:, 69]) and torch.equal(got[1], cache.planes[1].out[:, 69])
+    with pytest.raises(InvalidInput):
+        cache.newest(out=torch.empty((2, S, d), device=q.device))        # wrong dtype
+    host_in = torch.empty((2, S, 1, d)).pin_memory()
+    host_out = torch.empty((2, S, d), dtype=torch.bfloat16).pin_memory()
+    dev_in = torch.empty((2, S, 1, d), device=q.device)
+    dev_new = torch.empty((2, S, d), dtype=torch.bfloat16, device=q.device)
+
+    def one_step():
+        dev_in.copy_(host_in, non_blocking=True)
+        cache.step(dev_in[0], dev_in[1], views=False)
+        cache.newest(out=dev_new)
+        host_out.copy_(dev_new, non_blocking=True)
+
+    graph = cache.capture(one_step)
+    assert cache.tokens == 70
+    ref = KVCache(S, d, 256, kcfg, vcfg, pitch=q)
+    ref.prefill(K[:, :70].contiguous(), V[:, :70].contiguous())
+    for t in range(70, 200):
+        host_in[0].copy_(Kh[:, t:t + 1])
+        host_in[1].copy_(Vh[:, t:t + 1])
+        cache.replay(graph)
+        torch.cuda.synchronize()
+        ref.append(K[:, t:t + 1].contiguous(), V[:, t:t + 1].contiguous())
+        if t % 13 == 0 or t in (127, 128, 199):
+            ko, vo = ref.decode()
+            torch.cuda.synchronize()
+            assert torch.equal(host_out[0], ko[:, t].cpu()), t
+            assert torch.equal(host_out[1], vo[:, t].cpu()), t
+    ref.decode()
+    torch.cuda.synchronize()
+    _assert_same(ref, cache, "host-to-host graph")
+    with pytest.raises(InvalidInput):
+        cache.capture(lambda: None)                                      # no step inside
+
+
 def test_stepped_cache_against_the_cpu_oracles(q):
     """The stepped cache itself against the specification: per-channel keys bit-exact (codes,
     ranges, decoded values after rounding to bf16), TurboQuant value codes bit-exact against the

@@ -151,6 +151,21 @@ def test_cache_entry_points_check_extents_before_any_device_work(lib):
     assert lib.pitch_enqueue_cache_append_noalloc(C.byref(d), src_for(d), 0, 1, None) == 1 and b"group size" in err()
 
 
+def test_newest_token_gather_checks_its_arguments(lib):
+    import ctypes as C
+    f = lib.pitch_enqueue_cache_newest
+    d = _cache_desc()
+    need = 2 * 48 * 64 * 2
+    assert f(C.byref(d), None, None, need, None) == 1 and b"destination" in lib.pitch_last_error()
+    assert f(C.byref(d), None, 0x50008, need, None) == 1 and b"aligned" in lib.pitch_last_error()
+    assert f(C.byref(d), None, 0x50000, need - 1, None) == 1 and b"needs 12288" in lib.pitch_last_error()
+    assert f(C.byref(_cache_desc(tokens=0)), None, 0x50000, need, None) == 1 and b"no token" in lib.pitch_last_error()
+    assert f(C.byref(d), 0x60000, 0x50000, need, None) == 1 and b"capacity" in lib.pitch_last_error()   # counter without capacity
+    d.planes[1].out_bytes = 47 * (1 << 30) + 32768 * 64 * 2 - 1
+    assert f(C.byref(d), None, 0x50000, need, None) == 1 and b"output buffer" in lib.pitch_last_error()
+    assert f(None, None, 0x50000, need, None) == 1
+
+
 def test_attention_workspace_and_shape_rules(lib):
     """Pure host logic of the cache attention entry point: run partitioning and refusals."""
     import ctypes as C
