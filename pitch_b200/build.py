@@ -66,7 +66,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     todo = sources() if force else _stale_objects()
 
     def compile_one(src: Path):
-        cmd = [nvcc, *NVCC_FLAGS, "-split-compile", "2", "-c", str(src), "-o", str(_obj(src))]
+        cmd = [nvcc, *NVCC_FLAGS, "-c", str(src), "-o", str(_obj(src))]
         if verbose:
             cmd[1:1] = ["-Xptxas", "-v"]
             print(" ".join(cmd), file=sys.stderr)

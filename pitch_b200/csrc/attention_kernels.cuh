@@ -554,8 +554,10 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
     unsigned char* table = smem + (AT_TABLE_ADDR - smem_addr);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    unsigned char* area = warp < G::LOW_WARPS ? smem + warp * G::WARP_SMEM
-                                              : table + CD_TABLE_BYTES + (warp - G::LOW_WARPS) * G::WARP_SMEM;
+    // (one base pointer plus an offset, so that every access stays a plain shared-memory access)
+    const uint32_t area_offset = warp < G::LOW_WARPS ? (uint32_t)(warp * G::WARP_SMEM)
+        : (uint32_t)(AT_TABLE_ADDR + CD_TABLE_BYTES + (warp - G::LOW_WARPS) * G::WARP_SMEM) - smem_addr;
+    unsigned char* area = smem + area_offset;
     float* gstep = reinterpret_cast<float*>(area);                                          // [64]
     float* goff = gstep + 64;                                                               // [64] lo - 16 * step
     uint2* qf = reinterpret_cast<uint2*>(goff + 64);                                        // [3 parts][blocks][32 lanes]
