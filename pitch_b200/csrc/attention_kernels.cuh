@@ -175,12 +175,17 @@ __device__ __forceinline__ void issue_attn_tile(unsigned char* stage, const unsi
         constexpr int CPR = G::ROWB / 16;                           // 16-byte chunks per token row
 #pragma unroll
         for (int i = 0; i < CPR; ++i) {
-            const int c = lane + 32 * i, token = c / CPR;            // chunk c of the tile's code bytes
+            const int c = lane + 32 * i, token = c / CPR;            // chunk c of the tile's key bytes
             const int live = token < nvalid ? 16 : 0;
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
                          :: "r"(base + c * 16), "l"(live ? ksrc + c * 16 : ksrc), "r"(live) : "memory");
+            // value rows are VPITCH apart (3 or 5 chunks): eight lanes that write the SAME chunk of eight
+            // consecutive rows land in eight different bank groups, eight consecutive chunks do not
+            const int idx = (lane >> 3) + 4 * i, vtoken = (idx / CPR) * 8 + (lane & 7), part = idx % CPR;
+            const int vlive = vtoken < nvalid ? 16 : 0;
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
-                         :: "r"(base + G::STAGE_K + token * G::VPITCH + (c % CPR) * 16), "l"(live ? vsrc + c * 16 : vsrc), "r"(live) : "memory");
+                         :: "r"(base + G::STAGE_K + vtoken * G::VPITCH + part * 16),
+                            "l"(vlive ? vsrc + (vtoken * CPR + part) * 16 : vsrc), "r"(vlive) : "memory");
         }
     } else {
         // rows of 48 bytes: 8-byte pieces, so that a piece never straddles two rows
