@@ -34,10 +34,10 @@ extern "C" {
 // -------------------------------------------------------------------------------- attention
 // How a segment's tokens are cut into runs (one warp each).  Depends on the shape and on the GPU's
 // multiprocessor count only, so that the workspace size can be computed ahead of the call: runs of
-// whole 32-token tiles, about one run per warp that the GPU keeps resident (16 per multiprocessor at
-// head dimension 64, 8 at 128), at least 4 tiles long.
-static void attention_slices(int sms, int dim, int64_t segments, int64_t tokens, int* splits, int* tokens_per_split) {
-    const int64_t tiles = ceil_div(tokens, 32), slots = (int64_t)sms * (dim == 64 ? AttnGeom<64>::WARPS : AttnGeom<128>::WARPS);
+// whole 32-token tiles, about one run per warp that the GPU keeps resident (`warps` per multiprocessor:
+// attn_warps), at least 4 tiles long.
+static void attention_slices(int sms, int warps, int64_t segments, int64_t tokens, int* splits, int* tokens_per_split) {
+    const int64_t tiles = ceil_div(tokens, 32), slots = (int64_t)sms * warps;
     int64_t run = ceil_div(segments * tiles, slots);
     if (run < 4) run = 4;
     // rounding the runs per segment up must not push the total past the resident warps: a few
@@ -75,8 +75,14 @@ static int check_attention_shape(const pitch_cache_desc* d, int n_queries) {
 
 int64_t pitch_cache_attention_workspace(const pitch_cache_desc* d, int n_queries) {
     if (check_attention_shape(d, n_queries)) return -1;
-    int splits, tps;
-    attention_slices(desc_sm_count(d), d->dim, d->segments, d->tokens, &splits, &tps);
+    // the run layout can depend on the precision of the call (attn_warps): room for either
+    const int sms = desc_sm_count(d);
+    int splits = 0;
+    for (int fast = 0; fast < 2; ++fast) {
+        int sp, tps;
+        attention_slices(sms, attn_warps(d->dim, d->planes[1].bits, fast != 0), d->segments, d->tokens, &sp, &tps);
+        if (sp > splits) splits = sp;
+    }
     return d->segments * splits * n_queries * (2 + d->dim) * (int64_t)sizeof(float);
 }
 
@@ -119,7 +125,9 @@ int pitch_enqueue_cache_attention(const pitch_cache_desc* d, const pitch_attenti
     memset(&p, 0, sizeof p);
     p.segments = (int)d->segments;
     p.tokens = (int)d->tokens;
-    attention_slices(sm_count(), d->dim, d->segments, d->tokens, &p.splits, &p.tokens_per_split);
+    const bool fast = a->precision == PITCH_ATTENTION_BF16;
+    const int warps = attn_warps(d->dim, d->planes[1].bits, fast);
+    attention_slices(sm_count(), warps, d->segments, d->tokens, &p.splits, &p.tokens_per_split);
     if ((int64_t)p.segments * p.splits > 0x7FFFFFFF) return fail(PITCH_ERR_INVALID_INPUT, "segments x runs exceeds 2^31 - 1");
     p.n_queries = a->n_queries;
     const bool turbo_keys = d->planes[0].kind == PITCH_PLANE_TURBO;
@@ -148,7 +156,6 @@ int pitch_enqueue_cache_attention(const pitch_cache_desc* d, const pitch_attenti
         const bool wide = d->dim == 128;
         // all the shared memory a block may have: the kernel's table must sit at a fixed shared-memory address
         const int smem = AT_SMEM_BYTES;
-        const int warps = wide ? AttnGeom<128>::WARPS : AttnGeom<64>::WARPS;
         static std::atomic<bool> configured[64];
         if (dev >= 0 && dev < 64 && !configured[dev].load(std::memory_order_acquire)) {
             int optin = 0;
@@ -166,7 +173,7 @@ int pitch_enqueue_cache_attention(const pitch_cache_desc* d, const pitch_attenti
                 return launch_status(false, "cache_attention (shared memory opt-in)");
             configured[dev].store(true, std::memory_order_release);
         }
-        // one CTA per SM (16 warps at dim 64, 8 at dim 128); a warp takes runs warp, warp + all warps, ...
+        // one CTA per SM (attn_warps warps); a warp takes runs warp, warp + all warps, ...
         int64_t ctas = ceil_div((int64_t)p.segments * p.splits, warps);
         if (ctas > sm_count()) ctas = sm_count();
         // Both launches are programmatic dependent launches: each grid may be scheduled while the
@@ -182,7 +189,6 @@ int pitch_enqueue_cache_attention(const pitch_cache_desc* d, const pitch_attenti
         cfg.stream = s;
         cfg.attrs = pdl;
         cfg.numAttrs = 1;
-        const bool fast = a->precision == PITCH_ATTENTION_BF16;
         if (wide && vbits == 3) {
             if (fast) cudaLaunchKernelEx(&cfg, attention_partial_kernel<128, 3, true, true>, p);
             else cudaLaunchKernelEx(&cfg, attention_partial_kernel<128, 3, false, true>, p);

@@ -64,25 +64,41 @@ constexpr int AT_TABLE_ADDR = 0x10000;      // shared-memory address of the cent
 constexpr int AT_SMEM_RESERVED = 1024;      // start of a block's dynamic shared memory when it takes all there is
 constexpr int AT_SMEM_BYTES = 232448;       // dynamic shared memory of a launch: the most a block may have (227 KB)
 
-// Sizes for head dimension D (64 or 128) and code width BITS (4; 3 at D = 128).
+// Warps of a CTA (one CTA per multiprocessor): 16 at head dimension 64, 8 at 128 where the accumulators
+// double - and 10 there for 4-bit codes with bf16 operands, the one variant that measured faster with
+// more warps than that (20 warps at dimension 64 fit in 96 registers but ran slower: the shared-memory
+// pipe, not the latency of a warp's own chain, is what the extra warps queue on).
+__host__ __device__ constexpr int attn_warps(int dim, int bits, bool fast) {
+    return dim == 64 ? 16 : (bits == 4 && fast ? 10 : 8);
+}
+
+// Sizes of a tile for head dimension D (64 or 128) and code width BITS (4; 3 at D = 128).
 template <int D, int BITS = 4> struct AttnGeom {
-    static constexpr int WARPS = D == 64 ? 16 : 8;             // warps per CTA (one CTA per multiprocessor)
-    static constexpr int THREADS = WARPS * 32;
     static constexpr int NKB = D / 16;                         // blocks of 16 channels / coordinates
     static constexpr int ROWB = D * BITS / 8;                  // bytes of codes per token
     static constexpr int VPITCH = ROWB + (BITS == 4 ? 16 : 8); // value rows padded (bank spread)
     static constexpr int PART_FLOATS = 2 + D;                  // per (segment, run, query): max, sum, D accumulators
     static constexpr int STAGE_K = 32 * ROWB;                  // a tile's key codes
     static constexpr int STAGE_V = 32 * VPITCH;                // a tile's value codes
-    static constexpr int STAGE_BYTES = STAGE_K + STAGE_V + 256;          // + 32 value norms + 32 key norms (TurboQuant keys)
-    // per warp: per-group steps and offsets of the keys; query fragments (3 parts); two tile buffers (one in flight)
-    static constexpr int WARP_SMEM = 512 + 3 * NKB * 32 * 8 + 2 * STAGE_BYTES;
+};
+
+// Layout of a CTA's shared memory for one kernel variant.
+template <int D, int BITS, bool FAST, bool TK> struct AttnCta {
+    typedef AttnGeom<D, BITS> G;
+    static constexpr int WARPS = attn_warps(D, BITS, FAST);
+    static constexpr int THREADS = WARPS * 32;
+    static constexpr int QF_PARTS = FAST ? 2 : 3;                                   // bf16 parts of the query kept
+    static constexpr int RANGE_BYTES = TK ? 0 : 512;                                // per-group steps and offsets of per-channel keys
+    static constexpr int STAGE_BYTES = G::STAGE_K + G::STAGE_V + (TK ? 256 : 128);   // + 32 value norms (+ 32 key norms)
+    // per warp: [steps, offsets;] query fragments; two tile buffers (one in flight)
+    static constexpr int WARP_SMEM = RANGE_BYTES + QF_PARTS * G::NKB * 32 * 8 + 2 * STAGE_BYTES;
     // The centroid table sits at shared-memory address AT_TABLE_ADDR exactly (see table_word), the warps'
     // areas below and above it.  The kernel is launched with all the shared memory a block may have
     // (AT_SMEM_BYTES of dynamic memory), which pins the start of its dynamic memory to an address of
     // 0 ... AT_SMEM_RESERVED: a later start would not fit the multiprocessor and the launch would fail.
-    static constexpr int LOW_WARPS = (AT_TABLE_ADDR - AT_SMEM_RESERVED) / WARP_SMEM;    // areas below the table
-    static_assert(LOW_WARPS >= 1 && LOW_WARPS < WARPS, "warps' areas on both sides of the table");
+    static constexpr int LOW_FIT = (AT_TABLE_ADDR - AT_SMEM_RESERVED) / WARP_SMEM;
+    static constexpr int LOW_WARPS = LOW_FIT < WARPS - 1 ? LOW_FIT : WARPS - 1;     // areas below the table
+    static_assert(LOW_WARPS >= 1, "warps' areas on both sides of the table");
     static_assert(AT_TABLE_ADDR + CD_TABLE_BYTES + (WARPS - LOW_WARPS) * WARP_SMEM <= AT_SMEM_BYTES, "the areas above the table must fit");
 };
 
@@ -547,12 +563,13 @@ __device__ __forceinline__ void rotate_query(const float* __restrict__ qrow, flo
 }
 
 template <int D, int BITS, bool FAST, bool TK>
-__global__ void __launch_bounds__(AttnGeom<D, BITS>::THREADS, 1)
+__global__ void __launch_bounds__(AttnCta<D, BITS, FAST, TK>::THREADS, 1)
 attention_partial_kernel(const __grid_constant__ AttentionParams p) {
     static_assert(D == 64 || TK, "per-channel keys are handled at head dimension 64 only");
     static_assert(BITS == 4 || (BITS == 3 && D == 128 && TK), "3-bit codes are handled at head dimension 128 with TurboQuant keys");
     typedef AttnGeom<D, BITS> G;
-    constexpr int AT_WARPS = G::WARPS, AT_STAGE_BYTES = G::STAGE_BYTES, AT_PART_FLOATS = G::PART_FLOATS;
+    typedef AttnCta<D, BITS, FAST, TK> C;
+    constexpr int AT_WARPS = C::WARPS, AT_STAGE_BYTES = C::STAGE_BYTES, AT_PART_FLOATS = G::PART_FLOATS;
     extern __shared__ __align__(1024) unsigned char smem[];
     // the table at shared address AT_TABLE_ADDR; warps 0 ... LOW_WARPS - 1 below it, the others above
     const uint32_t smem_addr = (uint32_t)__cvta_generic_to_shared(smem);            // <= AT_SMEM_RESERVED
@@ -560,17 +577,17 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     // (one base pointer plus an offset, so that every access stays a plain shared-memory access)
-    const uint32_t area_offset = warp < G::LOW_WARPS ? (uint32_t)(warp * G::WARP_SMEM)
-        : (uint32_t)(AT_TABLE_ADDR + CD_TABLE_BYTES + (warp - G::LOW_WARPS) * G::WARP_SMEM) - smem_addr;
+    const uint32_t area_offset = warp < C::LOW_WARPS ? (uint32_t)(warp * C::WARP_SMEM)
+        : (uint32_t)(AT_TABLE_ADDR + CD_TABLE_BYTES + (warp - C::LOW_WARPS) * C::WARP_SMEM) - smem_addr;
     unsigned char* area = smem + area_offset;
-    float* gstep = reinterpret_cast<float*>(area);                                          // [64]
+    float* gstep = reinterpret_cast<float*>(area);                                          // [64] (per-channel keys only)
     float* goff = gstep + 64;                                                               // [64] lo - 16 * step
-    uint2* qf = reinterpret_cast<uint2*>(goff + 64);                                        // [3 parts][blocks][32 lanes]
-    unsigned char* stage0 = reinterpret_cast<unsigned char*>(qf + 3 * G::NKB * 32);         // two tile buffers
+    uint2* qf = reinterpret_cast<uint2*>(area + C::RANGE_BYTES);                            // [parts][blocks][32 lanes]
+    unsigned char* stage0 = reinterpret_cast<unsigned char*>(qf + C::QF_PARTS * G::NKB * 32);   // two tile buffers
     const int R = p.n_queries;
     const uint32_t slot = (uint32_t)AT_TABLE_ADDR | (uint32_t)lane * 4u;
 
-    for (int e = threadIdx.x; e < (1 << (2 * BITS)); e += G::THREADS) {
+    for (int e = threadIdx.x; e < (1 << (2 * BITS)); e += C::THREADS) {
         // one table entry per thread (all pairs of codes), written to its 32 lane slots
         uint32_t hi, lo;
         split_pair(p.book.c[e & ((1 << BITS) - 1)], p.book.c[e >> BITS], hi, lo);
