@@ -11,6 +11,7 @@
 #include <atomic>
 #include <cstring>
 #include <mutex>
+#include <type_traits>
 
 #include "append_kernels.cuh"
 #include "cache_kernels.cuh"
@@ -222,7 +223,7 @@ int launch_cache64_impl(const Cache64Params& p, int64_t tokens_for_grid, cudaStr
     constexpr int smem = cache64_smem_bytes<T>();
     if (dev >= 0 && dev < 64 && !configured[dev].load(std::memory_order_acquire)) {
         // idempotent: two threads racing here both set the same attribute
-        if (cudaFuncSetAttribute(cache_decode_kernel<T, D, BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(cache_decode_kernel<T, D, BITS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
             return launch_status(false, "cache_decode (shared memory opt-in)");
         configured[dev].store(true, std::memory_order_release);
     }
@@ -244,13 +245,17 @@ int launch_cache64_impl(const Cache64Params& p, int64_t tokens_for_grid, cudaStr
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaLaunchKernelEx(&cfg, cache_decode_kernel<T, D, BITS>, p);
+    cudaLaunchKernelEx(&cfg, cache_decode_kernel<T, D, BITS, false>, p);
     return PITCH_OK;
 }
 
-// dim in {64, 128}, bits (of the TurboQuant planes) in {3, 4}
+// dim in {64, 128}, bits (of the TurboQuant planes) in {3, 4}.  A cache that mixes per-channel and
+// TurboQuant planes takes the kernel that deals its items by drawn tickets (instances in abi_cache_tickets.cu).
 template <typename T>
 int launch_cache64(const Cache64Params& p, int dim, int bits, int64_t tokens_for_grid, cudaStream_t s) {
+    bool turbo = false, channel = false;
+    for (int i = 0; i < p.n_planes; ++i) (p.plane[i].kind == 0 ? turbo : channel) = true;
+    if (turbo && channel) return launch_cache64_tickets(p, dim, bits, std::is_same<T, float>::value ? PITCH_F32 : (std::is_same<T, __half>::value ? PITCH_F16 : PITCH_BF16), tokens_for_grid, s);
     if (dim == 64)
         return bits == 4 ? launch_cache64_impl<T, 64, 4>(p, tokens_for_grid, s) : launch_cache64_impl<T, 64, 3>(p, tokens_for_grid, s);
     return bits == 4 ? launch_cache64_impl<T, 128, 4>(p, tokens_for_grid, s) : launch_cache64_impl<T, 128, 3>(p, tokens_for_grid, s);

@@ -71,6 +71,8 @@ int cache64_single_plane(int kind, int dim, int bits, int group_size, uint32_t s
 // The same kernel family with exact key-bias removal on plane 0 (abi_cache_bias.cu); `p` carries the
 // bias row pointer and the rotary tables.  dim in {64, 128}, bits (of the TurboQuant planes) in {3, 4}.
 int launch_cache64_bias(const pitch::Cache64Params& p, int dim, int bits, int dtype, int64_t tokens_for_grid, cudaStream_t s);
+// The whole-cache launch with its items dealt by drawn tickets (cache_decode_kernel<..., true>): abi_cache_tickets.cu.
+int launch_cache64_tickets(const pitch::Cache64Params& p, int dim, int bits, int dtype, int64_t tokens_for_grid, cudaStream_t s);
 
 }  // namespace pitch_abi
 

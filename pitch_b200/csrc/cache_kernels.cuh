@@ -710,7 +710,17 @@ __device__ __forceinline__ void channel_step_warp(const Plane64& P, const StepPl
 //     of a per-channel plane's newest group (re-quantised from the residual) and the item that
 //     receives the new TurboQuant vector (encoded by the warp that decodes it).  One warp each,
 //     taken first, by the warps that come last in the round-robin of the main items.
-template <typename T, int D, int BITS>
+//
+// TICKETS selects how the main items are dealt to the warps.  false: a fixed deal - warp w of CTA c is
+// worker w * gridDim + c and takes every (gridDim * 16)-th position, planes innermost; nothing to compute
+// per item.  true: the positions are dealt to the CTAs round-robin and the warps of a CTA draw them, one
+// plane at a time, from a counter in shared memory as they become free: no warp idles at the end while
+// another still has a whole item more to do, and warps that got the costlier items fall behind no one.
+// That costs about 30 instructions per item.  It pays for a cache that mixes per-channel (cheap) and
+// TurboQuant (costly) planes - 2.7 % of the whole step at config 4's size, 12 % for an eighth of it, where
+// a warp has five items - and does not for a cache of TurboQuant planes only, whose launch is bound by
+// instruction issue (6 % slower at config 5's shape): the host picks.
+template <typename T, int D, int BITS, bool TICKETS>
 __global__ void __launch_bounds__(CD_THREADS, 1)
 cache_decode_kernel(const __grid_constant__ Cache64Params p) {
     constexpr int TOKENS = Item64<D>::TOKENS, LPV = Item64<D>::LPV;
@@ -743,6 +753,8 @@ cache_decode_kernel(const __grid_constant__ Cache64Params p) {
         }
         if (threadIdx.x < (1 << BITS) - 1) s_edges[threadIdx.x] = 0.5f * (p.book.c[threadIdx.x] + p.book.c[threadIdx.x + 1]);
     }
+    int* s_next = reinterpret_cast<int*>(s_edges) + 15;       // the CTA's work counter (the boundaries use 15 slots at most)
+    if (TICKETS && threadIdx.x == 0) *s_next = 0;
     __syncthreads();
     // Everything above touched only kernel parameters and shared memory.  Under programmatic
     // dependent launch this grid may have started before the previous kernel of the stream ended:
@@ -807,6 +819,29 @@ cache_decode_kernel(const __grid_constant__ Cache64Params p) {
         }
         return c.seg < p.segments;
     };
+    // The drawn deal.  A ticket is drawn (by lane 0) one item ahead of its use, so that the counter's
+    // latency is never on the warp's path: ticket() while an item is decoded, resolve() when the next one
+    // is to be fetched.  (segments x items fits 31 bits: the host checks it.)
+    const int positions = p.segments * full_items;
+    const int my_positions = positions > (int)blockIdx.x ? (positions - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const float inv_items = full_items > 0 ? 1.0f / (float)full_items : 0.0f;
+    auto ticket = [&]() { return lane == 0 ? atomicAdd(s_next, 1) : 0; };
+    auto resolve = [&](int drawn, Cursor64& c) {
+        const int k = __shfl_sync(0xFFFFFFFFu, drawn, 0);
+        const int np = p.n_planes;
+        const int kp = np == 2 ? (k >> 1) : (np == 1 ? k : k / np);
+        if (kp >= my_positions) return false;
+        const int pos = (int)blockIdx.x + (int)gridDim.x * kp;
+        c.pl = k - kp * np;
+        // pos / full_items without an integer division: the float quotient is within one of it
+        int seg = (int)((float)pos * inv_items);
+        int item = pos - seg * full_items;
+        if (item < 0) { --seg; item += full_items; }
+        if (item >= full_items) { ++seg; item -= full_items; }
+        c.seg = seg;
+        c.item = item;
+        return true;
+    };
 
     if (!refuse) {
     // ---- edge items: the partial last item and everything an append touches
@@ -845,7 +880,30 @@ cache_decode_kernel(const __grid_constant__ Cache64Params p) {
     }
 
     // ---- main items, software pipelined with two register buffers used alternately
-    if (full_items > 0) {
+    if constexpr (TICKETS) {
+        if (full_items > 0) {
+            Cursor64 cur, nxt;
+            int drawn = ticket();
+            if (resolve(drawn, cur)) {
+                Prefetch64 fa, fb;
+                fetch(cur, fa);
+                drawn = ticket();
+#pragma unroll 1
+                while (true) {
+                    bool more = resolve(drawn, nxt);
+                    if (more) { fetch(nxt, fb); drawn = ticket(); }
+                    decode(cur, fa);
+                    if (!more) break;
+                    cur = nxt;
+                    more = resolve(drawn, nxt);
+                    if (more) { fetch(nxt, fa); drawn = ticket(); }
+                    decode(cur, fb);
+                    if (!more) break;
+                    cur = nxt;
+                }
+            }
+        }
+    } else if (full_items > 0) {
         Cursor64 cur;
         cur.pl = 0;
         cur.seg = warp_id / full_items;
