@@ -36,7 +36,7 @@ struct PointerSet {
     void add(const void* q) { if (q != nullptr && n < 24) p[n++] = q; }
 };
 
-struct VerdictCache {
+struct CheckedPointers {
     static const int SLOTS = 16;
     std::mutex lock;
     PointerSet key[SLOTS];
@@ -58,7 +58,7 @@ struct VerdictCache {
         key[slot] = k;
         device[slot] = dev;
     }
-} g_verdicts;
+} g_checked;
 
 // Asks the driver about one pointer: device (or managed) memory, and of which GPU.
 int pointer_device(const void* ptr, const char* what, int plane, int* dev) {
@@ -160,7 +160,7 @@ int check_desc_device(const pitch_cache_desc* d, bool with_out, const PointerSet
         key.add(d->key_bias->sin_table);
     }
     for (int i = 0; i < extra.n; ++i) key.add(extra.p[i]);
-    if (g_verdicts.find(key, device)) return PITCH_OK;
+    if (g_checked.find(key, device)) return PITCH_OK;
     int dev = -1, st, at = 0;
     for (int i = 0; i < d->n_planes; ++i) {
         if ((st = pointer_device(key.p[at++], "codes", i, &dev))) return st;
@@ -170,7 +170,7 @@ int check_desc_device(const pitch_cache_desc* d, bool with_out, const PointerSet
     for (; at < key.n; ++at)
         if ((st = pointer_device(key.p[at], "auxiliary buffer (key-bias tables, residual, token counter)", 0, &dev))) return st;
     if (dev < 0) cudaGetDevice(&dev);
-    g_verdicts.store(key, dev);
+    g_checked.store(key, dev);
     *device = dev;
     return PITCH_OK;
 }

@@ -824,7 +824,7 @@ cache_decode_kernel(const __grid_constant__ Cache64Params p) {
     // is to be fetched.  (segments x items fits 31 bits: the host checks it.)
     const int positions = p.segments * full_items;
     const int my_positions = positions > (int)blockIdx.x ? (positions - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
-    const float inv_items = full_items > 0 ? 1.0f / (float)full_items : 0.0f;
+    const float inv_items = full_items > 0 ? __frcp_rd(__int2float_ru(full_items)) : 0.0f;     // never above 1 / full_items
     auto ticket = [&]() { return lane == 0 ? atomicAdd(s_next, 1) : 0; };
     auto resolve = [&](int drawn, Cursor64& c) {
         const int k = __shfl_sync(0xFFFFFFFFu, drawn, 0);
@@ -833,10 +833,10 @@ cache_decode_kernel(const __grid_constant__ Cache64Params p) {
         if (kp >= my_positions) return false;
         const int pos = (int)blockIdx.x + (int)gridDim.x * kp;
         c.pl = k - kp * np;
-        // pos / full_items without an integer division: the float quotient is within one of it
-        int seg = (int)((float)pos * inv_items);
+        // pos / full_items without an integer division: every rounding of the float quotient goes down, so
+        // it is the quotient or one less (segments < 2^16 keeps the error below one)
+        int seg = __float2int_rd(__fmul_rd(__int2float_rd(pos), inv_items));
         int item = pos - seg * full_items;
-        if (item < 0) { --seg; item += full_items; }
         if (item >= full_items) { ++seg; item -= full_items; }
         c.seg = seg;
         c.item = item;

@@ -205,3 +205,54 @@ def test_decode_and_attention_replay_from_a_cuda_graph(q):
     torch.cuda.synchronize()
     ko2, vo2 = (pl.out[:, :T] for pl in cache.planes)
     assert torch.equal(ko2, want[0]) and torch.equal(vo2, want[1]) and torch.equal(out, want[2])
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("n_planes", [1, 3, 4])
+def test_descriptors_with_one_three_and_four_planes(q, n_planes, d):
+    """The C descriptor takes 1...4 planes.  A launch over the planes of two caches at once (per-channel and
+    TurboQuant planes mixed: the kernel that deals its items by drawn tickets, with a plane count that is
+    not a power of two) must write what the caches' own two-plane launches write."""
+    import ctypes as C
+
+    import torch
+    from pitch_b200 import ChannelQuantConfig, KVCache, QuantConfig, _native
+    from pitch_b200.codec import stream_handle
+    S, T = 5, 777
+    rng = np.random.default_rng(77)
+    caches = []
+    for i in range(2):
+        cache = KVCache(S, d, T, ChannelQuantConfig(d, 4, 64), QuantConfig("turboQuant", d, 4, seed=11 + i), out_dtype="bfloat16", pitch=q)
+        K = torch.from_numpy((rng.standard_normal((S, T, d)) + 1.5).astype(np.float32)).to(q.device)
+        V = torch.from_numpy(rng.standard_normal((S, T, d)).astype(np.float32)).to(q.device)
+        cache.prefill(K, V)
+        caches.append(cache)
+    planes = [caches[0].planes[0], caches[0].planes[1], caches[1].planes[1], caches[1].planes[0]][:n_planes]
+    if n_planes == 1:
+        planes = [caches[0].planes[1]]
+    want = []
+    for cache in caches:
+        cache.decode()
+    torch.cuda.synchronize()
+    for pl in planes:
+        want.append(pl.out[:, :T].clone())
+        pl.out.zero_()
+    desc = _native.CacheDesc()
+    desc.dim, desc.out_dtype, desc.segments, desc.tokens, desc.n_planes = d, 2, S, T, n_planes
+    for i, pl in enumerate(planes):
+        p = desc.planes[i]
+        p.kind = pl.kind
+        p.bits = pl.config.bits
+        p.group_size = pl.config.group_size if pl.is_channel else 0
+        p.seed = 0 if pl.is_channel else pl.config.seed
+        for name in ("codes", "side", "out"):
+            t = getattr(pl, name)
+            setattr(p, name, t.data_ptr())
+            setattr(p, name + "_seg_stride", t.stride(0) * t.element_size())
+            setattr(p, name + "_bytes", t.numel() * t.element_size())
+    lib = _native.lib()
+    st = lib.pitch_enqueue_cache_decode(C.byref(desc), stream_handle(None, q.device))
+    assert st == 0, lib.pitch_last_error()
+    torch.cuda.synchronize()
+    for pl, w in zip(planes, want):
+        assert torch.equal(pl.out[:, :T].view(torch.int16), w.view(torch.int16)), pl.name
