@@ -439,9 +439,11 @@ def run_ours(args) -> None:
         # the whole step is captured once (KVCache.capture) and replayed per token: one graph launch per step
         graph = cache.capture(enqueue_step)
 
+        host_in_np, hkv_np = host_in.numpy(), hkv.numpy()
+
         def e2e_step(i):
-            host_in.copy_(hkv[i])                               # the caller's new token, written into pinned memory
-            cache.replay(graph)
+            np.copyto(host_in_np, hkv_np[i])                    # the caller's new token, written into pinned memory
+            cache.replay(graph, views=False)
             stream.synchronize()                                # the host holds the step's result
             return cache.tokens
 

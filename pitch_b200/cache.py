@@ -359,13 +359,14 @@ class KVCache:
             _native.check(st)
         return out
 
-    def replay(self, graph):
-        """Replays a graph made by ``capture_step``: one more token per segment."""
+    def replay(self, graph, views: bool = True):
+        """Replays a graph made by ``capture_step`` / ``capture``: one more token per segment.  Returns the
+        decoded planes as ``step`` does (``views=False``: nothing, for a loop that reads its results elsewhere)."""
         if self.tokens >= self.capacity:
             raise InvalidInput(f"cache holds {self.tokens} of {self.capacity} tokens; cannot append 1")
         graph.replay()
         self.tokens += 1
-        return tuple(pl.out[:, :self.tokens] for pl in self.planes)
+        return tuple(pl.out[:, :self.tokens] for pl in self.planes) if views else None
 
     def prefill(self, keys, values, stream=None) -> None:
         """Bulk-encodes ``[segments, T, dim]`` tensors into an empty cache with the stand-alone
