@@ -443,7 +443,7 @@ def run_ours(args) -> None:
     e2e_full = None
     if not args.kernel_only:
         e2e_steps = max(3, min(20, K))
-        cache.truncate(TOKENS - GROUP)                      # make room again (a group boundary)
+        cache.truncate(min(TOKENS - GROUP, cache.tokens // GROUP * GROUP))                      # make room again (a group boundary)
         hkv = torch.randn((e2e_steps + 1, 2, segments, 1, DIM))                     # new keys and values of every step (host)
         host_in = torch.empty((2, segments, 1, DIM)).pin_memory()                   # where the caller puts a step's new token
         dkv = torch.empty((2, segments, 1, DIM), device=dev)                        # where it lands on the device
@@ -486,7 +486,7 @@ def run_ours(args) -> None:
             # the same with the WHOLE decoded cache copied back every step (what no consumer of a KV cache does;
             # reported for comparison with earlier runs): bound by the PCIe link
             n_full = 3
-            cache.truncate(TOKENS - GROUP)
+            cache.truncate(min(TOKENS - GROUP, cache.tokens // GROUP * GROUP))
             host_k = torch.empty((segments, cache.capacity, DIM), dtype=torch.bfloat16).pin_memory()
             host_v = torch.empty((segments, cache.capacity, DIM), dtype=torch.bfloat16).pin_memory()
             t0 = time.perf_counter()
