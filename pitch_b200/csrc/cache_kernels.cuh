@@ -761,6 +761,30 @@ cache_decode_kernel(const __grid_constant__ Cache64Params p) {
     // wait for it (and for its memory to be visible) before reading the cache, then let the next
     // kernel of the stream be scheduled as soon as multiprocessors free up (it waits for this grid
     // in the same way before it touches memory).
+    if (TICKETS && p.state == nullptr) {
+        // While waiting: ask the L2 for the codes and side information of the items this CTA's first round of
+        // tickets stands for (warp w: ticket w), so that the first fetches after the wait do not start from a
+        // cold cache.  A prefetch changes nothing that can be observed; the addresses are inside the planes'
+        // buffers whatever the previous kernel is still writing there.  (Measured at config 4's size: 83.0 us
+        // per step without, 81.5 us with one round, 81.7 with two, 82.4 with four.)
+        const int items_guess = (int)(p.tokens / TOKENS);
+        for (int k = warp; k < CD_WARPS && items_guess > 0; k += CD_WARPS) {
+            const int kp = k / p.n_planes, pl = k - kp * p.n_planes;
+            const int64_t pos = blockIdx.x + (int64_t)gridDim.x * kp;
+            if (pos >= (int64_t)p.segments * items_guess) break;
+            const int seg = (int)(pos / items_guess), item = (int)(pos - (int64_t)seg * items_guess);
+            const Plane64& P = p.plane[pl];
+            const unsigned char* codes = P.codes + seg * P.codes_seg_stride + (int64_t)item * (P.kind == 0 ? ITEM_CODE_BYTES : CH_ITEM_CODE_BYTES);
+            const unsigned char* side = P.side + seg * P.side_seg_stride +
+                                        (P.kind == 0 ? (int64_t)item * TOKENS * 4 : (int64_t)(item / P.group_items) * (2 * D) * 2);
+            // whole 128-byte pieces inside the item's own bytes only (at least the piece its first byte lies in)
+            const int code_lines = (P.kind == 0 ? ITEM_CODE_BYTES : CH_ITEM_CODE_BYTES) / 128;
+            const int side_bytes = P.kind == 0 ? TOKENS * 4 : 2 * D * 2;
+            const int side_lines = side_bytes >= 128 ? side_bytes / 128 : 1;
+            if (lane < code_lines) asm volatile("prefetch.global.L2 [%0];" :: "l"(codes + lane * 128));
+            else if (lane < code_lines + side_lines) asm volatile("prefetch.global.L2 [%0];" :: "l"(side + (lane - code_lines) * 128));
+        }
+    }
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;");
     unsigned char* stage = stage_base + warp * WarpStage<T, 64>::BYTES;
