@@ -761,16 +761,17 @@ cache_decode_kernel(const __grid_constant__ Cache64Params p) {
     // wait for it (and for its memory to be visible) before reading the cache, then let the next
     // kernel of the stream be scheduled as soon as multiprocessors free up (it waits for this grid
     // in the same way before it touches memory).
-    if (TICKETS && p.state == nullptr) {
-        // While waiting: ask the L2 for the codes and side information of the items this CTA's first round of
-        // tickets stands for (warp w: ticket w), so that the first fetches after the wait do not start from a
-        // cold cache.  A prefetch changes nothing that can be observed; the addresses are inside the planes'
+    if (p.state == nullptr) {
+        // While waiting: ask the L2 for the codes and side information of the items this CTA takes first
+        // (drawn deal: those its first round of tickets stands for, warp w: ticket w; fixed deal: every plane
+        // of the warp's first position), so that the first fetches after the wait do not start from a cold
+        // cache.  A prefetch changes nothing that can be observed; the addresses are inside the planes'
         // buffers whatever the previous kernel is still writing there.  (Measured at config 4's size: 83.0 us
         // per step without, 81.5 us with one round, 81.7 with two, 82.4 with four.)
         const int items_guess = (int)(p.tokens / TOKENS);
-        for (int k = warp; k < CD_WARPS && items_guess > 0; k += CD_WARPS) {
-            const int kp = k / p.n_planes, pl = k - kp * p.n_planes;
-            const int64_t pos = blockIdx.x + (int64_t)gridDim.x * kp;
+        for (int k = TICKETS ? warp : 0; k < (TICKETS ? CD_WARPS : p.n_planes) && items_guess > 0; k += TICKETS ? CD_WARPS : 1) {
+            const int kp = TICKETS ? k / p.n_planes : 0, pl = TICKETS ? k - kp * p.n_planes : k;
+            const int64_t pos = TICKETS ? blockIdx.x + (int64_t)gridDim.x * kp : (int64_t)warp * gridDim.x + blockIdx.x;
             if (pos >= (int64_t)p.segments * items_guess) break;
             const int seg = (int)(pos / items_guess), item = (int)(pos - (int64_t)seg * items_guess);
             const Plane64& P = p.plane[pl];
