@@ -587,6 +587,23 @@ attention_partial_kernel(const __grid_constant__ AttentionParams p) {
     const int R = p.n_queries;
     const uint32_t slot = (uint32_t)AT_TABLE_ADDR | (uint32_t)lane * 4u;
 
+    {
+        // Before anything else: ask the L2 for the first tile of this warp's first run (its codes arrive while
+        // the table is built and the grid waits for its predecessor).  A prefetch changes nothing that can be
+        // observed; the addresses are inside the planes' buffers.
+        const int run = blockIdx.x * C::WARPS + warp;
+        if (run < p.segments * p.splits) {
+            const int64_t seg = run / p.splits;
+            const int64_t tok = (int64_t)(run - (int)seg * p.splits) * p.tokens_per_split;
+            constexpr int LINES = G::STAGE_K / 128;                     // a tile's codes of one plane: 8, 16 or 12 lines
+            const int64_t left = ((int64_t)p.tokens - tok) * G::ROWB;   // bytes of codes from the tile's first token on
+            const unsigned char* src = lane < LINES ? p.k_codes + seg * p.k_codes_seg : p.v_codes + seg * p.v_codes_seg;
+            const int line = lane < LINES ? lane : lane - LINES;
+            if (lane < 2 * LINES && (int64_t)line * 128 < left)
+                asm volatile("prefetch.global.L2 [%0];" :: "l"(src + tok * G::ROWB + line * 128));
+        }
+    }
+
     for (int e = threadIdx.x; e < (1 << (2 * BITS)); e += C::THREADS) {
         // one table entry per thread (all pairs of codes), written to its 32 lane slots
         uint32_t hi, lo;
