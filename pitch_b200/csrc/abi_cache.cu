@@ -223,7 +223,7 @@ int launch_cache64_impl(const Cache64Params& p, int64_t tokens_for_grid, cudaStr
     constexpr int smem = cache64_smem_bytes<T>();
     if (dev >= 0 && dev < 64 && !configured[dev].load(std::memory_order_acquire)) {
         // idempotent: two threads racing here both set the same attribute
-        if (cudaFuncSetAttribute(cache_decode_kernel<T, D, BITS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(cache_decode_kernel<T, D, BITS, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
             return launch_status(false, "cache_decode (shared memory opt-in)");
         configured[dev].store(true, std::memory_order_release);
     }
@@ -245,7 +245,7 @@ int launch_cache64_impl(const Cache64Params& p, int64_t tokens_for_grid, cudaStr
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaLaunchKernelEx(&cfg, cache_decode_kernel<T, D, BITS, false>, p);
+    cudaLaunchKernelEx(&cfg, cache_decode_kernel<T, D, BITS, 0>, p);
     return PITCH_OK;
 }
 

@@ -73,6 +73,7 @@ int cache64_single_plane(int kind, int dim, int bits, int group_size, uint32_t s
 int launch_cache64_bias(const pitch::Cache64Params& p, int dim, int bits, int dtype, int64_t tokens_for_grid, cudaStream_t s);
 // The whole-cache launch with its items dealt by drawn tickets (cache_decode_kernel<..., true>): abi_cache_tickets.cu.
 int launch_cache64_tickets(const pitch::Cache64Params& p, int dim, int bits, int dtype, int64_t tokens_for_grid, cudaStream_t s);
+int launch_cache64_tickets_ahead(const pitch::Cache64Params& p, int dim, int bits, int dtype, int64_t tokens_for_grid, cudaStream_t s);
 
 }  // namespace pitch_abi
 

@@ -711,18 +711,23 @@ __device__ __forceinline__ void channel_step_warp(const Plane64& P, const StepPl
 //     receives the new TurboQuant vector (encoded by the warp that decodes it).  One warp each,
 //     taken first, by the warps that come last in the round-robin of the main items.
 //
-// TICKETS selects how the main items are dealt to the warps.  false: a fixed deal - warp w of CTA c is
+// DEAL selects how the main items are dealt to the warps.  0: a fixed deal - warp w of CTA c is
 // worker w * gridDim + c and takes every (gridDim * 16)-th position, planes innermost; nothing to compute
-// per item.  true: the positions are dealt to the CTAs round-robin and the warps of a CTA draw them, one
+// per item.  1: the positions are dealt to the CTAs round-robin and the warps of a CTA draw them, one
 // plane at a time, from a counter in shared memory as they become free: no warp idles at the end while
 // another still has a whole item more to do, and warps that got the costlier items fall behind no one.
 // That costs about 30 instructions per item.  It pays for a cache that mixes per-channel (cheap) and
 // TurboQuant (costly) planes - 2.7 % of the whole step at config 4's size, 12 % for an eighth of it, where
 // a warp has five items - and does not for a cache of TurboQuant planes only, whose launch is bound by
 // instruction issue (6 % slower at config 5's shape): the host picks.
-template <typename T, int D, int BITS, bool TICKETS>
+// DEAL 2 is the drawn deal plus a request to the L2, with every item fetched, for the item the CTA reaches 16
+// positions later: worth its instructions (and registers) only where a warp has few items and the start of
+// the launch weighs - a quarter or an eighth of config 4's cache: 23.3 -> 22.2 us and 13.7 -> 13.2 us per
+// step; the whole cache loses to it, 81.4 -> 82.3 us.
+template <typename T, int D, int BITS, int DEAL>
 __global__ void __launch_bounds__(CD_THREADS, 1)
 cache_decode_kernel(const __grid_constant__ Cache64Params p) {
+    constexpr bool TICKETS = DEAL != 0;
     constexpr int TOKENS = Item64<D>::TOKENS, LPV = Item64<D>::LPV;
     constexpr int ITEM_CODE_BYTES = 32 * 8 * BITS;          // TurboQuant: 32 lanes x 64 codes
     constexpr int CH_ITEM_CODE_BYTES = 1024;                // per-channel, 4 bits: 2048 codes
@@ -868,6 +873,25 @@ cache_decode_kernel(const __grid_constant__ Cache64Params p) {
         return true;
     };
 
+    // The item the CTA will reach AHEAD positions after the one just fetched (same plane): asked of the L2
+    // now, so that whichever warp draws it finds its codes there.  Every item is asked for once, by the warp
+    // that holds the ticket AHEAD positions before it.
+    constexpr int AHEAD = 16;
+    auto ask_ahead = [&](const Cursor64& c) {
+        if constexpr (DEAL != 2) return;
+        const int pos = c.seg * full_items + c.item + AHEAD * (int)gridDim.x;
+        if (pos >= positions) return;
+        int seg = __float2int_rd(__fmul_rd(__int2float_rd(pos), inv_items));
+        int item = pos - seg * full_items;
+        if (item >= full_items) { ++seg; item -= full_items; }
+        const Plane64& P = p.plane[c.pl];
+        const unsigned char* codes = P.codes + seg * P.codes_seg_stride + (int64_t)item * (P.kind == 0 ? ITEM_CODE_BYTES : CH_ITEM_CODE_BYTES);
+        const int code_lines = (P.kind == 0 ? ITEM_CODE_BYTES : CH_ITEM_CODE_BYTES) / 128;
+        if (lane < code_lines) asm volatile("prefetch.global.L2 [%0];" :: "l"(codes + lane * 128));
+        else if (lane == code_lines && P.kind == 0)
+            asm volatile("prefetch.global.L2 [%0];" :: "l"(P.side + seg * P.side_seg_stride + (int64_t)item * TOKENS * 4));
+    };
+
     if (!refuse) {
     // ---- edge items: the partial last item and everything an append touches
     if (edge_items > 0) {
@@ -916,12 +940,12 @@ cache_decode_kernel(const __grid_constant__ Cache64Params p) {
 #pragma unroll 1
                 while (true) {
                     bool more = resolve(drawn, nxt);
-                    if (more) { fetch(nxt, fb); drawn = ticket(); }
+                    if (more) { fetch(nxt, fb); drawn = ticket(); ask_ahead(nxt); }
                     decode(cur, fa);
                     if (!more) break;
                     cur = nxt;
                     more = resolve(drawn, nxt);
-                    if (more) { fetch(nxt, fa); drawn = ticket(); }
+                    if (more) { fetch(nxt, fa); drawn = ticket(); ask_ahead(nxt); }
                     decode(cur, fb);
                     if (!more) break;
                     cur = nxt;
